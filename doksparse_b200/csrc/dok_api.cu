@@ -1,0 +1,213 @@
+// C-ABI entry points of the fused DOK tensor paths (declared in include/doksparse.h): the keys of a batch are
+// formed on the fly from broadcast index tensors (or from the position of a non-zero element of a dense
+// tensor) instead of being materialised as an int64[n, ndim] matrix first.
+#include "dok_kernels.cuh"
+
+// dense source of __setitem__ viewed through the selector's common shape (strides in elements, 0 = broadcast);
+// replaces the extra StrictTensorAccessor of sparse_dok_set_items_dense (sparse_dok_tensor_impl.cu:290,309).
+struct StridedValues {
+  const char *src;
+  int selector_ndim;
+  ll_t sizes[DOK_MAX_SELECTOR_NDIM];
+  ll_t strides[DOK_MAX_SELECTOR_NDIM];
+  __device__ __forceinline__ const char *row(const DevTable &t, ll_t e) const {
+    ull_t rem = (ull_t)e;
+    ll_t off = 0;
+    for (int j = selector_ndim - 1; j >= 0; j--) {
+      const ull_t size = (ull_t)sizes[j];
+      const ull_t q = rem / size;
+      off += (ll_t)(rem - q * size) * strides[j];
+      rem = q;
+    }
+    return src + off * (ll_t)t.vb;
+  }
+};
+
+static bool make_sel(const dok_selectors *sel, const DevHash &dh, SelKeys *out) {
+  if (!sel || sel->ndim != dh.ks || dh.dtype != DOK_I64) return false;
+  if (sel->selector_ndim < 0 || sel->selector_ndim > DOK_MAX_SELECTOR_NDIM) return false;
+  ll_t n = 1;
+  for (int j = 0; j < sel->selector_ndim; j++) {
+    if (sel->sizes[j] < 0) return false;
+    n *= sel->sizes[j];
+  }
+  for (int d = 0; d < sel->ndim; d++) if (n > 0 && !sel->ptr[d]) return false;
+  out->s = *sel;
+  out->n = n;
+  return n <= DOK_MAX_BATCH;
+}
+
+// ---- from_dense ------------------------------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ bool dok_nonzero(T bits, int is_float) {
+  // `x != 0`: for floating types both signed zeros compare equal to zero, NaN does not
+  return is_float ? (T)(bits << 1) != 0 : bits != 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(DOK_TPB) k_dense_count(const T *__restrict__ dense, ll_t numel, int is_float, ll_t *count_out) {
+  int c = 0;
+  const ll_t stride = (ll_t)gridDim.x * DOK_TPB;
+  for (ll_t i = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x; i < numel; i += stride) c += dok_nonzero<T>(__ldcs(dense + i), is_float);
+  dok_warp_add(count_out, c);
+}
+
+struct DenseShape { int ndim; ll_t sizes[DOK_MAX_KEY_SIZE]; };
+
+template <typename T>
+__global__ void __launch_bounds__(DOK_TPB) k_dense_insert(DevTable t, DevHash hp, const T *__restrict__ dense, ll_t numel,
+                                                          int is_float, DenseShape shape, ll_t *counters) {
+  int outcome = -1;
+  const ll_t stride = (ll_t)gridDim.x * DOK_TPB;
+  for (ll_t base = (ll_t)blockIdx.x * DOK_TPB; base < numel; base += stride) {
+    const ll_t i = base + threadIdx.x;
+    outcome = -1;
+    if (i < numel) {
+      const T v = __ldcs(dense + i);
+      if (dok_nonzero<T>(v, is_float)) {
+        // unravel the row-major position into the index tuple; each index is one factor of the uuid product
+        ll_t idx[DOK_MAX_KEY_SIZE];
+        ull_t rem = (ull_t)i;
+#pragma unroll
+        for (int d = DOK_MAX_KEY_SIZE - 1; d >= 0; d--) {
+          idx[d] = 0;
+          if (d < shape.ndim) {
+            const ull_t size = (ull_t)shape.sizes[d];
+            const ull_t q = rem / size;
+            idx[d] = (ll_t)(rem - q * size);
+            rem = q;
+          }
+        }
+        ll_t u = dok_uuid_term(idx[0], hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+#pragma unroll
+        for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
+          if (d < shape.ndim) u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
+        const ll_t uuid = dok_llabs(u);
+        const ll_t slot = dok_find_or_claim(t, uuid, &outcome);
+        if (slot >= 0) {
+          ll_t *krow = (ll_t *)(t.keys + slot * (ll_t)t.kb);
+#pragma unroll
+          for (int d = 0; d < DOK_MAX_KEY_SIZE; d++) if (d < shape.ndim) krow[hp.perm[d]] = idx[d];
+          *(T *)(t.buckets + slot * (ll_t)t.bb + 8) = v;
+        }
+      }
+    }
+    if (counters) {
+      dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
+      dok_warp_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
+      dok_warp_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
+      dok_warp_add(counters + DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
+    }
+  }
+}
+
+static unsigned streaming_grid(ll_t numel) {
+  const ll_t blocks = (numel + DOK_TPB - 1) / DOK_TPB;
+  const ll_t cap = 148 * 8;   // 8 resident blocks of 256 threads per SM
+  return (unsigned)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
+extern "C" {
+
+int dok_dok_get(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel, void *out_values,
+                uint8_t *out_found, const void *fallback, int64_t *counters, void *stream) {
+  DevHash dh;
+  DevTable dt;
+  SelKeys sk;
+  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || !make_sel(sel, dh, &sk)) return DOK_BAD_ARG;
+  if (sk.n > 0 && !out_values) return DOK_BAD_ARG;
+  return launch_get(dt, dh, sk, out_values, out_found, fallback, counters, 0, (cudaStream_t)stream);
+}
+
+int dok_dok_count_exists(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel, int64_t *counters,
+                         void *stream) {
+  DevHash dh;
+  DevTable dt;
+  SelKeys sk;
+  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || !make_sel(sel, dh, &sk) || !counters) return DOK_BAD_ARG;
+  if (sk.n == 0) return DOK_OK;
+  k_find<0><<<(unsigned)((sk.n + DOK_TPB - 1) / DOK_TPB), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, nullptr, (ll_t *)counters);
+  return dok_check_launch();
+}
+
+int dok_dok_zero_items(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel, int64_t *counters,
+                       void *stream) {
+  DevHash dh;
+  DevTable dt;
+  SelKeys sk;
+  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || !make_sel(sel, dh, &sk) || !counters) return DOK_BAD_ARG;
+  if (sk.n == 0) return DOK_OK;
+  k_find<1><<<(unsigned)((sk.n + DOK_TPB - 1) / DOK_TPB), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, nullptr, (ll_t *)counters);
+  return dok_check_launch();
+}
+
+int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel, const void *src,
+                      const int64_t *src_strides, int64_t *slot_scratch, int64_t epoch, int64_t *counters,
+                      void *stream) {
+  DevHash dh;
+  DevTable dt;
+  SelKeys sk;
+  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || !make_sel(sel, dh, &sk)) return DOK_BAD_ARG;
+  if (sk.n == 0) return DOK_OK;
+  if (!src || !src_strides || !slot_scratch || !dt.stamp || epoch < 1 || epoch > 0x7fffffffLL) return DOK_BAD_ARG;
+  StridedValues sv;
+  sv.src = (const char *)src;
+  sv.selector_ndim = sel->selector_ndim;
+  for (int j = 0; j < DOK_MAX_SELECTOR_NDIM; j++) {
+    sv.sizes[j] = j < sel->selector_ndim ? sel->sizes[j] : 1;
+    sv.strides[j] = j < sel->selector_ndim ? src_strides[j] : 0;
+  }
+  const unsigned grid = (unsigned)((sk.n + DOK_TPB - 1) / DOK_TPB);
+  k_set_claim<<<grid, DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, (ll_t *)slot_scratch, (ll_t)epoch, (ll_t *)counters);
+  int rc = dok_check_launch();
+  if (rc != DOK_OK) return rc;
+  k_set_write<<<grid, DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, sv, (const ll_t *)slot_scratch, (ll_t)epoch, nullptr);
+  return dok_check_launch();
+}
+
+int dok_dense_count_nonzero(const void *dense, int64_t numel, int elem_bytes, int is_float, int64_t *count_out,
+                            void *stream) {
+  if (numel < 0 || !count_out || (numel > 0 && !dense)) return DOK_BAD_ARG;
+  if (numel == 0) return DOK_OK;
+  const unsigned grid = streaming_grid(numel);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (elem_bytes) {
+    case 1: k_dense_count<unsigned char><<<grid, DOK_TPB, 0, st>>>((const unsigned char *)dense, numel, is_float, (ll_t *)count_out); break;
+    case 2: k_dense_count<unsigned short><<<grid, DOK_TPB, 0, st>>>((const unsigned short *)dense, numel, is_float, (ll_t *)count_out); break;
+    case 4: k_dense_count<unsigned><<<grid, DOK_TPB, 0, st>>>((const unsigned *)dense, numel, is_float, (ll_t *)count_out); break;
+    case 8: k_dense_count<ull_t><<<grid, DOK_TPB, 0, st>>>((const ull_t *)dense, numel, is_float, (ll_t *)count_out); break;
+    default: return DOK_BAD_ARG;
+  }
+  return dok_check_launch();
+}
+
+int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, const void *dense, const int64_t *sizes,
+                             int64_t numel, int is_float, int64_t *counters, void *stream) {
+  DevHash dh;
+  DevTable dt;
+  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || dh.dtype != DOK_I64 || !sizes || numel < 0) return DOK_BAD_ARG;
+  if (numel == 0) return DOK_OK;
+  if (!dense) return DOK_BAD_ARG;
+  DenseShape shape;
+  shape.ndim = dh.ks;
+  ll_t prod = 1;
+  for (int d = 0; d < DOK_MAX_KEY_SIZE; d++) {
+    shape.sizes[d] = d < dh.ks ? sizes[d] : 1;
+    if (shape.sizes[d] < 1) return DOK_BAD_ARG;
+    prod *= shape.sizes[d];
+  }
+  if (prod != numel) return DOK_BAD_ARG;
+  const unsigned grid = streaming_grid(numel);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (dt.vb) {
+    case 1: k_dense_insert<unsigned char><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned char *)dense, numel, is_float, shape, (ll_t *)counters); break;
+    case 2: k_dense_insert<unsigned short><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned short *)dense, numel, is_float, shape, (ll_t *)counters); break;
+    case 4: k_dense_insert<unsigned><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned *)dense, numel, is_float, shape, (ll_t *)counters); break;
+    case 8: k_dense_insert<ull_t><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const ull_t *)dense, numel, is_float, shape, (ll_t *)counters); break;
+    default: return DOK_BAD_ARG;
+  }
+  return dok_check_launch();
+}
+
+}  // extern "C"

@@ -1,0 +1,170 @@
+// Batch routing for the hash-sharded table (declared in include/doksparse.h): a stable partition of a batch by
+// owner shard, and the inverse permutation applied to the results.  The reference is single-GPU and has no
+// counterpart; what is preserved is its single-table semantics: rows keep their batch order inside each owner's
+// segment, so "last row wins" on the owner equals "last row wins" on one big table.
+#include "dok_host.cuh"
+
+#define DOK_PART_ROUNDS 8
+#define DOK_PART_TILE (DOK_TPB * DOK_PART_ROUNDS)
+
+__device__ __forceinline__ void dok_copy_row(char *dst, const char *src, int bytes) {
+  if ((bytes & 7) == 0) for (int i = 0; i < (bytes >> 3); i++) ((ull_t *)dst)[i] = ((const ull_t *)src)[i];
+  else if ((bytes & 3) == 0) for (int i = 0; i < (bytes >> 2); i++) ((unsigned *)dst)[i] = ((const unsigned *)src)[i];
+  else if ((bytes & 1) == 0) for (int i = 0; i < (bytes >> 1); i++) ((unsigned short *)dst)[i] = ((const unsigned short *)src)[i];
+  else for (int i = 0; i < bytes; i++) dst[i] = src[i];
+}
+
+static __global__ void __launch_bounds__(DOK_TPB) k_part_count(DevHash hp, RowKeys keys, int n_shards, ll_t tiles,
+                                                               ll_t *__restrict__ tile_counts) {
+  __shared__ int hist[DOK_MAX_SHARDS];
+  if (threadIdx.x < DOK_MAX_SHARDS) hist[threadIdx.x] = 0;
+  __syncthreads();
+  const ll_t base = (ll_t)blockIdx.x * DOK_PART_TILE;
+#pragma unroll
+  for (int r = 0; r < DOK_PART_ROUNDS; r++) {
+    const ll_t e = base + r * DOK_TPB + threadIdx.x;
+    if (e < keys.n) atomicAdd(&hist[dok_owner_shard(keys.uuid(hp, e), n_shards)], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < n_shards) tile_counts[(ll_t)threadIdx.x * tiles + blockIdx.x] = hist[threadIdx.x];
+}
+
+// In-place exclusive scan by one block; a[n] receives the total.
+static __global__ void __launch_bounds__(1024) k_part_scan(ll_t *a, ll_t n) {
+  __shared__ ll_t partial[1024];
+  const ll_t per = (n + 1023) / 1024;
+  const ll_t lo = threadIdx.x * per, hi = lo + per < n ? lo + per : n;
+  ll_t s = 0;
+  for (ll_t i = lo; i < hi; i++) s += a[i];
+  partial[threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ll_t run = 0;
+    for (int i = 0; i < 1024; i++) { const ll_t v = partial[i]; partial[i] = run; run += v; }
+    a[n] = run;
+  }
+  __syncthreads();
+  ll_t run = partial[threadIdx.x];
+  for (ll_t i = lo; i < hi; i++) { const ll_t v = a[i]; a[i] = run; run += v; }
+}
+
+static __global__ void k_part_shard_counts(const ll_t *tile_offsets, int n_shards, ll_t tiles, ll_t *shard_counts) {
+  const int o = threadIdx.x;
+  if (o < n_shards) shard_counts[o] = tile_offsets[(ll_t)(o + 1) * tiles] - tile_offsets[(ll_t)o * tiles];
+}
+
+static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(DevHash hp, RowKeys keys, const char *__restrict__ values,
+                                                                 int vb, int n_shards, ll_t tiles,
+                                                                 const ll_t *__restrict__ tile_offsets, char *keys_out,
+                                                                 char *values_out, ll_t *__restrict__ dest_index) {
+  __shared__ int warp_count[DOK_TPB / 32][DOK_MAX_SHARDS];
+  __shared__ int running[DOK_MAX_SHARDS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int kb = hp.ks * hp.elem_bytes;
+  for (int i = threadIdx.x; i < (DOK_TPB / 32) * DOK_MAX_SHARDS; i += DOK_TPB) (&warp_count[0][0])[i] = 0;
+  if (threadIdx.x < DOK_MAX_SHARDS) running[threadIdx.x] = 0;
+  __syncthreads();
+  const ll_t base = (ll_t)blockIdx.x * DOK_PART_TILE;
+  for (int r = 0; r < DOK_PART_ROUNDS; r++) {
+    const ll_t e = base + r * DOK_TPB + threadIdx.x;
+    const int owner = e < keys.n ? dok_owner_shard(keys.uuid(hp, e), n_shards) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, owner);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (owner >= 0 && rank == 0) warp_count[warp][owner] = __popc(peers);
+    __syncthreads();
+    if (owner >= 0) {
+      int before = running[owner] + rank;
+      for (int w = 0; w < warp; w++) before += warp_count[w][owner];
+      const ll_t dest = tile_offsets[(ll_t)owner * tiles + blockIdx.x] + before;
+      dest_index[e] = dest;
+      dok_copy_row(keys_out + dest * kb, (const char *)keys.keys + e * kb, kb);
+      if (values) dok_copy_row(values_out + dest * vb, values + e * vb, vb);
+    }
+    __syncthreads();
+    if (threadIdx.x < n_shards) {
+      int s = 0;
+      for (int w = 0; w < DOK_TPB / 32; w++) { s += warp_count[w][threadIdx.x]; warp_count[w][threadIdx.x] = 0; }
+      running[threadIdx.x] += s;
+    }
+    __syncthreads();
+  }
+}
+
+static __global__ void __launch_bounds__(DOK_TPB) k_unpermute(const char *__restrict__ grouped_values,
+                                                              const uint8_t *__restrict__ grouped_found,
+                                                              const ll_t *__restrict__ dest_index, int vb, ll_t n,
+                                                              char *__restrict__ out_values, uint8_t *__restrict__ out_found) {
+  const ll_t i = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
+  if (i >= n) return;
+  const ll_t g = dest_index[i];
+  if (out_values) dok_copy_row(out_values + i * vb, grouped_values + g * vb, vb);
+  if (out_found) out_found[i] = grouped_found[g];
+}
+
+extern "C" {
+
+int64_t dok_partition_tiles(int64_t n) { return (n + DOK_PART_TILE - 1) / DOK_PART_TILE; }
+
+int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards,
+                              int64_t *tile_offsets, int64_t *shard_counts, void *stream) {
+  DevHash dh;
+  if (!dok_make_hash(hp, &dh) || n < 0 || n > DOK_MAX_BATCH || n_shards < 1 || n_shards > DOK_MAX_SHARDS) return DOK_BAD_ARG;
+  if (!tile_offsets || !shard_counts || (n > 0 && !keys)) return DOK_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const ll_t tiles = dok_partition_tiles(n);
+  if (tiles > 0) {
+    RowKeys rk{keys, n};
+    k_part_count<<<(unsigned)tiles, DOK_TPB, 0, st>>>(dh, rk, n_shards, tiles, (ll_t *)tile_offsets);
+    int rc = dok_check_launch();
+    if (rc != DOK_OK) return rc;
+  }
+  k_part_scan<<<1, 1024, 0, st>>>((ll_t *)tile_offsets, (ll_t)n_shards * tiles);
+  int rc = dok_check_launch();
+  if (rc != DOK_OK) return rc;
+  k_part_shard_counts<<<1, DOK_MAX_SHARDS, 0, st>>>((const ll_t *)tile_offsets, n_shards, tiles, (ll_t *)shard_counts);
+  return dok_check_launch();
+}
+
+int dok_shard_partition_scatter(const dok_hash_params *hp, const void *keys, const void *values, int value_bytes,
+                                int64_t n, int n_shards, const int64_t *tile_offsets, void *keys_out, void *values_out,
+                                int64_t *dest_index, void *stream) {
+  DevHash dh;
+  if (!dok_make_hash(hp, &dh) || n < 0 || n > DOK_MAX_BATCH || n_shards < 1 || n_shards > DOK_MAX_SHARDS) return DOK_BAD_ARG;
+  if (n == 0) return DOK_OK;
+  if (!keys || !tile_offsets || !keys_out || !dest_index) return DOK_BAD_ARG;
+  if (values && (!values_out || value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES)) return DOK_BAD_ARG;
+  const ll_t tiles = dok_partition_tiles(n);
+  RowKeys rk{keys, n};
+  k_part_scatter<<<(unsigned)tiles, DOK_TPB, 0, (cudaStream_t)stream>>>(
+      dh, rk, (const char *)values, value_bytes, n_shards, tiles, (const ll_t *)tile_offsets, (char *)keys_out,
+      (char *)values_out, (ll_t *)dest_index);
+  return dok_check_launch();
+}
+
+int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found, const int64_t *dest_index,
+                        int value_bytes, int64_t n, void *out_values, uint8_t *out_found, void *stream) {
+  if (n < 0 || n > DOK_MAX_BATCH) return DOK_BAD_ARG;
+  if (n == 0) return DOK_OK;
+  if (!dest_index || (out_values && (!grouped_values || value_bytes < 1)) || (out_found && !grouped_found)) return DOK_BAD_ARG;
+  k_unpermute<<<(unsigned)((n + DOK_TPB - 1) / DOK_TPB), DOK_TPB, 0, (cudaStream_t)stream>>>(
+      (const char *)grouped_values, grouped_found, (const ll_t *)dest_index, value_bytes, n, (char *)out_values, out_found);
+  return dok_check_launch();
+}
+
+/* owner shard of each row (diagnostics and host-side tests of the routing) */
+static __global__ void k_owner(DevHash hp, RowKeys keys, int n_shards, int *owner_out) {
+  const ll_t e = (ll_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e < keys.n) owner_out[e] = dok_owner_shard(keys.uuid(hp, e), n_shards);
+}
+
+int dok_shard_owner(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, int32_t *owner_out,
+                    void *stream) {
+  DevHash dh;
+  if (!dok_make_hash(hp, &dh) || n < 0 || n_shards < 1 || n_shards > DOK_MAX_SHARDS || (n > 0 && (!keys || !owner_out))) return DOK_BAD_ARG;
+  if (n == 0) return DOK_OK;
+  RowKeys rk{keys, n};
+  k_owner<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(dh, rk, n_shards, owner_out);
+  return dok_check_launch();
+}
+
+}  // extern "C"

@@ -1,0 +1,581 @@
+"""CudaClosedHashmap: the reference's batched GPU hash map
+(sparse_dok/components/cuda_closed_hashmap.py) with the same constructor, methods, attributes and
+error behaviour, on top of libdoksparse.so.
+
+What is kept from the reference
+  * key identity is the 64-bit uuid; uuids are bit-identical for identical parameters and keys;
+  * parameters are drawn lazily from the global numpy random state with the reference's calls and
+    in the reference's order (:66-113, :350-357), so a seeded run draws the same parameters;
+  * set / get / remove / rehash bookkeeping: n_elements, n_buckets, rehash trigger and new size
+    (:363-366), `remove` dedups with `unique(dim=0)` and returns flags for the sorted unique rows
+    (:438-454), `set` returns None (:384), RuntimeError("store something first") (:391-392).
+What is different (the slot layout is not part of the contract)
+  * `_uuid` and `_values` are strided views of one interleaved bucket array; `_keys` is separate;
+  * the start bucket comes from a mixer of the uuid, not from prime1/alpha1/beta1 (which are still
+    drawn, to keep the random stream aligned with the reference);
+  * duplicates inside one `set` batch resolve deterministically to the last row.
+"""
+import ctypes
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from . import _lib as L
+from .util import next_prime
+
+
+class CudaClosedHashmap:
+    def __init__(
+        self,
+        n_buckets=1024,
+        device="cuda:0",
+        prime1=None,
+        prime2=None,
+        alpha1=None,
+        alpha2=None,
+        beta1=None,
+        beta2=None,
+        key_size=None,
+        key_perm=None,
+        rehash_factor=2.0,
+        rehash_threshold=0.75,
+    ):
+        self._empty_marker = -1
+        self._removed_marker = -3
+        self._n_buckets = int(n_buckets)
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise L.DokError("CudaClosedHashmap needs a CUDA device: there is no CPU path")
+        L.lib()  # fail loudly now if the extension is missing
+        # before the first `set` only the tags exist (cuda_closed_hashmap.py:40)
+        self._buckets = None
+        self._uuid_only = torch.full((self._n_buckets,), self._empty_marker, device=self.device, dtype=torch.long)
+        self._key_store = None
+        # state that shallow clones (views) must see together: the duplicate-resolution stamps with their epoch,
+        # and the host-side upper bound of n_elements that lets `set` skip a device synchronisation
+        self._shared = {"stamp": None, "epoch": 0, "bound": 0}
+        self._value_shape = None
+        self._value_dtype = None
+
+        self._key_size = key_size
+        self._prime1, self._prime2 = prime1, prime2
+        self._alpha1, self._alpha2 = alpha1, alpha2
+        self._beta1, self._beta2 = beta1, beta2
+        self._n_elements = torch.zeros(size=(), device=self.device, dtype=torch.long)
+        self._rehash_factor = rehash_factor
+        self._rehash_threshold = rehash_threshold
+
+        self._key_perm = None
+        if key_perm is not None:
+            if not isinstance(key_perm, Tensor):
+                key_perm = torch.tensor(key_perm, dtype=torch.long, device=self.device)
+            self._key_perm = key_perm.to(device=self.device, dtype=torch.long)
+        self._hp = None       # cached ctypes dok_hash_params
+        self._table = None
+
+    # ------------------------------------------------------------------ parameters (lazy, reference order)
+    def _current_key_size(self):
+        assert self._key_store is not None or self._key_size is not None
+        if self._key_store is not None:
+            return int(np.prod(self._key_store.shape[1:]))
+        return int(self._key_size)
+
+    def _as_param(self, values):
+        return torch.tensor([int(v) for v in values], device=self.device, dtype=torch.long)
+
+    @property
+    def prime1(self):
+        if self._prime1 is None:
+            raw = [np.random.randint(self.n_buckets, self.n_buckets * 2) for _ in range(self._current_key_size())]
+            self._prime1 = self._as_param(next_prime(r) for r in raw)
+        return self._prime1
+
+    @property
+    def prime2(self):
+        if self._prime2 is None:
+            raw = [np.random.randint(0, 2 ** 60, dtype="int64") for _ in range(self._current_key_size())]
+            self._prime2 = self._as_param(next_prime(r) for r in raw)
+        return self._prime2
+
+    def _draw_below_prime1(self):
+        return self._as_param(np.random.randint(int(p)) - 1 for p in self.prime1.cpu())
+
+    @property
+    def alpha1(self):
+        if self._alpha1 is None:
+            self._alpha1 = self._draw_below_prime1()
+        return self._alpha1
+
+    @property
+    def alpha2(self):
+        if self._alpha2 is None:
+            self._alpha2 = self._draw_below_prime1()
+        return self._alpha2
+
+    @property
+    def beta1(self):
+        if self._beta1 is None:
+            self._beta1 = self._draw_below_prime1()
+        return self._beta1
+
+    @property
+    def beta2(self):
+        if self._beta2 is None:
+            self._beta2 = self._draw_below_prime1()
+        return self._beta2
+
+    @property
+    def key_perm(self):
+        if self._key_perm is None:
+            assert self._key_store is not None
+            self._key_perm = torch.arange(int(np.prod(self.key_shape)), device=self.device)
+        else:
+            assert self._key_perm.shape[0] == np.prod(self.key_shape)
+        return self._key_perm
+
+    @key_perm.setter
+    def key_perm(self, new):
+        if not isinstance(new, Tensor):
+            new = torch.tensor([int(i) for i in new], device=self.device, dtype=torch.long)
+        new = new.to(device=self.device, dtype=torch.long)
+        assert new.shape == self.key_perm.shape
+        self._key_perm = new
+        self._hp = None
+
+    def _materialise_parameters(self):
+        # evaluation order of the reference's kernel call (cuda_closed_hashmap.py:350-357)
+        return (self.prime1, self.prime2, self.alpha1, self.alpha2, self.beta1, self.beta2, self.key_perm)
+
+    # ------------------------------------------------------------------ storage
+    def _allocate(self, key_shape, key_dtype, value_shape, value_dtype):
+        value_bytes = int(np.prod(value_shape, dtype=np.int64)) * torch.empty((), dtype=value_dtype).element_size()
+        key_size = int(np.prod(key_shape, dtype=np.int64))
+        if key_dtype not in L.DTYPE_CODES:
+            raise L.DokError(f"unsupported key dtype {key_dtype}")
+        if not (1 <= key_size <= L.MAX_KEY_SIZE):
+            raise L.DokError(f"keys may have 1..{L.MAX_KEY_SIZE} elements, got {key_size}")
+        if not (1 <= value_bytes <= L.MAX_VALUE_BYTES):
+            raise L.DokError(f"value rows may have 1..{L.MAX_VALUE_BYTES} bytes, got {value_bytes}")
+        bb = L.lib().dok_bucket_bytes(value_bytes)
+        self._bucket_bytes, self._value_bytes = bb, value_bytes
+        self._value_shape, self._value_dtype = torch.Size(value_shape), value_dtype
+        self._buckets = torch.empty(self._n_buckets * bb, device=self.device, dtype=torch.uint8)
+        self._key_store = torch.empty(self._n_buckets, *key_shape, device=self.device, dtype=key_dtype)
+        self._uuid_only = None
+        self._shared["stamp"] = None
+        self._hp = None
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_map_init(self._c_table(), L.stream_ptr(self.device)), "dok_map_init")
+
+    def _begin_bulk_insert(self, key_shape, key_dtype, value_shape, value_dtype, n_new):
+        """What `set` does to a never-used map before its kernel runs, for a batch known to hold `n_new` pairwise
+        different new keys: allocate, draw the parameters, grow if the reference's trigger fires (which re-draws them,
+        cuda_closed_hashmap.py:365-366, 456-468), account for the new elements.  The caller then inserts the rows."""
+        assert self._key_store is None
+        self._allocate(key_shape, key_dtype, value_shape, value_dtype)
+        if n_new == 0:
+            return
+        self._materialise_parameters()
+        if n_new > int(self._rehash_threshold * self.n_buckets):
+            self.__init__(n_buckets=int(n_new * self._rehash_factor), device=self.device, key_perm=self._key_perm,
+                          rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold)
+            self._allocate(key_shape, key_dtype, value_shape, value_dtype)
+            self._materialise_parameters()
+        self._n_elements += n_new
+        self._shared["bound"] = n_new
+
+    @property
+    def _uuid(self):
+        """[n_buckets] int64 tags: uuid, -1 empty, -3 removed (a strided view of the bucket array)."""
+        if self._buckets is None:
+            return self._uuid_only
+        return self._buckets.view(torch.int64).as_strided((self._n_buckets,), (self._bucket_bytes // 8,), 0)
+
+    @property
+    def _values(self):
+        """[n_buckets, *value_shape] view of the value bytes inside the bucket array (None before the first set)."""
+        if self._buckets is None:
+            return None
+        es = torch.empty((), dtype=self._value_dtype).element_size()
+        inner = []
+        acc = 1
+        for s in reversed(self._value_shape):
+            inner.append(acc)
+            acc *= s
+        strides = (self._bucket_bytes // es,) + tuple(reversed(inner))
+        return self._buckets.view(self._value_dtype).as_strided((self._n_buckets,) + tuple(self._value_shape), strides, 8 // es)
+
+    @property
+    def _keys(self):
+        """[n_buckets, *key_shape] key rows in storage-column order (None before the first set)."""
+        return self._key_store
+
+    def _ensure_stamp(self):
+        sh = self._shared
+        if sh["stamp"] is None:
+            sh["stamp"] = torch.zeros(self._n_buckets, device=self.device, dtype=torch.long)
+            sh["epoch"] = 0
+        if sh["epoch"] >= 2 ** 31 - 2:
+            sh["stamp"].zero_()
+            sh["epoch"] = 0
+        sh["epoch"] += 1
+        return sh["epoch"]
+
+    def _c_table(self):
+        t = L.Table()
+        t.buckets = self._buckets.data_ptr()
+        t.keys = self._key_store.data_ptr()
+        stamp = self._shared["stamp"]
+        t.stamp = stamp.data_ptr() if stamp is not None else None
+        t.n_buckets = self._n_buckets
+        t.bucket_bytes = self._bucket_bytes
+        t.value_bytes = self._value_bytes
+        self._table = t   # keeps the struct alive for the duration of the call
+        return ctypes.byref(t)
+
+    def _c_hash(self):
+        if self._hp is None:
+            self._materialise_parameters()
+            hp = L.HashParams()
+            ks = int(np.prod(self.key_shape))
+            hp.key_size = ks
+            hp.key_dtype = L.DTYPE_CODES[self._key_store.dtype]
+            a2, b2, p2, perm = (x.cpu().tolist() for x in (self.alpha2, self.beta2, self.prime2, self.key_perm))
+            assert len(a2) == len(b2) == len(p2) == len(perm) == ks
+            for i in range(ks):
+                hp.alpha2[i], hp.beta2[i], hp.prime2[i], hp.key_perm[i] = a2[i], b2[i], p2[i], perm[i]
+                assert abs(p2[i]) >= 2, "prime2 entries must have magnitude >= 2"
+            self._hp = hp
+        return ctypes.byref(self._hp)
+
+    def _counters(self):
+        return torch.zeros(L.N_COUNTERS, device=self.device, dtype=torch.long)
+
+    # ------------------------------------------------------------------ compaction
+    def items(self, keys=True, values=True, uuid=True, transposed_keys=False):
+        """(keys, values, uuid) of the live slots in slot order, from one pass over the tags."""
+        assert self._buckets is not None
+        lib = L.lib()
+        with torch.cuda.device(self.device):
+            st = L.stream_ptr(self.device)
+            tiles = lib.dok_compact_tiles(self._n_buckets)
+            offsets = torch.empty(tiles + 1, device=self.device, dtype=torch.long)
+            L.check(lib.dok_map_compact_count(self._c_table(), L.ptr(offsets), st), "dok_map_compact_count")
+            count = int(offsets[-1].item())
+            ks = int(np.prod(self.key_shape))
+            k = v = u = None
+            if keys:
+                shape = (ks, count) if transposed_keys else (count, ks)
+                k = torch.empty(shape, device=self.device, dtype=self._key_store.dtype)
+            if values:
+                v = torch.empty((count,) + tuple(self._value_shape), device=self.device, dtype=self._value_dtype)
+            if uuid:
+                u = torch.empty(count, device=self.device, dtype=torch.long)
+            if count:
+                L.check(lib.dok_map_compact_scatter(self._c_table(), self._c_hash(), L.ptr(offsets), L.ptr(k),
+                                                    int(transposed_keys), L.ptr(v), L.ptr(u), st),
+                        "dok_map_compact_scatter")
+        return k, v, u
+
+    @property
+    def nonempty_mask(self):
+        return (self._uuid != self._empty_marker) & (self._uuid != self._removed_marker)
+
+    def keys(self):
+        if self._key_store is None:
+            return None
+        return self.items(values=False, uuid=False)[0]
+
+    def values(self):
+        if self._buckets is None:
+            return None
+        return self.items(keys=False, uuid=False)[1]
+
+    def uuid(self):
+        if self._buckets is None:
+            return self._uuid_only[:0]
+        return self.items(keys=False, values=False)[2]
+
+    def set_values(self, selectors, new_values):
+        masked_values = self._values[self.nonempty_mask]
+        masked_values[selectors] = new_values
+        self._values[self.nonempty_mask] = masked_values
+
+    def permute_keys(self, ordering):
+        assert self._key_store is not None, "hashmap is empty"
+        assert len(self.key_shape) == 1, "keys are not one dimensional"
+        assert len(ordering) == self.key_shape[0]
+        assert len(set(ordering)) == len(ordering), "duplicates are not allowed"
+        self._materialise_parameters()
+        self._key_store = self._key_store[:, ordering].contiguous()
+        for name in ("_alpha1", "_alpha2", "_beta1", "_beta2", "_prime1", "_prime2"):
+            setattr(self, name, getattr(self, name)[ordering])
+        self._key_size = int(np.prod(self._key_store.shape[1:]))
+        self._hp = None
+
+    def clone(self, deepclone=False):
+        self._materialise_parameters()
+        cp = (lambda x: x.clone()) if deepclone else (lambda x: x)
+        new = CudaClosedHashmap(
+            n_buckets=self.n_buckets, device=self.device,
+            prime1=cp(self.prime1), prime2=cp(self.prime2), alpha1=cp(self.alpha1), alpha2=cp(self.alpha2),
+            beta1=cp(self.beta1), beta2=cp(self.beta2), key_perm=cp(self._key_perm),
+            rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
+        )
+        if self._buckets is not None:
+            new._buckets = cp(self._buckets)
+            new._key_store = cp(self._key_store)
+            new._uuid_only = None
+            new._bucket_bytes, new._value_bytes = self._bucket_bytes, self._value_bytes
+            new._value_shape, new._value_dtype = self._value_shape, self._value_dtype
+        else:
+            new._uuid_only = cp(self._uuid_only)
+        new._n_elements = cp(self._n_elements)
+        if deepclone:
+            new._shared["bound"] = self._shared["bound"]
+        else:
+            new._shared = self._shared   # a view writes the same slots: same stamps, epoch and bound
+        return new
+
+    # ------------------------------------------------------------------ sizes
+    @property
+    def n_elements(self):
+        n = int(self._n_elements.item())
+        self._shared["bound"] = n
+        return n
+
+    @property
+    def n_buckets(self):
+        return self._n_buckets
+
+    @property
+    def load_factor(self):
+        return self.n_elements / self.n_buckets
+
+    @property
+    def n_tombstones(self):
+        return int((self._uuid == self._removed_marker).sum().item())
+
+    @property
+    def key_shape(self):
+        assert self._key_store is not None
+        return self._key_store.shape[1:]
+
+    @property
+    def value_shape(self):
+        assert self._buckets is not None
+        return self._value_shape
+
+    @property
+    def key_type(self):
+        return self._key_store.dtype
+
+    @property
+    def value_type(self):
+        return self._value_dtype
+
+    def __len__(self):
+        return self.n_elements
+
+    # ------------------------------------------------------------------ python-side hashes of the reference
+    def _keys_as_long_bits(self, keys):
+        n_keys = keys.shape[0]
+        keys = keys.reshape(n_keys, -1).clone()
+        if keys.dtype == torch.float:
+            keys = keys.view(dtype=torch.int32).long()
+            keys[keys == -2 ** 31] = 0
+        elif keys.dtype == torch.half:
+            keys = keys.view(dtype=torch.int16).long()
+            keys[keys == -2 ** 15] = 0
+        elif keys.dtype == torch.double:
+            keys = keys.view(dtype=torch.int64)
+            keys[keys == -2 ** 63] = 0
+        else:
+            keys = keys.to(torch.long)
+        return keys
+
+    def get_hash(self, keys):
+        """Python-side first hash of the reference (cuda_closed_hashmap.py:278-300; bit-casts floats, unlike the
+        kernels).  Diagnostic only: this library does not place rows with it."""
+        keys = self._keys_as_long_bits(keys)
+        terms = (self.alpha1[None] * keys + self.beta1[None]) % self.prime1[None]
+        if self._key_perm is not None:
+            terms = terms[:, self._key_perm]
+        return terms.prod(dim=-1).abs() % self.n_buckets
+
+    def get_uuid(self, keys):
+        """Python-side second hash of the reference (cuda_closed_hashmap.py:302-319).  `device_uuid` returns what
+        the kernels use."""
+        keys = self._keys_as_long_bits(keys)
+        return ((self.alpha2[None] * keys + self.beta2[None]) % self.prime2[None]).prod(dim=-1).abs()
+
+    def test_uniformity(self, keys):
+        hash_codes = self.get_hash(keys)
+        logits = (torch.bincount(hash_codes, minlength=self.n_buckets) + 1).log()
+        logp = torch.log_softmax(logits, dim=-1)
+        return (-(logp * logp.exp()).sum(dim=-1)).exp() / self.n_buckets
+
+    def device_uuid(self, keys):
+        """uuid of each key row exactly as the kernels compute it (value cast of the key elements)."""
+        assert self._key_store is not None
+        keys = keys.contiguous()
+        out = torch.empty(keys.shape[0], device=self.device, dtype=torch.long)
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_map_uuid(self._c_table(), self._c_hash(), L.ptr(keys), keys.shape[0], L.ptr(out), None,
+                                         L.stream_ptr(self.device)), "dok_map_uuid")
+        return out
+
+    # ------------------------------------------------------------------ set
+    def _launch_set(self, keys, values, assume_unique):
+        lib = L.lib()
+        n = keys.shape[0]
+        cnt = self._counters()
+        with torch.cuda.device(self.device):
+            st = L.stream_ptr(self.device)
+            if assume_unique:
+                L.check(lib.dok_map_set_unique(self._c_table(), self._c_hash(), L.ptr(keys), L.ptr(values), n, None,
+                                               L.ptr(cnt), st), "dok_map_set_unique")
+            else:
+                epoch = self._ensure_stamp()
+                scratch = torch.empty(n, device=self.device, dtype=torch.long)
+                L.check(lib.dok_map_set(self._c_table(), self._c_hash(), L.ptr(keys), L.ptr(values), n, L.ptr(scratch),
+                                        epoch, None, L.ptr(cnt), st), "dok_map_set")
+        return cnt
+
+    def _count_new(self, keys):
+        """Number of distinct new keys of a batch (cuda_closed_hashmap.py:350-363).  Integer keys: distinct absent
+        uuids, counted on the device with a scratch tag set.  Floating keys: distinct absent ROWS like the
+        reference, because the value cast makes different rows share a uuid."""
+        lib = L.lib()
+        n = keys.shape[0]
+        cnt = self._counters()
+        with torch.cuda.device(self.device):
+            st = L.stream_ptr(self.device)
+            if keys.dtype in L.FLOAT_DTYPES:
+                found = torch.empty(n, device=self.device, dtype=torch.bool)
+                L.check(lib.dok_map_count_exists(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(found),
+                                                 L.ptr(cnt), st), "dok_map_count_exists")
+                return int(keys[~found].unique(dim=0).shape[0])
+            slots = 2 * n
+            scratch = torch.empty(slots, device=self.device, dtype=torch.long)
+            L.check(lib.dok_map_count_new(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(scratch), slots,
+                                          L.ptr(cnt), st), "dok_map_count_new")
+        return int(cnt[L.CNT_CLAIMED_EMPTY].item())
+
+    def set(self, new_keys, new_values, assume_unique=False):
+        """Insert-or-assign a batch.  `assume_unique=True` promises pairwise different keys and runs one kernel
+        instead of two.  Returns None like the reference."""
+        assert new_keys.shape[0] == new_values.shape[0]
+        if self._key_store is None:
+            assert new_keys.device == new_values.device == self.device
+            self._allocate(new_keys.shape[1:], new_keys.dtype, new_values.shape[1:], new_values.dtype)
+        else:
+            assert new_keys.dtype == self._key_store.dtype
+            assert new_keys.device == self._key_store.device == self.device
+            assert new_keys.shape[1:] == self._key_store.shape[1:]
+            assert new_values.dtype == self._value_dtype
+            assert new_values.device == self.device
+            assert new_values.shape[1:] == self._value_shape
+        new_keys = new_keys.contiguous()
+        new_values = new_values.contiguous()
+        n = new_keys.shape[0]
+        if n == 0:
+            return
+        self._materialise_parameters()
+        limit = int(self._rehash_threshold * self.n_buckets)
+        row_counted = new_keys.dtype in L.FLOAT_DTYPES
+        if not row_counted and self._shared["bound"] + n <= limit:
+            # whatever the number of new keys is, the reference would not rehash: insert and count on the device
+            cnt = self._launch_set(new_keys, new_values, assume_unique)
+            self._n_elements += cnt[L.CNT_CLAIMED_EMPTY] + cnt[L.CNT_REUSED_REMOVED]
+            self._shared["bound"] += n
+            return
+        n_new = self._count_new(new_keys)
+        n_elements = self.n_elements
+        if n_elements + n_new > limit:
+            self.rehash(int((n_elements + n_new) * self._rehash_factor))
+        self._launch_set(new_keys, new_values, assume_unique)
+        self._n_elements += n_new
+        self._shared["bound"] = n_elements + n_new
+
+    # ------------------------------------------------------------------ get
+    def get(self, keys, fallback_value=None):
+        if self._key_store is None or self._buckets is None:
+            raise RuntimeError("store something first")
+        if keys.shape[0] == 0:
+            return (torch.empty(0, *self.value_shape, device=self.device, dtype=self._value_dtype),
+                    torch.empty(0, device=self.device, dtype=torch.bool))
+        assert keys.dtype == self._key_store.dtype
+        assert keys.device == self._key_store.device
+        assert keys.shape[1:] == self.key_shape
+        fb = None
+        if fallback_value is not None:
+            if not isinstance(fallback_value, torch.Tensor):
+                fallback_value = torch.tensor(fallback_value, dtype=self._value_dtype)
+            fb_host = torch.broadcast_to(fallback_value.to(dtype=self._value_dtype, device="cpu"), self.value_shape).contiguous()
+            fb = ctypes.c_void_p(fb_host.data_ptr())
+        keys = keys.contiguous()
+        n = keys.shape[0]
+        values = torch.empty(n, *self.value_shape, device=self.device, dtype=self._value_dtype)
+        is_found = torch.empty(n, device=self.device, dtype=torch.bool)
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_map_get(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(values), L.ptr(is_found),
+                                        fb, None, L.stream_ptr(self.device)), "dok_map_get")
+        return values, is_found
+
+    def probe_stats(self, keys):
+        """(mean probe length, hit rate) of a lookup batch."""
+        keys = keys.contiguous()
+        n = keys.shape[0]
+        values = torch.empty(n, *self.value_shape, device=self.device, dtype=self._value_dtype)
+        cnt = self._counters()
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_map_get_probe_stats(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(values), None,
+                                                    L.ptr(cnt), L.stream_ptr(self.device)), "dok_map_get_probe_stats")
+        cnt = cnt.cpu()
+        return cnt[L.CNT_PROBES].item() / max(n, 1), cnt[L.CNT_HITS].item() / max(n, 1)
+
+    # ------------------------------------------------------------------ remove
+    def remove_rows(self, keys):
+        """Kernel only: flags aligned to the rows given (no dedup, no sort).  Equal rows report once."""
+        keys = keys.contiguous()
+        n = keys.shape[0]
+        is_removed = torch.empty(n, device=self.device, dtype=torch.bool)
+        cnt = self._counters()
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_map_remove(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(is_removed), L.ptr(cnt),
+                                           L.stream_ptr(self.device)), "dok_map_remove")
+        self._n_elements -= cnt[L.CNT_HITS]
+        return is_removed
+
+    def remove(self, keys):
+        if self._key_store is None or self._buckets is None:
+            raise RuntimeError("store something first")
+        if keys.shape[0] == 0:
+            return torch.zeros(0, device=keys.device, dtype=torch.bool)
+        assert keys.dtype == self._key_store.dtype
+        assert keys.device == self._key_store.device
+        assert keys.shape[1:] == self.key_shape
+        unique_keys = keys.unique(dim=0)
+        return self.remove_rows(unique_keys)
+
+    # ------------------------------------------------------------------ rehash
+    def rehash(self, n_buckets):
+        keys, values, _ = self.items(uuid=False)
+        keys = keys.reshape((-1,) + tuple(self.key_shape))
+        self.__init__(
+            n_buckets=n_buckets, device=self.device, key_perm=self._key_perm,
+            rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
+        )
+        # live rows have pairwise different keys: one kernel
+        self.set(keys, values, assume_unique=True)
+
+    def __getitem__(self, keys):
+        return self.get(keys)
+
+    def __setitem__(self, keys, values):
+        return self.set(keys, values)
+
+    def __delitem__(self, keys):
+        return self.remove(keys)

@@ -1,0 +1,56 @@
+"""Small host helpers with the reference's names (sparse_dok/util.py:72-137, 289-293)."""
+import torch
+
+
+def next_prime(n):
+    """Smallest prime larger than n (the reference uses sympy.nextprime for its hash parameters,
+    cuda_closed_hashmap.py:76, 88)."""
+    import sympy
+    return int(sympy.nextprime(int(n)))
+
+
+_STR2DTYPE = {
+    "bool": torch.bool, "uint8": torch.uint8, "char": torch.uint8, "int8": torch.int8, "byte": torch.int8,
+    "int16": torch.int16, "short": torch.int16, "int32": torch.int32, "int": torch.int32,
+    "int64": torch.int64, "long": torch.int64, "float16": torch.float16, "half": torch.float16,
+    "bfloat16": torch.bfloat16, "float32": torch.float32, "float": torch.float32,
+    "float64": torch.float64, "double": torch.float64,
+}
+
+
+def str2dtype(s):
+    if isinstance(s, torch.dtype):
+        return s
+    if isinstance(s, str):
+        if s not in _STR2DTYPE:
+            raise ValueError(f"unrecognized type string {s}")
+        return _STR2DTYPE[s]
+    raise RuntimeError
+
+
+_DTYPE2CTYPE = {
+    torch.bool: "bool", torch.uint8: "uint8_t", torch.int8: "int8_t", torch.int16: "int16_t",
+    torch.int32: "int32_t", torch.int64: "int64_t", torch.float16: "half", torch.bfloat16: "bfloat16",
+    torch.float32: "float", torch.float64: "double",
+}
+
+
+def dtype2ctype(dtype):
+    return _DTYPE2CTYPE.get(str2dtype(dtype))
+
+
+def next_power_of_2(n):
+    """n itself if it is a power of two, else the next one; 1 for n == 0 (sparse_dok/util.py:125-137)."""
+    n = int(n)
+    if n and not (n & (n - 1)):
+        return n
+    return 1 << n.bit_length()
+
+
+def shape_to_stride(shape):
+    """Row-major element strides of a contiguous tensor of `shape`."""
+    out, acc = [], 1
+    for s in reversed(tuple(shape)):
+        out.append(acc)
+        acc *= int(s)
+    return tuple(reversed(out))

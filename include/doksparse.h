@@ -1,0 +1,232 @@
+/*
+ * doksparse.h -- C ABI of libdoksparse.so: the batched closed-hashing map of DeMoriarty/DOKSparse
+ * (sparse_dok 0.1.9.2) and the DOK tensor paths built on it, as hand-written CUDA for sm_100a.
+ *
+ * The reference has no FFI of its own: its native boundary is a CuPy RawKernel launch with raw
+ * data_ptr() integers (sparse_dok/components/cuda/closed_hashmap_impl.py:123-143).  Every entry
+ * point below names the reference launcher / kernel it replaces.  All pointers are DEVICE pointers
+ * unless a parameter says "host"; `stream` is a cudaStream_t passed as void*.  Nothing here
+ * allocates device memory, synchronises the stream, or throws: every call returns a dok_status.
+ *
+ * Key identity is the reference's 64-bit "uuid" (second hash), not the key bytes
+ * (closed_hashmap_impl_class.cu:280-312, 368-427, 459-484).  The uuid is reproduced bit for bit;
+ * the start bucket is free (the slot layout is not part of the contract) and is derived from the
+ * uuid with a 64-bit mixer.
+ *
+ * Storage of a table with n_buckets slots (three arrays, owned by the caller):
+ *   buckets : n_buckets rows of bucket_bytes = max(16, round_up(8 + value_bytes, 16)) bytes:
+ *             { int64 tag; value_bytes of value; padding }.  tag = uuid, -1 empty, -3 tombstone
+ *             (the reference's _uuid and _values arrays, interleaved so that a hit is one sector).
+ *   keys    : n_buckets rows of key_size * key_elem_bytes bytes, storage-column order
+ *             (the reference's _keys array; written by set, read only by compaction).
+ *   stamp   : n_buckets int64, zero-initialised, only needed by dok_map_set (may be NULL elsewhere).
+ */
+#ifndef DOKSPARSE_H
+#define DOKSPARSE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DOK_MAX_KEY_SIZE 8      /* key elements per row */
+#define DOK_MAX_VALUE_BYTES 248 /* value bytes per row  */
+#define DOK_MAX_SELECTOR_NDIM 8 /* dims of a broadcast selector shape */
+#define DOK_MAX_SHARDS 64
+
+#define DOK_TAG_EMPTY (-1LL)   /* cuda_closed_hashmap.py:36 */
+#define DOK_TAG_REMOVED (-3LL) /* cuda_closed_hashmap.py:37 */
+
+typedef enum dok_status {
+  DOK_OK = 0,
+  DOK_BAD_ARG = 1,       /* null pointer, size out of range, unsupported width */
+  DOK_CUDA_ERROR = 2,    /* a launch failed; dok_last_cuda_error() has the code */
+  DOK_TOO_LARGE = 3      /* request exceeds a fixed capacity (static scratch) */
+} dok_status;
+
+/* element type codes of key rows */
+typedef enum dok_dtype {
+  DOK_I8 = 0, DOK_U8 = 1, DOK_I16 = 2, DOK_I32 = 3, DOK_I64 = 4,
+  DOK_F16 = 5, DOK_BF16 = 6, DOK_F32 = 7, DOK_F64 = 8
+} dok_dtype;
+
+/* The uuid hash: uuid = | prod_i ( ((int64)key_i * alpha2[c] + beta2[c]) % prime2[c] ) |, c = key_perm[i],
+ * wrapping int64, C remainder, value cast of key_i (closed_hashmap_impl_class.cu:98-107, parameters
+ * indexed through keyPerm as in :54-63).  alpha2/beta2/prime2 are given UNPERMUTED, as the Python
+ * object holds them (cuda_closed_hashmap.py:79-113).  |prime2[c]| must be >= 2. */
+typedef struct dok_hash_params {
+  int32_t key_size;    /* 1..DOK_MAX_KEY_SIZE */
+  int32_t key_dtype;   /* dok_dtype of the caller's key rows */
+  int64_t alpha2[DOK_MAX_KEY_SIZE];
+  int64_t beta2[DOK_MAX_KEY_SIZE];
+  int64_t prime2[DOK_MAX_KEY_SIZE];
+  int32_t key_perm[DOK_MAX_KEY_SIZE]; /* storage column of key element i (set_key_permuted, :144-150) */
+} dok_hash_params;
+
+typedef struct dok_table {
+  void *buckets;
+  void *keys;
+  int64_t *stamp;      /* may be NULL except for dok_map_set / dok_dok_set_dense */
+  int64_t n_buckets;
+  int32_t bucket_bytes;
+  int32_t value_bytes;
+} dok_table;
+
+/* Counters written by the mutating calls (device int64[DOK_N_COUNTERS], ADDED to, not reset). */
+enum {
+  DOK_CNT_CLAIMED_EMPTY = 0, /* slots claimed from the empty state            */
+  DOK_CNT_REUSED_REMOVED = 1,/* tombstones reused                              */
+  DOK_CNT_FAILED = 2,        /* rows not stored: table full                    */
+  DOK_CNT_HITS = 3,          /* rows found (get / exists / remove / overwrite) */
+  DOK_CNT_DUPLICATES = 4,    /* rows of a set batch that lost to a later duplicate */
+  DOK_CNT_PROBES = 5,        /* total slots inspected (only when probe counting is requested) */
+  DOK_N_COUNTERS = 8
+};
+
+/* Selector view for the fused DOK kernels: ndim index tensors broadcast to one shape
+ * (sparse_dok_tensor.py:220-300 produces them; sparse_dok/util.py:295-310 and
+ * tensor_accessor.cu:1-121 are the reference's packing and accessor).  Strides in ELEMENTS, 0 for a
+ * broadcast dim.  Element e of the row-major linearisation of `sizes` addresses
+ * ptr[d][ sum_j idx_j * strides[d][j] ]. */
+typedef struct dok_selectors {
+  int32_t ndim;            /* number of index tensors = key_size of the DOK map */
+  int32_t selector_ndim;   /* dims of the common shape, 0..DOK_MAX_SELECTOR_NDIM */
+  int64_t sizes[DOK_MAX_SELECTOR_NDIM];
+  const int64_t *ptr[DOK_MAX_KEY_SIZE];
+  int64_t strides[DOK_MAX_KEY_SIZE][DOK_MAX_SELECTOR_NDIM];
+} dok_selectors;
+
+int dok_version(void);
+int dok_last_cuda_error(void);          /* cudaError_t of the last failed launch on this thread */
+int dok_bucket_bytes(int value_bytes);  /* max(16, round_up(8 + value_bytes, 16)); -1 if unsupported */
+
+/* Fills tags with DOK_TAG_EMPTY (values untouched) and, if present, zeroes `stamp`.
+ * Replaces `torch.zeros(n_buckets) + empty_marker`, cuda_closed_hashmap.py:40. */
+int dok_map_init(const dok_table *t, void *stream);
+
+/* uuid (and this library's start bucket) of each key row.  uuid_out / bucket_out may be NULL.
+ * Replaces nothing on the reference's hot path; CudaClosedHashmap.get_uuid
+ * (cuda_closed_hashmap.py:302-319) is the closest relative but bit-casts floats, which the kernels do not. */
+int dok_map_uuid(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
+                 int64_t *uuid_out, int64_t *bucket_out, void *stream);
+
+/* Batched lookup.  out_values[n, value_bytes] receives the stored row on a hit and `fallback`
+ * (HOST pointer to value_bytes bytes, NULL = zeros) on a miss; out_found[n] is 0/1.  counters may be NULL.
+ * Replaces ClosedHashmapImplCuda.get + closed_hashmap_get (closed_hashmap_impl.py:50-145,
+ * closed_hashmap_impl.cu:6-85) including the launcher's two pre-fills. */
+int dok_map_get(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
+                void *out_values, uint8_t *out_found, const void *fallback, int64_t *counters, void *stream);
+
+/* dok_map_get that also adds the number of slots inspected to counters[DOK_CNT_PROBES] (mean probe length
+ * = probes / n); fallback is zeros.  No counterpart in the reference. */
+int dok_map_get_probe_stats(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
+                            void *out_values, uint8_t *out_found, int64_t *counters, void *stream);
+
+/* Insert-or-assign, ONE kernel, for batches whose rows have pairwise different uuids (rows with equal
+ * uuid race: one of them wins, rows may tear).  out_stored[n] may be NULL.
+ * Replaces ClosedHashmapImplCuda.set + closed_hashmap_set (closed_hashmap_impl.py:147-213,
+ * closed_hashmap_impl.cu:87-156, ClosedHashmap::set closed_hashmap_impl_class.cu:368-427). */
+int dok_map_set_unique(const dok_table *t, const dok_hash_params *hp, const void *keys, const void *values,
+                       int64_t n, uint8_t *out_stored, int64_t *counters, void *stream);
+
+/* Insert-or-assign for any batch: rows with equal uuid resolve to the LAST row in batch order, exactly one
+ * slot per uuid, rows never torn (what a serial run of the reference kernel produces).  Two kernels:
+ * claim (find or claim the slot, atomicMax of (epoch<<32 | row) on t->stamp) then write (winners only).
+ * slot_scratch: device int64[n], contents irrelevant.  epoch: 1..2^31-1, strictly larger than any epoch used
+ * on this table since `stamp` was last zeroed.  n < 2^32. */
+int dok_map_set(const dok_table *t, const dok_hash_params *hp, const void *keys, const void *values,
+                int64_t n, int64_t *slot_scratch, int64_t epoch, uint8_t *out_stored, int64_t *counters,
+                void *stream);
+
+/* Batched removal: the slot's tag becomes DOK_TAG_REMOVED, key/value bytes stay.  With equal uuids in the
+ * batch exactly one row reports 1.  Replaces ClosedHashmapImplCuda.remove + closed_hashmap_remove
+ * (closed_hashmap_impl.py:215-278, closed_hashmap_impl.cu:158-220). */
+int dok_map_remove(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
+                   uint8_t *out_removed, int64_t *counters, void *stream);
+
+/* counters[DOK_CNT_HITS] += number of rows present; out_flags may be NULL.
+ * Replaces ClosedHashmap::exists as used by sparse_dok_count_items
+ * (closed_hashmap_impl_class.cu:253-278, sparse_dok_tensor_impl.cu:3-56). */
+int dok_map_count_exists(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
+                         uint8_t *out_flags, int64_t *counters, void *stream);
+
+/* Number of DISTINCT uuids of the batch that are absent from the table: what `set` needs before it can
+ * decide on a rehash (replaces the pre-get + `unique(dim=0)` of cuda_closed_hashmap.py:350-363 for keys
+ * whose uuid is injective).  scratch_tags: device int64[scratch_slots], scratch_slots >= 2*n; it is
+ * (re)initialised by the call.  Adds the count to counters[DOK_CNT_CLAIMED_EMPTY]. */
+int dok_map_count_new(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
+                      int64_t *scratch_tags, int64_t scratch_slots, int64_t *counters, void *stream);
+
+/* Live-slot compaction in slot order (replaces nonempty_mask + the boolean-mask gathers of
+ * cuda_closed_hashmap.py:157-172, 233-234).  Step 1 counts per tile and scans:
+ *   tile_offsets: device int64[dok_compact_tiles(n_buckets) + 1]; the last element is the live count.
+ * Step 2 scatters; any of keys_out [count, key_size] (columns permuted by key_perm like keys()),
+ * values_out [count, value_bytes], uuid_out [count] may be NULL.  keys_transposed != 0 writes
+ * keys_out as [key_size, count] (what SparseDOKTensor.indices() returns, sparse_dok_tensor.py:156-162). */
+int64_t dok_compact_tiles(int64_t n_buckets);
+int dok_map_compact_count(const dok_table *t, int64_t *tile_offsets, void *stream);
+int dok_map_compact_scatter(const dok_table *t, const dok_hash_params *hp, const int64_t *tile_offsets,
+                            void *keys_out, int keys_transposed, void *values_out, int64_t *uuid_out,
+                            void *stream);
+
+/* ---- fused DOK tensor paths: keys are formed on the fly from broadcast selector views ---------------- */
+
+/* Dense gather with fill: out[e] = stored value or `fallback` (HOST, NULL = zeros).
+ * Replaces the stack + transpose + get of SparseDOKTensor.__getitem__ (sparse_dok_tensor.py:302-315). */
+int dok_dok_get(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel,
+                void *out_values, uint8_t *out_found, const void *fallback, int64_t *counters, void *stream);
+
+/* Replaces sparse_dok_count_items (sparse_dok_tensor_impl.cu:3-56, launcher sparse_dok_tensor_impl.py:56-108). */
+int dok_dok_count_exists(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel,
+                         int64_t *counters, void *stream);
+
+/* Insert-or-assign of a broadcast dense source, last selector element wins on duplicates, zeros stored.
+ * src_strides in elements of value_bytes.  Replaces sparse_dok_set_items_dense
+ * (sparse_dok_tensor_impl.cu:270-313, launcher sparse_dok_tensor_impl.py:412-474). */
+int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel,
+                      const void *src, const int64_t *src_strides, int64_t *slot_scratch, int64_t epoch,
+                      int64_t *counters, void *stream);
+
+/* Tombstones every selected element that is present; counters[DOK_CNT_HITS] += removed.
+ * Replaces sparse_dok_zero_items (sparse_dok_tensor_impl.cu:58-108). */
+int dok_dok_zero_items(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel,
+                       int64_t *counters, void *stream);
+
+/* from_dense: counts the non-zero elements of a contiguous dense tensor (step 1), then inserts
+ * (unravelled index -> value) for each of them (step 2) without materialising COO indices.
+ * Replaces tensor.to_sparse() + coalesce + set of SparseDOKTensor.from_dense (sparse_dok_tensor.py:71-90).
+ * elem_bytes in {1,2,4,8} (= value_bytes of the table); is_float != 0 makes -0.0 count as zero;
+ * sizes[ndim] is the dense shape, ndim = hp->key_size, keys are int64. */
+int dok_dense_count_nonzero(const void *dense, int64_t numel, int elem_bytes, int is_float, int64_t *count_out,
+                            void *stream);
+int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, const void *dense,
+                             const int64_t *sizes /* host */, int64_t numel, int is_float, int64_t *counters,
+                             void *stream);
+
+/* ---- hash-sharded table: batch routing (no counterpart in the reference, which is single-GPU) ------- */
+
+/* Owner shard of each row: mulhi64(mix(uuid ^ salt), n_shards).  Stable partition of a batch by owner:
+ * step 1 per-tile histogram + scan -> tile_offsets int64[n_shards * dok_partition_tiles(n) + 1] and
+ * shard_counts int64[n_shards]; step 2 scatters key rows (and value rows, if values != NULL) into
+ * keys_out/values_out grouped by owner, order within an owner preserved; dest_index[n] receives each
+ * row's position in the grouped order (used by dok_shard_unpermute). */
+int64_t dok_partition_tiles(int64_t n);
+int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards,
+                              int64_t *tile_offsets, int64_t *shard_counts, void *stream);
+int dok_shard_partition_scatter(const dok_hash_params *hp, const void *keys, const void *values,
+                                int value_bytes, int64_t n, int n_shards, const int64_t *tile_offsets,
+                                void *keys_out, void *values_out, int64_t *dest_index, void *stream);
+
+/* out_values[i] = grouped_values[dest_index[i]], out_found[i] = grouped_found[dest_index[i]] */
+int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found, const int64_t *dest_index,
+                        int value_bytes, int64_t n, void *out_values, uint8_t *out_found, void *stream);
+
+/* owner_out[i] = owner shard of row i (diagnostics; the partition computes the same value internally) */
+int dok_shard_owner(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, int32_t *owner_out,
+                    void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DOKSPARSE_H */

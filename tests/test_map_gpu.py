@@ -1,0 +1,338 @@
+"""Parity of the CUDA hash map (through the C ABI) with the CPU oracle and with the reference-generated
+golden streams.  Integer / byte work: everything is compared bit-exactly."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import port
+from tests.helpers import TORCH_OF, assert_same_bytes, assert_same_items, dev, host
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "map_streams.npz")
+
+
+def new_maps(seed, **kwargs):
+    from doksparse_b200 import CudaClosedHashmap
+    np.random.seed(seed)
+    c = CudaClosedHashmap(**kwargs)
+    o = port.OracleHashmap(**kwargs)
+    return c, o
+
+
+def both(seed_state, fn_cuda, fn_oracle):
+    """Runs the two implementations from the same numpy random state (parameter draws happen lazily)."""
+    np.random.set_state(seed_state)
+    a = fn_cuda()
+    after = np.random.get_state()
+    np.random.set_state(seed_state)
+    b = fn_oracle()
+    np.random.set_state(after)
+    return a, b
+
+
+class Pair:
+    """A CUDA map and an oracle map that consume identical numpy random streams."""
+
+    def __init__(self, seed=0, **kwargs):
+        from doksparse_b200 import CudaClosedHashmap
+        self.c = CudaClosedHashmap(**kwargs)
+        self.o = port.OracleHashmap(**kwargs)
+        np.random.seed(seed)
+        self.state = np.random.get_state()
+
+    def run(self, fn_cuda, fn_oracle):
+        a, b = both(self.state, fn_cuda, fn_oracle)
+        self.state = np.random.get_state()
+        return a, b
+
+    def set(self, keys, values, **kw):
+        self.run(lambda: self.c.set(dev(keys), dev(values), **kw), lambda: self.o.set(keys, values))
+        self.check_sizes()
+
+    def get(self, keys, fallback=None):
+        (cv, cf), (ov, of) = self.run(lambda: self.c.get(dev(keys), fallback), lambda: self.o.get(keys, fallback))
+        np.testing.assert_array_equal(host(cf), of)
+        assert_same_bytes(host(cv), ov)
+        return ov, of
+
+    def remove(self, keys):
+        cr, orr = self.run(lambda: self.c.remove(dev(keys)), lambda: self.o.remove(keys))
+        np.testing.assert_array_equal(host(cr), orr)
+        self.check_sizes()
+        return orr
+
+    def check_sizes(self):
+        assert self.c.n_elements == self.o.n_elements
+        assert self.c.n_buckets == self.o.n_buckets
+
+    def check_items(self):
+        assert_same_items(self.c, self.o)
+        assert self.c.n_tombstones <= self.c.n_buckets
+
+
+def rand_keys(rng, n, dtype, ks, lo, hi):
+    if np.issubdtype(dtype, np.floating):
+        return rng.uniform(lo, hi, size=(n, ks)).astype(dtype)
+    return rng.integers(lo, hi, size=(n, ks)).astype(dtype)
+
+
+def rand_values(rng, n, dtype, vs):
+    if np.issubdtype(dtype, np.floating):
+        return rng.standard_normal((n, vs)).astype(dtype)
+    return rng.integers(-2 ** 31, 2 ** 31, size=(n, vs)).astype(dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+
+def test_golden_streams_from_the_reference():
+    """Replays the streams recorded from the reference's own kernels (tests/golden) on the GPU."""
+    from doksparse_b200 import CudaClosedHashmap
+    data = np.load(GOLDEN)
+    names = sorted({k.split("/")[0] for k in data.files})
+    assert len(names) == 7
+    for name in names:
+        nb, ks, vs = (int(x) for x in data[f"{name}/meta"])
+        params = {k: torch.from_numpy(data[f"{name}/param/{k}"]).cuda()
+                  for k in ("prime1", "prime2", "alpha1", "alpha2", "beta1", "beta2")}
+        c = CudaClosedHashmap(n_buckets=nb, key_perm=data[f"{name}/param/key_perm"].tolist(),
+                              rehash_threshold=10.0, **params)     # the recorded streams never rehash
+        for step in range(5):
+            g = lambda key: data[f"{name}/step{step}/{key}"]
+            c.set(dev(g("set_keys")), dev(g("set_values")), assume_unique=bool(step % 2))
+            cv, cf = c.get(dev(g("get_keys")), 7)
+            np.testing.assert_array_equal(host(cf), g("get_found"))
+            assert_same_bytes(host(cv), g("get_values"))
+            np.testing.assert_array_equal(host(c.remove_rows(dev(g("remove_keys")))), g("remove_flags"))
+            k, v, u = c.items()
+            ck, cv_, cu = port.sort_items(host(k), host(v), host(u))
+            np.testing.assert_array_equal(cu, g("items_uuid"))
+            np.testing.assert_array_equal(ck, g("items_keys").reshape(ck.shape))
+            assert_same_bytes(cv_, g("items_values").reshape(cv_.shape))
+            assert c.n_elements == len(cu)
+
+
+UUID_CASES = [
+    (np.int64, 1, -2 ** 62, 2 ** 62), (np.int64, 2, -10 ** 9, 10 ** 9), (np.int64, 4, 0, 5000), (np.int64, 8, -100, 100),
+    (np.int32, 3, -2 ** 31, 2 ** 31 - 1), (np.int16, 2, -2 ** 15, 2 ** 15 - 1), (np.int8, 2, -128, 127),
+    (np.uint8, 3, 0, 255), (np.float32, 3, -1e6, 1e6), (np.float32, 1, 0, 1), (np.float64, 2, -1e12, 1e12),
+    (np.float16, 2, -1000, 1000),
+]
+
+
+@pytest.mark.parametrize("kd,ks,lo,hi", UUID_CASES)
+def test_uuid_is_bit_identical(kd, ks, lo, hi):
+    """The device uuid equals the oracle's restatement of get_uuid (closed_hashmap_impl_class.cu:98-107),
+    parameter permutation included."""
+    rng = np.random.default_rng(ks * 31 + 1)
+    perm = list(rng.permutation(ks))
+    p = Pair(seed=ks, n_buckets=4096, key_perm=perm)
+    keys = rand_keys(rng, 5000, kd, ks, lo, hi)
+    vals = np.zeros((5000, 1), dtype=np.float32)
+    p.set(keys, vals)
+    np.testing.assert_array_equal(host(p.c.device_uuid(dev(keys))), p.o.hash_uuid(keys)[1])
+
+
+COMBOS = [
+    (np.int64, 1, np.float32, 1, -2 ** 62, 2 ** 62), (np.int64, 1, np.float32, 2, 0, 10 ** 6),
+    (np.int64, 1, np.float32, 4, 0, 3000), (np.int64, 1, np.int64, 1, 0, 3000),
+    (np.int64, 2, np.float32, 1, 0, 60), (np.int64, 3, np.float32, 1, 0, 20), (np.int64, 4, np.float32, 1, 0, 9),
+    (np.int64, 2, np.float64, 1, 0, 60), (np.int32, 2, np.float32, 3, -50, 50), (np.int16, 3, np.int32, 2, -9, 9),
+    (np.float32, 3, np.int64, 5, -20, 20), (np.float64, 2, np.float32, 1, -50, 50),
+    (np.int64, 1, np.uint8, 3, 0, 3000), (np.int64, 2, np.float16, 5, 0, 60), (np.int64, 1, np.float64, 31, 0, 3000),
+]
+
+
+@pytest.mark.parametrize("kd,ks,vd,vs,lo,hi", COMBOS)
+def test_operation_stream_matches_oracle(kd, ks, vd, vs, lo, hi):
+    """set / get / remove with automatic rehashing, duplicates inside batches (last row wins), tombstone reuse:
+    flags, values, remove flags, n_elements, n_buckets and the live items all equal the serial oracle."""
+    rng = np.random.default_rng(7 + ks + vs)
+    p = Pair(seed=11 + vs, n_buckets=64)
+    for step in range(8):
+        n = 40 + 30 * step
+        keys, vals = rand_keys(rng, n, kd, ks, lo, hi), rand_values(rng, n, vd, vs)
+        if step % 3 == 2:                                # force duplicates inside the batch
+            keys[n // 2:] = keys[: n - n // 2]
+        p.set(keys, vals)
+        q = np.concatenate([keys[::2], rand_keys(rng, n, kd, ks, lo, hi)])
+        p.get(q, fallback=None if step % 2 else 3)
+        p.remove(q[rng.permutation(len(q))[: len(q) // 3]])
+        p.check_items()
+    assert p.c.n_buckets > 64          # the stream grew the table at least once
+
+
+def test_tiny_tables_wraparound_and_full():
+    """8..64 bucket tables driven to 100 % load: probe wrap-around, a full table refuses silently
+    (closed_hashmap_impl_class.cu:426), tombstones are reused."""
+    for nb in (8, 13, 64):
+        rng = np.random.default_rng(nb)
+        p = Pair(seed=nb, n_buckets=nb, rehash_threshold=100.0)
+        keys = rng.permutation(10 * nb)[: 2 * nb].astype(np.int64)[:, None]
+        vals = rng.standard_normal((2 * nb, 2)).astype(np.float32)
+        first, second = keys[:nb], keys[nb:]
+        p.set(first, vals[:nb])
+        p.check_items()
+        assert host(p.c._uuid != -1).all()                     # 100 % load
+        ov, of = p.get(keys)
+        assert of[:nb].all() and not of[nb:].any()
+        # a full table: further distinct keys are not stored (the reference drops them without an error)
+        p.c.set(dev(second), dev(vals[nb:]), assume_unique=True)
+        cv, cf = p.c.get(dev(second))
+        assert not host(cf).any()
+        p.c._n_elements.fill_(nb); p.c._shared["bound"] = nb    # bookkeeping of the refused rows is not compared
+        removed = p.remove(first[::2])
+        assert removed.all()
+        assert p.c.n_tombstones == len(first[::2])
+        p.set(second[: nb // 4], vals[nb: nb + nb // 4])        # lands in tombstones
+        p.check_items()
+        assert p.c.n_tombstones == p.o.n_tombstones
+
+
+def test_config1_shape_float_keys_collapse():
+    """BASELINE config 1 as written: float32[3] keys in [0,1) -> int64[5] values, 2^21 buckets.  The value cast of
+    the device hash sends every key to the same uuid, so one slot is live, every lookup hits and returns the last
+    stored row, and n_elements counts distinct ROWS like the reference."""
+    n = 200_000
+    rng = np.random.default_rng(0)
+    keys = rng.random((n, 3), dtype=np.float32)
+    vals = rng.integers(0, 2 ** 63 - 1, size=(n, 5), dtype=np.int64)
+    p = Pair(seed=0, n_buckets=2 ** 21)
+    p.set(keys, vals)
+    assert p.c.n_elements == n and int(host(p.c.nonempty_mask).sum()) == 1
+    q = np.concatenate([keys[: n // 2], rng.random((n // 2, 3), dtype=np.float32)])
+    ov, of = p.get(q)
+    assert of.all() and (ov == vals[-1]).all()
+    p.remove(keys[rng.permutation(n)[: n // 4]])
+    p.get(q)
+    p.check_items()
+
+
+def test_config1_injective_float_keys():
+    """Config 1 with keys floor(U(0, 2^24)) stored as float32 (the value cast is then injective): a million-row
+    set, a half-present get, removal of a quarter and a re-get, all against the oracle."""
+    n = 1_000_000
+    rng = np.random.default_rng(1)
+    keys = np.floor(rng.uniform(0, 2 ** 24, size=(n, 3))).astype(np.float32)
+    vals = rng.integers(0, 2 ** 63 - 1, size=(n, 5), dtype=np.int64)
+    p = Pair(seed=1, n_buckets=2 ** 21)
+    p.set(keys, vals)
+    fresh = np.floor(rng.uniform(0, 2 ** 24, size=(n // 2, 3))).astype(np.float32)
+    q = np.concatenate([keys[: n // 2], fresh])
+    p.get(q)
+    p.remove(keys[rng.permutation(n)[: n // 4]])
+    ov, of = p.get(q)
+    assert 0.3 < of.mean() < 0.45
+    p.check_items()
+
+
+def test_duplicates_last_row_wins_across_blocks():
+    """100k rows over 1000 distinct keys: thousands of CUDA blocks race for the same slots; the result must be the
+    serial one (last row of the batch per key) and no row may be torn."""
+    rng = np.random.default_rng(3)
+    n = 100_000
+    keys = rng.integers(0, 1000, size=(n, 2)).astype(np.int64)
+    keys[:, 1] = keys[:, 0] * 7
+    vals = np.repeat(np.arange(n, dtype=np.float32)[:, None], 6, axis=1)     # a torn row would mix two indices
+    p = Pair(seed=3, n_buckets=4096)
+    p.set(keys, vals)
+    uniq = np.unique(keys, axis=0)
+    ov, of = p.get(uniq)
+    assert of.all() and (ov == ov[:, :1]).all()
+    p.check_items()
+    p.set(keys[::-1].copy(), vals)          # all keys now present: overwrite path, again last row wins
+    p.get(uniq)
+    p.check_items()
+
+
+def test_key_perm_views_share_storage():
+    """A shallow clone with another key_perm sees the same slots with permuted key columns
+    (cuda_closed_hashmap.py:213-231, closed_hashmap_impl_class.cu:54-63, 144-150)."""
+    rng = np.random.default_rng(4)
+    p = Pair(seed=4, n_buckets=1024)
+    keys = rng.integers(0, 50, size=(300, 3)).astype(np.int64)
+    vals = rng.standard_normal((300, 1)).astype(np.float32)
+    p.set(keys, vals)
+    view = p.c.clone(False)
+    view.key_perm = [2, 0, 1]
+    perm = np.array([2, 0, 1])
+    # column i of the view's key is storage column perm[i]: a key (a,b,c) of the original is (c,a,b) in the view
+    v1, f1 = p.c.get(dev(keys))
+    v2, f2 = view.get(dev(keys[:, perm]))
+    assert host(f1).all() and host(f2).all()
+    assert_same_bytes(host(v1), host(v2))
+    np.testing.assert_array_equal(host(view.keys()), host(p.c.keys())[:, perm])
+    newk = rng.integers(100, 150, size=(50, 3)).astype(np.int64)
+    newv = rng.standard_normal((50, 1)).astype(np.float32)
+    view.set(dev(newk[:, perm]), dev(newv))
+    v3, f3 = p.c.get(dev(newk))
+    assert host(f3).all()
+    assert_same_bytes(host(v3), newv)
+    assert p.c.n_elements == view.n_elements
+
+
+def test_api_surface_and_errors():
+    from doksparse_b200 import CudaClosedHashmap
+    m = CudaClosedHashmap()
+    assert m.n_buckets == 1024 and m._empty_marker == -1 and m._removed_marker == -3
+    assert m.keys() is None and m.values() is None and m._keys is None and m._values is None
+    assert (host(m._uuid) == -1).all() and len(m) == 0
+    keys = torch.arange(10, device="cuda")[:, None]
+    with pytest.raises(RuntimeError, match="store something first"):
+        m.get(keys)
+    with pytest.raises(RuntimeError, match="store something first"):
+        m.remove(keys)
+    assert m.set(keys, torch.ones(10, 2, device="cuda")) is None
+    m[keys + 10] = torch.zeros(10, 2, device="cuda")
+    values, found = m[torch.arange(30, device="cuda")[:, None]]
+    assert values.shape == (30, 2) and found.dtype == torch.bool and found.sum().item() == 20
+    assert m.key_shape == (1,) and m.value_shape == (2,) and m.key_type == torch.long and m.value_type == torch.float32
+    assert m._keys.shape == (1024, 1) and m._values.shape == (1024, 2) and m._uuid.shape == (1024,)
+    e_v, e_f = m.get(keys[:0])
+    assert e_v.shape == (0, 2) and e_f.shape == (0,)
+    assert m.remove(keys[:0]).shape == (0,)
+    m.set(keys[:0], torch.ones(0, 2, device="cuda"))
+    with pytest.raises(AssertionError):
+        m.get(keys.int())
+    with pytest.raises(AssertionError):
+        m.set(keys, torch.ones(10, 3, device="cuda"))
+    del m[keys]
+    assert m.n_elements == 10 and abs(m.load_factor - 10 / 1024) < 1e-12
+    # in-place edits through the public storage views reach the table
+    m._values.mul_(0).add_(5)
+    assert (host(m.values()) == 5).all()
+    d = m.clone(deepclone=True)
+    d.remove(keys + 10)
+    assert d.n_elements == 0 and m.n_elements == 10
+    m.rehash(5000)
+    assert m.n_buckets == 5000 and m.n_elements == 10 and m.n_tombstones == 0
+    assert (host(m.get(keys + 10)[0]) == 5).all()
+
+
+def test_large_roundtrip_properties():
+    """Size-independent properties at 2^24 rows (no oracle): every stored key is found with its value, absent keys
+    are not, removed keys disappear, counters are exact."""
+    from doksparse_b200 import CudaClosedHashmap
+    n = 1 << 24
+    g = torch.Generator(device="cuda").manual_seed(0)
+    keys = torch.randperm(1 << 26, device="cuda", generator=g)[:n][:, None] * 64 + 5
+    vals = torch.stack([keys[:, 0].float(), (keys[:, 0] % 977).float()], dim=1)
+    np.random.seed(0)
+    m = CudaClosedHashmap(n_buckets=1 << 25)
+    m.set(keys, vals)
+    assert m.n_elements == n and m.n_buckets == 1 << 25
+    v, f = m.get(keys)
+    assert bool(f.all()) and torch.equal(v, vals)
+    v, f = m.get(keys + 1, fallback_value=-2.0)
+    assert not bool(f.any()) and bool((v == -2).all())
+    flags = m.remove_rows(keys[: n // 2])
+    assert bool(flags.all()) and m.n_elements == n - n // 2
+    v, f = m.get(keys)
+    assert int(f.sum().item()) == n - n // 2 and not bool(f[: n // 2].any())
+    m.set(keys[: n // 4], vals[: n // 4], assume_unique=True)
+    assert m.n_elements == n - n // 2 + n // 4
+    k2, v2, u2 = m.items()
+    assert k2.shape[0] == m.n_elements
+    assert torch.equal(torch.sort(k2[:, 0]).values, torch.sort(torch.cat([keys[: n // 4, 0], keys[n // 2:, 0]])).values)
