@@ -29,7 +29,9 @@ class HashParams(ctypes.Structure):
     _fields_ = [
         ("key_size", ctypes.c_int32), ("key_dtype", ctypes.c_int32),
         ("alpha2", ctypes.c_int64 * MAX_KEY_SIZE), ("beta2", ctypes.c_int64 * MAX_KEY_SIZE),
-        ("prime2", ctypes.c_int64 * MAX_KEY_SIZE), ("key_perm", ctypes.c_int32 * MAX_KEY_SIZE),
+        ("prime2", ctypes.c_int64 * MAX_KEY_SIZE),
+        ("alpha1", ctypes.c_int64 * MAX_KEY_SIZE), ("beta1", ctypes.c_int64 * MAX_KEY_SIZE),
+        ("prime1", ctypes.c_int64 * MAX_KEY_SIZE), ("key_perm", ctypes.c_int32 * MAX_KEY_SIZE),
     ]
 
 

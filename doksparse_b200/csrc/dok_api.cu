@@ -80,11 +80,14 @@ __global__ void __launch_bounds__(DOK_TPB) k_dense_insert(DevTable t, DevHash hp
           }
         }
         ll_t u = dok_uuid_term(idx[0], hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+        ll_t h = dok_uuid_term(idx[0], hp.a1[0], hp.b1[0], hp.p1[0], hp.m1[0]);
 #pragma unroll
         for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
-          if (d < shape.ndim) u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
-        const ll_t uuid = dok_llabs(u);
-        const ll_t slot = dok_find_or_claim(t, uuid, &outcome);
+          if (d < shape.ndim) {
+            u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
+            h = (ll_t)((ull_t)h * (ull_t)dok_uuid_term(idx[d], hp.a1[d], hp.b1[d], hp.p1[d], hp.m1[d]));
+          }
+        const ll_t slot = dok_find_or_claim(t, KeyHash{dok_llabs(u), dok_llabs(h)}, &outcome);
         if (slot >= 0) {
           ll_t *krow = (ll_t *)(t.keys + slot * (ll_t)t.kb);
 #pragma unroll

@@ -29,18 +29,25 @@ struct DevHash {
   int dtype;                    // dok_dtype of the key rows
   int elem_bytes;               // bytes of one key element
   int pad_;
-  ll_t a[DOK_MAX_KEY_SIZE];     // alpha2[key_perm[i]]
+  ll_t a[DOK_MAX_KEY_SIZE];     // alpha2[key_perm[i]]   -- second hash: the uuid (key identity)
   ll_t b[DOK_MAX_KEY_SIZE];     // beta2[key_perm[i]]
   ull_t p[DOK_MAX_KEY_SIZE];    // |prime2[key_perm[i]]|  (>= 2)
   ull_t m[DOK_MAX_KEY_SIZE];    // floor(2^64 / p)
+  ll_t a1[DOK_MAX_KEY_SIZE];    // alpha1[key_perm[i]]   -- first hash: only decorrelates the probe chains of
+  ll_t b1[DOK_MAX_KEY_SIZE];    // beta1[key_perm[i]]       keys whose uuids collide (see dok_start_bucket)
+  ull_t p1[DOK_MAX_KEY_SIZE];   // |prime1[key_perm[i]]|
+  ull_t m1[DOK_MAX_KEY_SIZE];   // floor(2^64 / p1)
   int perm[DOK_MAX_KEY_SIZE];   // storage column of key element i
 };
+
+struct KeyHash { ll_t uuid; ll_t hash1; };
 
 struct DevTable {
   char *buckets;    // n_buckets * bb bytes: {int64 tag; value; pad}
   char *keys;       // n_buckets * kb bytes
   ll_t *stamp;      // n_buckets or nullptr
   ll_t nb;
+  ull_t nb_magic;   // floor(2^64 / nb)
   int bb;           // bucket bytes (multiple of 16)
   int vb;           // value bytes
   int kb;           // key row bytes
@@ -80,16 +87,24 @@ __device__ __forceinline__ ll_t dok_key_elem(const void *keys, int dtype, ll_t i
   }
 }
 
-// Mixer (the 64-bit finaliser of MurmurHash3) and multiply-high range reduction: the start bucket of this
-// library.  Any table size works without a modulo.
+// Mixer (the 64-bit finaliser of MurmurHash3); with a multiply-high range reduction any table size works
+// without a modulo.
 __device__ __forceinline__ ull_t dok_mix64(ull_t h) {
   h ^= h >> 33; h *= 0xff51afd7ed558ccdULL;
   h ^= h >> 33; h *= 0xc4ceb9fe1a85ec53ULL;
   h ^= h >> 33;
   return h;
 }
-__device__ __forceinline__ ll_t dok_start_bucket(ll_t uuid, ll_t nb) {
-  return (ll_t)__umul64hi(dok_mix64((ull_t)uuid), (ull_t)nb);
+// Start bucket.  In the reference two keys whose uuids collide are still told apart as long as their probe
+// chains (first hash modulo n_buckets) do not meet; a uuid collision is not rare there, because alpha2 may be
+// drawn as 0 (cuda_closed_hashmap.py:100), which makes one key element drop out of the uuid.  To keep that
+// property the start bucket mixes the uuid with the reference's first hash reduced modulo n_buckets: keys
+// that collide in BOTH collide here too, keys that collide in the uuid only get unrelated chains.
+__device__ __forceinline__ ll_t dok_start_bucket(const KeyHash &h, ll_t nb, ull_t nb_magic) {
+  const ull_t h1 = (ull_t)h.hash1;
+  ull_t r = h1 - __umul64hi(h1, nb_magic) * (ull_t)nb;       // h1 % nb
+  if (r >= (ull_t)nb) r -= (ull_t)nb;
+  return (ll_t)__umul64hi(dok_mix64((ull_t)h.uuid ^ ((r + 1) * 0x9e3779b97f4a7c15ULL)), (ull_t)nb);
 }
 #define DOK_SHARD_SALT 0x9e3779b97f4a7c15ULL
 __device__ __forceinline__ int dok_owner_shard(ll_t uuid, int n_shards) {
@@ -105,11 +120,17 @@ struct RowKeys {          // contiguous [n, ks] rows of the key dtype (closed_ha
   const void *keys;
   ll_t n;
   __device__ __forceinline__ ll_t count() const { return n; }
-  __device__ __forceinline__ ll_t uuid(const DevHash &hp, ll_t e) const {
-    ll_t u = dok_uuid_term(dok_key_elem(keys, hp.dtype, e * hp.ks), hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
-    for (int i = 1; i < hp.ks; i++)
-      u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(dok_key_elem(keys, hp.dtype, e * hp.ks + i), hp.a[i], hp.b[i], hp.p[i], hp.m[i]));
-    return dok_llabs(u);
+  // get_uuid and get_hash of the reference (closed_hashmap_impl_class.cu:87-107) in one pass over the key
+  __device__ __forceinline__ KeyHash hash(const DevHash &hp, ll_t e) const {
+    ll_t k = dok_key_elem(keys, hp.dtype, e * hp.ks);
+    ll_t u = dok_uuid_term(k, hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+    ll_t h = dok_uuid_term(k, hp.a1[0], hp.b1[0], hp.p1[0], hp.m1[0]);
+    for (int i = 1; i < hp.ks; i++) {
+      k = dok_key_elem(keys, hp.dtype, e * hp.ks + i);
+      u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(k, hp.a[i], hp.b[i], hp.p[i], hp.m[i]));
+      h = (ll_t)((ull_t)h * (ull_t)dok_uuid_term(k, hp.a1[i], hp.b1[i], hp.p1[i], hp.m1[i]));
+    }
+    return KeyHash{dok_llabs(u), dok_llabs(h)};
   }
   // set_key_permuted (closed_hashmap_impl_class.cu:144-150): storage column perm[i] <- key element i
   __device__ __forceinline__ void store_key(const DevHash &hp, ll_t e, char *dst_row) const {
@@ -157,15 +178,20 @@ struct SelKeys {
       }
     }
   }
-  __device__ __forceinline__ ll_t uuid(const DevHash &hp, ll_t e) const {
+  __device__ __forceinline__ KeyHash hash(const DevHash &hp, ll_t e) const {
     ll_t off[DOK_MAX_KEY_SIZE];
     offsets(e, off);
-    ll_t u = dok_uuid_term(s.ptr[0][off[0]], hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+    ll_t k = s.ptr[0][off[0]];
+    ll_t u = dok_uuid_term(k, hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+    ll_t h = dok_uuid_term(k, hp.a1[0], hp.b1[0], hp.p1[0], hp.m1[0]);
 #pragma unroll
     for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
-      if (d < s.ndim)
-        u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(s.ptr[d][off[d]], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
-    return dok_llabs(u);
+      if (d < s.ndim) {
+        k = s.ptr[d][off[d]];
+        u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(k, hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
+        h = (ll_t)((ull_t)h * (ull_t)dok_uuid_term(k, hp.a1[d], hp.b1[d], hp.p1[d], hp.m1[d]));
+      }
+    return KeyHash{dok_llabs(u), dok_llabs(h)};
   }
   __device__ __forceinline__ void store_key(const DevHash &hp, ll_t e, char *dst_row) const {
     ll_t off[DOK_MAX_KEY_SIZE];
@@ -191,8 +217,9 @@ __device__ __forceinline__ ll_t dok_cas_tag(const DevTable &t, ll_t slot, ll_t e
 
 // Lookup: returns the slot holding `uuid`, or -1 (ClosedHashmap::get / exists,
 // closed_hashmap_impl_class.cu:253-312).  The loop is bounded by n_buckets like the reference's.
-__device__ __forceinline__ ll_t dok_find(const DevTable &t, ll_t uuid, int *probes) {
-  ll_t slot = dok_start_bucket(uuid, t.nb);
+__device__ __forceinline__ ll_t dok_find(const DevTable &t, const KeyHash &kh, int *probes) {
+  const ll_t uuid = kh.uuid;
+  ll_t slot = dok_start_bucket(kh, t.nb, t.nb_magic);
   for (ll_t i = 0; i < t.nb; i++) {
     const ll_t tag = dok_load_tag(t, slot);
     if (tag == uuid) { if (probes) *probes = (int)i + 1; return slot; }
@@ -210,8 +237,9 @@ enum { DOK_OUT_FOUND = 0, DOK_OUT_CLAIMED_EMPTY = 1, DOK_OUT_REUSED = 2, DOK_OUT
 // tag the slot is claimed by CAS unless a tombstone was seen.  Phase 2 starts at the remembered tombstone and
 // tries tombstone->uuid, then empty->uuid, slot by slot.  Unlike the reference, a CAS that loses to the SAME
 // uuid joins that slot instead of walking on, so that equal uuids of one batch always meet in one slot.
-__device__ __forceinline__ ll_t dok_find_or_claim(const DevTable &t, ll_t uuid, int *outcome) {
-  ll_t slot = dok_start_bucket(uuid, t.nb);
+__device__ __forceinline__ ll_t dok_find_or_claim(const DevTable &t, const KeyHash &kh, int *outcome) {
+  const ll_t uuid = kh.uuid;
+  ll_t slot = dok_start_bucket(kh, t.nb, t.nb_magic);
   ll_t first_removed = -1;
   for (ll_t i = 0; i < t.nb; i++) {
     ll_t tag = dok_load_tag(t, slot);

@@ -36,7 +36,7 @@ inline int dok_dtype_bytes(int dtype) {
   }
 }
 
-// Permutes the uuid parameters by key_perm (what the reference's kernel-side constructor does,
+// Permutes the hash parameters by key_perm (what the reference's kernel-side constructor does,
 // closed_hashmap_impl_class.cu:54-63) and precomputes floor(2^64 / p) per prime.
 inline bool dok_make_hash(const dok_hash_params *hp, DevHash *out) {
   if (!hp || hp->key_size < 1 || hp->key_size > DOK_MAX_KEY_SIZE) return false;
@@ -54,10 +54,17 @@ inline bool dok_make_hash(const dok_hash_params *hp, DevHash *out) {
     const long long prime = hp->prime2[c];
     const unsigned long long p = prime < 0 ? (0ULL - (unsigned long long)prime) : (unsigned long long)prime;
     if (p < 2) return false;
+    const long long prime1 = hp->prime1[c];
+    const unsigned long long p1 = prime1 < 0 ? (0ULL - (unsigned long long)prime1) : (unsigned long long)prime1;
+    if (p1 < 2) return false;
     out->a[i] = hp->alpha2[c];
     out->b[i] = hp->beta2[c];
     out->p[i] = p;
     out->m[i] = (unsigned long long)((((unsigned __int128)1) << 64) / p);
+    out->a1[i] = hp->alpha1[c];
+    out->b1[i] = hp->beta1[c];
+    out->p1[i] = p1;
+    out->m1[i] = (unsigned long long)((((unsigned __int128)1) << 64) / p1);
     out->perm[i] = c;
   }
   return true;
@@ -72,6 +79,7 @@ inline bool dok_make_table(const dok_table *t, const DevHash *dh, DevTable *out)
   out->keys = (char *)t->keys;
   out->stamp = (ll_t *)t->stamp;
   out->nb = t->n_buckets;
+  out->nb_magic = t->n_buckets > 1 ? (unsigned long long)((((unsigned __int128)1) << 64) / (unsigned long long)t->n_buckets) : 0ULL;
   out->bb = bb;
   out->vb = t->value_bytes;
   out->kb = dh ? dh->ks * dh->elem_bytes : 0;

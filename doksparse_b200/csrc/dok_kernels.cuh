@@ -44,12 +44,13 @@ __global__ void __launch_bounds__(DOK_TPB) k_get(DevTable t, DevHash hp, Keys ke
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   int hit = 0, probes = 0;
   if (e < keys.count()) {
-    const ll_t uuid = keys.uuid(hp, e);
+    const KeyHash kh = keys.hash(hp, e);
+    const ll_t uuid = kh.uuid;
     char *dst = out_values + e * (ll_t)t.vb;
     if (UNITS == 1 || UNITS == 2) {
       constexpr int NW = UNITS == 1 ? 1 : 3;
       ull_t w[NW];
-      ll_t slot = dok_start_bucket(uuid, t.nb);
+      ll_t slot = dok_start_bucket(kh, t.nb, t.nb_magic);
       for (ll_t i = 0; i < t.nb; i++) {
         const char *row = t.buckets + slot * (ll_t)(UNITS * 16);
         const ulonglong2 u0 = dok_ld16(row);
@@ -69,7 +70,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_get(DevTable t, DevHash hp, Keys ke
       if (hit) dok_store_out<NW>(dst, w, t.vb);
       else dok_store_fallback(t, fb, dst);
     } else {
-      const ll_t slot = dok_find(t, uuid, &probes);
+      const ll_t slot = dok_find(t, kh, &probes);
       hit = slot >= 0;
       if (hit) dok_load_value(t, slot, dst);
       else dok_store_fallback(t, fb, dst);
@@ -110,8 +111,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_unique(DevTable t, DevHash hp, 
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   int outcome = -1;
   if (e < keys.count()) {
-    const ll_t uuid = keys.uuid(hp, e);
-    const ll_t slot = dok_find_or_claim(t, uuid, &outcome);
+    const ll_t slot = dok_find_or_claim(t, keys.hash(hp, e), &outcome);
     if (slot >= 0) {
       keys.store_key(hp, e, t.keys + slot * (ll_t)t.kb);
       dok_store_value(t, slot, values.row(t, e));
@@ -135,8 +135,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_claim(DevTable t, DevHash hp, K
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   int outcome = -1, dup = 0;
   if (e < keys.count()) {
-    const ll_t uuid = keys.uuid(hp, e);
-    const ll_t slot = dok_find_or_claim(t, uuid, &outcome);
+    const ll_t slot = dok_find_or_claim(t, keys.hash(hp, e), &outcome);
     slot_out[e] = slot;
     if (slot >= 0) {
       const ll_t mine = (epoch << 32) | e;
@@ -181,10 +180,10 @@ __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys k
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   int hit = 0;
   if (e < keys.count()) {
-    const ll_t uuid = keys.uuid(hp, e);
-    const ll_t slot = dok_find(t, uuid, nullptr);
+    const KeyHash kh = keys.hash(hp, e);
+    const ll_t slot = dok_find(t, kh, nullptr);
     hit = slot >= 0;
-    if (REMOVE && hit) hit = dok_cas_tag(t, slot, uuid, DOK_REMOVED) == uuid;
+    if (REMOVE && hit) hit = dok_cas_tag(t, slot, kh.uuid, DOK_REMOVED) == kh.uuid;
     if (out_flags) out_flags[e] = (uint8_t)hit;
   }
   dok_warp_add(counters ? counters + DOK_CNT_HITS : nullptr, hit);
@@ -202,8 +201,9 @@ __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, K
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   int claimed = 0;
   if (e < keys.count()) {
-    const ll_t uuid = keys.uuid(hp, e);
-    if (dok_find(t, uuid, nullptr) < 0) {
+    const KeyHash kh = keys.hash(hp, e);
+    const ll_t uuid = kh.uuid;
+    if (dok_find(t, kh, nullptr) < 0) {
       ll_t slot = (ll_t)__umul64hi(dok_mix64((ull_t)uuid ^ 0x5851f42d4c957f2dULL), (ull_t)scratch_slots);
       for (ll_t i = 0; i < scratch_slots; i++) {
         ll_t tag = __ldcg(&scratch[slot]);
@@ -235,9 +235,9 @@ template <class Keys>
 __global__ void k_uuid(DevTable t, DevHash hp, Keys keys, ll_t *uuid_out, ll_t *bucket_out) {
   const ll_t e = (ll_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= keys.count()) return;
-  const ll_t uuid = keys.uuid(hp, e);
-  if (uuid_out) uuid_out[e] = uuid;
-  if (bucket_out) bucket_out[e] = t.nb > 0 ? dok_start_bucket(uuid, t.nb) : 0;
+  const KeyHash kh = keys.hash(hp, e);
+  if (uuid_out) uuid_out[e] = kh.uuid;
+  if (bucket_out) bucket_out[e] = t.nb > 0 ? dok_start_bucket(kh, t.nb, t.nb_magic) : 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -29,7 +29,10 @@ int dok_map_uuid(const dok_table *t, const dok_hash_params *hp, const void *keys
   DevTable dt;
   memset(&dt, 0, sizeof(dt));
   if (!dok_make_hash(hp, &dh) || n < 0 || (n > 0 && !keys)) return DOK_BAD_ARG;
-  if (t) dt.nb = t->n_buckets;
+  if (t && t->n_buckets > 0) {
+    dt.nb = t->n_buckets;
+    dt.nb_magic = dt.nb > 1 ? (ull_t)((((unsigned __int128)1) << 64) / (ull_t)dt.nb) : 0ULL;
+  }
   if (n == 0) return DOK_OK;
   RowKeys rk{keys, n};
   k_uuid<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(dt, dh, rk, (ll_t *)uuid_out, (ll_t *)bucket_out);

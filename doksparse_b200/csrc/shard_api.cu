@@ -23,7 +23,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_count(DevHash hp, RowKe
 #pragma unroll
   for (int r = 0; r < DOK_PART_ROUNDS; r++) {
     const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    if (e < keys.n) atomicAdd(&hist[dok_owner_shard(keys.uuid(hp, e), n_shards)], 1);
+    if (e < keys.n) atomicAdd(&hist[dok_owner_shard(keys.hash(hp, e).uuid, n_shards)], 1);
   }
   __syncthreads();
   if (threadIdx.x < n_shards) tile_counts[(ll_t)threadIdx.x * tiles + blockIdx.x] = hist[threadIdx.x];
@@ -67,7 +67,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(DevHash hp, Row
   const ll_t base = (ll_t)blockIdx.x * DOK_PART_TILE;
   for (int r = 0; r < DOK_PART_ROUNDS; r++) {
     const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    const int owner = e < keys.n ? dok_owner_shard(keys.uuid(hp, e), n_shards) : -1;
+    const int owner = e < keys.n ? dok_owner_shard(keys.hash(hp, e).uuid, n_shards) : -1;
     const unsigned peers = __match_any_sync(0xffffffffu, owner);
     const int rank = __popc(peers & ((1u << lane) - 1u));
     if (owner >= 0 && rank == 0) warp_count[warp][owner] = __popc(peers);
@@ -154,7 +154,7 @@ int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found
 /* owner shard of each row (diagnostics and host-side tests of the routing) */
 static __global__ void k_owner(DevHash hp, RowKeys keys, int n_shards, int *owner_out) {
   const ll_t e = (ll_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (e < keys.n) owner_out[e] = dok_owner_shard(keys.uuid(hp, e), n_shards);
+  if (e < keys.n) owner_out[e] = dok_owner_shard(keys.hash(hp, e).uuid, n_shards);
 }
 
 int dok_shard_owner(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, int32_t *owner_out,

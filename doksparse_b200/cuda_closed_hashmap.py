@@ -59,9 +59,10 @@ class CudaClosedHashmap:
         self._value_dtype = None
 
         self._key_size = key_size
-        self._prime1, self._prime2 = prime1, prime2
-        self._alpha1, self._alpha2 = alpha1, alpha2
-        self._beta1, self._beta2 = beta1, beta2
+        as_param = lambda v: v if v is None or isinstance(v, Tensor) else self._as_param(np.asarray(v).reshape(-1).tolist())
+        self._prime1, self._prime2 = as_param(prime1), as_param(prime2)
+        self._alpha1, self._alpha2 = as_param(alpha1), as_param(alpha2)
+        self._beta1, self._beta2 = as_param(beta1), as_param(beta2)
         self._n_elements = torch.zeros(size=(), device=self.device, dtype=torch.long)
         self._rehash_factor = rehash_factor
         self._rehash_threshold = rehash_threshold
@@ -241,11 +242,21 @@ class CudaClosedHashmap:
             ks = int(np.prod(self.key_shape))
             hp.key_size = ks
             hp.key_dtype = L.DTYPE_CODES[self._key_store.dtype]
-            a2, b2, p2, perm = (x.cpu().tolist() for x in (self.alpha2, self.beta2, self.prime2, self.key_perm))
-            assert len(a2) == len(b2) == len(p2) == len(perm) == ks
+            names = ("alpha2", "beta2", "prime2", "alpha1", "beta1", "prime1")
+            host = {name: getattr(self, name).cpu().tolist() for name in names}
+            perm = self.key_perm.cpu().tolist()
+            assert all(len(v) == ks for v in host.values()) and len(perm) == ks
+            for name in names:
+                arr = getattr(hp, name)
+                for i in range(ks):
+                    arr[i] = host[name][i]
             for i in range(ks):
-                hp.alpha2[i], hp.beta2[i], hp.prime2[i], hp.key_perm[i] = a2[i], b2[i], p2[i], perm[i]
-                assert abs(p2[i]) >= 2, "prime2 entries must have magnitude >= 2"
+                hp.key_perm[i] = perm[i]
+                assert abs(host["prime1"][i]) >= 2 and abs(host["prime2"][i]) >= 2, "primes must have magnitude >= 2"
+            if 0 in host["alpha2"]:
+                import warnings
+                warnings.warn("alpha2 contains 0: the uuid ignores that key element, so keys differing only there "
+                              "are told apart only by their first hash (the reference draws alpha2 from [-1, prime1-2])")
             self._hp = hp
         return ctypes.byref(self._hp)
 

@@ -11,7 +11,7 @@
  * Key identity is the reference's 64-bit "uuid" (second hash), not the key bytes
  * (closed_hashmap_impl_class.cu:280-312, 368-427, 459-484).  The uuid is reproduced bit for bit;
  * the start bucket is free (the slot layout is not part of the contract) and is derived from the
- * uuid with a 64-bit mixer.
+ * uuid and the reference's first hash with a 64-bit mixer.
  *
  * Storage of a table with n_buckets slots (three arrays, owned by the caller):
  *   buckets : n_buckets rows of bucket_bytes = max(16, round_up(8 + value_bytes, 16)) bytes:
@@ -51,16 +51,22 @@ typedef enum dok_dtype {
   DOK_F16 = 5, DOK_BF16 = 6, DOK_F32 = 7, DOK_F64 = 8
 } dok_dtype;
 
-/* The uuid hash: uuid = | prod_i ( ((int64)key_i * alpha2[c] + beta2[c]) % prime2[c] ) |, c = key_perm[i],
- * wrapping int64, C remainder, value cast of key_i (closed_hashmap_impl_class.cu:98-107, parameters
- * indexed through keyPerm as in :54-63).  alpha2/beta2/prime2 are given UNPERMUTED, as the Python
- * object holds them (cuda_closed_hashmap.py:79-113).  |prime2[c]| must be >= 2. */
+/* Hash parameters, given UNPERMUTED, as the Python object holds them (cuda_closed_hashmap.py:66-113).
+ * Second hash = the uuid, the key's identity, reproduced bit for bit:
+ *   uuid  = | prod_i ( ((int64)key_i * alpha2[c] + beta2[c]) % prime2[c] ) |,  c = key_perm[i],
+ * wrapping int64, C remainder, value cast of key_i (closed_hashmap_impl_class.cu:98-107, parameters indexed
+ * through keyPerm as in :54-63).  First hash (same form with alpha1/beta1/prime1, :87-96): the reference starts
+ * probing at hash1 % n_buckets; this library starts at mix(uuid, hash1 % n_buckets), so keys that the reference
+ * tells apart only by their first hash stay apart here as well.  |prime1[c]|, |prime2[c]| must be >= 2. */
 typedef struct dok_hash_params {
   int32_t key_size;    /* 1..DOK_MAX_KEY_SIZE */
   int32_t key_dtype;   /* dok_dtype of the caller's key rows */
   int64_t alpha2[DOK_MAX_KEY_SIZE];
   int64_t beta2[DOK_MAX_KEY_SIZE];
   int64_t prime2[DOK_MAX_KEY_SIZE];
+  int64_t alpha1[DOK_MAX_KEY_SIZE];
+  int64_t beta1[DOK_MAX_KEY_SIZE];
+  int64_t prime1[DOK_MAX_KEY_SIZE];
   int32_t key_perm[DOK_MAX_KEY_SIZE]; /* storage column of key element i (set_key_permuted, :144-150) */
 } dok_hash_params;
 

@@ -212,8 +212,8 @@ class OracleHashmap:
         if new_keys.shape[0] == 0:
             return None
         _, is_found = self._kernel_get(new_keys)
-        missing = new_keys[~is_found].reshape(int((~is_found).sum()), -1)
-        n_new = np.unique(missing, axis=0).shape[0] if missing.shape[0] else 0
+        n_missing = int((~is_found).sum())
+        n_new = np.unique(new_keys[~is_found].reshape(n_missing, -1), axis=0).shape[0] if n_missing else 0
         if self._n_elements + n_new > int(self._rehash_threshold * self.n_buckets):
             self.rehash(int((self._n_elements + n_new) * self._rehash_factor))
         stored = np.zeros(new_keys.shape[0], dtype=np.uint8)
@@ -293,6 +293,8 @@ class OracleHashmap:
 
 
 def sort_items(k, v, u):
+    if len(u) == 0:
+        return np.ascontiguousarray(k).reshape(0, 0), np.ascontiguousarray(v).reshape(0, 0), u
     k = np.ascontiguousarray(k).reshape(len(u), -1)
     v = np.ascontiguousarray(v).reshape(len(u), -1)
     order = np.lexsort(tuple(k[:, j] for j in reversed(range(k.shape[1]))) + (u,))

@@ -41,7 +41,7 @@ def test_bucket_geometry():
     assert lib.dok_bucket_bytes(16) == 32 and lib.dok_bucket_bytes(40) == 48
     assert lib.dok_bucket_bytes(0) == -1 and lib.dok_bucket_bytes(249) == -1
     assert lib.dok_compact_tiles(1) == 1 and lib.dok_compact_tiles(2049) == 2
-    assert ctypes.sizeof(_lib.HashParams) == 8 + 3 * 64 + 32
+    assert ctypes.sizeof(_lib.HashParams) == 8 + 6 * 64 + 32
     assert ctypes.sizeof(_lib.Table) == 40
 
 

@@ -60,7 +60,18 @@ class Pair:
 
     def remove(self, keys):
         cr, orr = self.run(lambda: self.c.remove(dev(keys)), lambda: self.o.remove(keys))
-        np.testing.assert_array_equal(host(cr), orr)
+        if np.issubdtype(keys.dtype, np.floating):
+            # float keys are cast by value, so different rows share a uuid (and a slot).  Exactly one row of such a
+            # group reports the removal; which one is unspecified on the GPU (the serial oracle reports the first of
+            # the sorted rows), so flags are compared per uuid group.
+            rows = np.unique(keys.reshape(len(keys), -1), axis=0).reshape((-1,) + keys.shape[1:])
+            _, uu = self.o.hash_uuid(rows)
+            order = np.argsort(uu, kind="stable")
+            bounds = np.flatnonzero(np.diff(uu[order], prepend=uu[order][0] - 1))
+            np.testing.assert_array_equal(np.add.reduceat(host(cr)[order].astype(int), bounds),
+                                          np.add.reduceat(orr[order].astype(int), bounds))
+        else:
+            np.testing.assert_array_equal(host(cr), orr)
         self.check_sizes()
         return orr
 
@@ -71,6 +82,16 @@ class Pair:
     def check_items(self):
         assert_same_items(self.c, self.o)
         assert self.c.n_tombstones <= self.c.n_buckets
+
+
+def good_parameters(n_buckets, ks, seed):
+    """Explicit hash parameters drawn like the reference draws them, rejecting alpha2 == 0 (a draw the reference
+    allows and that makes a key element drop out of the uuid)."""
+    np.random.seed(seed)
+    while True:
+        params = port.draw_hash_parameters(n_buckets, ks)
+        if (params["alpha2"] != 0).all():
+            return params
 
 
 def rand_keys(rng, n, dtype, ks, lo, hi):
@@ -136,23 +157,26 @@ def test_uuid_is_bit_identical(kd, ks, lo, hi):
 
 
 COMBOS = [
-    (np.int64, 1, np.float32, 1, -2 ** 62, 2 ** 62), (np.int64, 1, np.float32, 2, 0, 10 ** 6),
-    (np.int64, 1, np.float32, 4, 0, 3000), (np.int64, 1, np.int64, 1, 0, 3000),
-    (np.int64, 2, np.float32, 1, 0, 60), (np.int64, 3, np.float32, 1, 0, 20), (np.int64, 4, np.float32, 1, 0, 9),
-    (np.int64, 2, np.float64, 1, 0, 60), (np.int32, 2, np.float32, 3, -50, 50), (np.int16, 3, np.int32, 2, -9, 9),
-    (np.float32, 3, np.int64, 5, -20, 20), (np.float64, 2, np.float32, 1, -50, 50),
-    (np.int64, 1, np.uint8, 3, 0, 3000), (np.int64, 2, np.float16, 5, 0, 60), (np.int64, 1, np.float64, 31, 0, 3000),
+    (np.int64, 1, np.float32, 1, -2 ** 62, 2 ** 62), (np.int64, 1, np.float32, 2, 0, 10 ** 7),
+    (np.int64, 1, np.float32, 4, 0, 10 ** 7), (np.int64, 1, np.int64, 1, 0, 10 ** 7),
+    (np.int64, 2, np.float32, 1, 0, 5000), (np.int64, 3, np.float32, 1, 0, 300), (np.int64, 4, np.float32, 1, 0, 80),
+    (np.int64, 2, np.float64, 1, 0, 5000), (np.int32, 2, np.float32, 3, -5000, 5000), (np.int16, 3, np.int32, 2, -150, 150),
+    (np.float32, 3, np.int64, 5, -300, 300), (np.float64, 2, np.float32, 1, -5000, 5000),
+    (np.int64, 1, np.uint8, 3, 0, 10 ** 7), (np.int64, 2, np.float16, 5, 0, 5000), (np.int64, 1, np.float64, 31, 0, 10 ** 7),
 ]
 
 
 @pytest.mark.parametrize("kd,ks,vd,vs,lo,hi", COMBOS)
 def test_operation_stream_matches_oracle(kd, ks, vd, vs, lo, hi):
     """set / get / remove with automatic rehashing, duplicates inside batches (last row wins), tombstone reuse:
-    flags, values, remove flags, n_elements, n_buckets and the live items all equal the serial oracle."""
+    flags, values, remove flags, n_elements, n_buckets and the live items all equal the serial oracle.
+    Tables start at 2^16 buckets: the reference draws alpha and beta below 2 * n_buckets, and with small tables the
+    uuid (a product of small integers) of different multi-element keys coincides often; what happens to such keys
+    depends on the slot layout, in the reference as well as here, so parity is only defined without them."""
     rng = np.random.default_rng(7 + ks + vs)
-    p = Pair(seed=11 + vs, n_buckets=64)
-    for step in range(8):
-        n = 40 + 30 * step
+    p = Pair(seed=11 + vs, n_buckets=2 ** 16)
+    for step in range(6):
+        n = 30_000 + 20_000 * step
         keys, vals = rand_keys(rng, n, kd, ks, lo, hi), rand_values(rng, n, vd, vs)
         if step % 3 == 2:                                # force duplicates inside the batch
             keys[n // 2:] = keys[: n - n // 2]
@@ -161,7 +185,7 @@ def test_operation_stream_matches_oracle(kd, ks, vd, vs, lo, hi):
         p.get(q, fallback=None if step % 2 else 3)
         p.remove(q[rng.permutation(len(q))[: len(q) // 3]])
         p.check_items()
-    assert p.c.n_buckets > 64          # the stream grew the table at least once
+    assert p.c.n_buckets > 2 ** 16          # the stream grew the table at least once
 
 
 def test_tiny_tables_wraparound_and_full():
@@ -169,7 +193,7 @@ def test_tiny_tables_wraparound_and_full():
     (closed_hashmap_impl_class.cu:426), tombstones are reused."""
     for nb in (8, 13, 64):
         rng = np.random.default_rng(nb)
-        p = Pair(seed=nb, n_buckets=nb, rehash_threshold=100.0)
+        p = Pair(seed=nb, n_buckets=nb, rehash_threshold=100.0, **good_parameters(nb, 1, seed=nb))
         keys = rng.permutation(10 * nb)[: 2 * nb].astype(np.int64)[:, None]
         vals = rng.standard_normal((2 * nb, 2)).astype(np.float32)
         first, second = keys[:nb], keys[nb:]
@@ -205,8 +229,15 @@ def test_config1_shape_float_keys_collapse():
     q = np.concatenate([keys[: n // 2], rng.random((n // 2, 3), dtype=np.float32)])
     ov, of = p.get(q)
     assert of.all() and (ov == vals[-1]).all()
-    p.remove(keys[rng.permutation(n)[: n // 4]])
-    p.get(q)
+    # all rows share the one slot: exactly one row of the removal batch reports it (which one is unspecified when the
+    # rows race; the serial reference reports the first of the sorted unique rows)
+    dele = keys[rng.permutation(n)[: n // 4]]
+    removed = host(p.c.remove(dev(dele)))
+    o_removed = p.o.remove(dele)
+    assert removed.sum() == o_removed.sum() == 1 and removed.shape == o_removed.shape
+    p.check_sizes()
+    _, of = p.get(q)
+    assert not of.any()
     p.check_items()
 
 
