@@ -1,0 +1,436 @@
+#!/usr/bin/env python
+"""Benchmark of the hash-map hot path: batched get + set (+ remove of the rows the set inserted) on a
+hash-sharded CudaClosedHashmap.
+
+Workload (BASELINE.json configs[4], per-GPU shard, weak scaling): every GPU holds 2^28 int64 keys drawn
+uniformly from [0, 2^62) mapped to float32[2] values in a shard of 447,392,427 buckets (load 0.6); a step is,
+per GPU, a get of 32 Mi queries (80 % stored keys of ANY shard, 20 % absent), a set of 32 Mi rows (80 %
+stored keys -> overwrite, 20 % new keys) and the removal of the rows that set inserted, which keeps the load
+stationary.  With N GPUs the table has N * 2^28 keys and each rank routes its batch to the owning shards
+(stable partition + NCCL all-to-all) and gets the results back; N = 8 is exactly the 2^31-key configuration.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]            candidate (CUDA), one process per GPU
+  python bench.py --impl reference ...                            the reference's own kernels on the host cores
+
+One JSON line on stdout (rank 0).  Inputs are seeded and synthetic; nothing is read from disk except
+MEASURED_PEAKS.json (the roofline denominator).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M62 = (1 << 62) - 1
+KEY_BYTES, VALUE_BYTES = 8, 8
+HIT_FRACTION = 0.8
+LOAD_FACTOR = 0.6
+N_BATCHES = 4          # distinct query/update batches rotated over the steps (each is larger than L2)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["candidate", "reference"], default="candidate")
+    ap.add_argument("--keys-log2", type=int, default=28, help="stored keys per GPU (default 2^28)")
+    ap.add_argument("--batch-log2", type=int, default=25, help="queries per GPU and step (default 2^25 = 32 Mi)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) measurement")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# byte model and peaks
+# ---------------------------------------------------------------------------------------------------------------
+
+def algorithmic_bytes(op, kb=KEY_BYTES, vb=VALUE_BYTES, hit=HIT_FRACTION):
+    """Bytes one operation must move with the ideal layout (tag and value in one 32-byte sector)."""
+    sectors = -(-(8 + vb) // 32)
+    if op == "get":       # key in, value + flag out, one sector read per probe chain (hit: the bucket row, miss: one tag)
+        return kb + vb + 1 + 32 * (hit * sectors + (1 - hit))
+    if op == "set":       # key + value in, the bucket sector(s) and the key-row sector read and written back
+        return kb + vb + 2 * 32 * -(-(8 + vb + kb) // 32)
+    if op == "remove":    # key in, flag out, the tag sector read and written back
+        return kb + 1 + 2 * 32
+    raise ValueError(op)
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# synthetic keys: a bijection of [0, 2^62) makes every key index a distinct, uniformly spread key
+# ---------------------------------------------------------------------------------------------------------------
+
+def mix62_torch(x):
+    x = (x * 0x2545F4914F6CDD1D) & M62
+    x = x ^ (x >> 29)
+    x = (x * 0x1B03738712FAD5C9) & M62
+    x = x ^ (x >> 32)
+    return x
+
+
+def mix62_numpy(x):
+    x = x.astype(np.uint64)
+    m = np.uint64(M62)
+    x = (x * np.uint64(0x2545F4914F6CDD1D)) & m
+    x = x ^ (x >> np.uint64(29))
+    x = (x * np.uint64(0x1B03738712FAD5C9)) & m
+    x = x ^ (x >> np.uint64(32))
+    return x.astype(np.int64)
+
+
+def value_of_index(idx, xp):
+    """float32[2] value stored for key index idx (lets the bench verify what a get returns)"""
+    a = (idx & 0xFFFF)
+    b = ((idx >> 16) & 0xFF)
+    if xp is np:
+        return np.stack([a, b], axis=1).astype(np.float32)
+    return xp.stack([a, b], dim=1).float()
+
+
+def fixed_parameters():
+    """Explicit hash parameters, identical on every rank: one draw of the reference's generator (numpy seed 2024)
+    for a table of 2^28 / 0.6 buckets."""
+    return dict(prime1=[825411893], prime2=[131956765728754273], alpha1=[808106522], alpha2=[408516131],
+                beta1=[188156349], beta2=[614383798])
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.thread = [], None, None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+                for name, cell in zip(names, r[4:8]):
+                    if cell.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's own kernels compiled for the host (oracle/_ref), else the C restatement
+# ---------------------------------------------------------------------------------------------------------------
+
+def cpu_arm(steps, warmup, sample_keys_log2=24, sample_batch_log2=22, budget_s=None):
+    """One step = get(q) + set(q) + remove(inserted) on a table of 2^sample_keys_log2 keys at load 0.6, all host
+    threads.  Returns (Mops/s over get+set rows, description dict)."""
+    from oracle import port, ref
+    cores = len(os.sched_getaffinity(0))
+    n_keys, q = 1 << sample_keys_log2, 1 << sample_batch_log2
+    nb = int(n_keys / LOAD_FACTOR)
+    params = {k: np.asarray(v, dtype=np.int64) for k, v in fixed_parameters().items()}
+    params["key_perm"] = np.zeros(1, dtype=np.int64)
+    use_ref = os.path.exists(ref.map_lib_path("i64x1_f32x2"))
+    if use_ref:
+        table = ref.RefMap(nb, np.int64, 1, np.float32, 2, params, n_threads=cores)
+        do_set, do_get, do_remove = table.set, table.get, table.remove
+        kind = "reference"
+    else:
+        table = port.OracleHashmap(n_buckets=nb, n_threads=cores, **{k: v for k, v in params.items() if k != "key_perm"})
+        table._keys, table._values = np.zeros((nb, 1), np.int64), np.zeros((nb, 2), np.float32)
+        do_set, do_get, do_remove = table.set_rows, table._kernel_get, table.remove_rows
+        kind = "port"
+    idx = np.arange(n_keys, dtype=np.int64)
+    for lo in range(0, n_keys, 1 << 22):
+        part = idx[lo:lo + (1 << 22)]
+        do_set(mix62_numpy(part)[:, None], value_of_index(part, np))
+    n_hit = int(q * HIT_FRACTION)
+    batches = []
+    for b in range(2):
+        rng = np.random.default_rng(b)
+        hit_idx = (np.arange(n_hit, dtype=np.int64) * 7919 + 104729 * (b + 1)) % n_keys
+        miss_idx = (1 << 40) + (b << 32) + np.arange(q - n_hit, dtype=np.int64)
+        new_idx = (1 << 41) + (b << 32) + np.arange(q - n_hit, dtype=np.int64)
+        perm = rng.permutation(q)
+        gq = mix62_numpy(np.concatenate([hit_idx, miss_idx]))[perm][:, None]
+        sk_idx = np.concatenate([hit_idx, new_idx])[perm]
+        batches.append((gq, mix62_numpy(sk_idx)[:, None], value_of_index(sk_idx, np), mix62_numpy(new_idx)[:, None]))
+
+    def step(b):
+        gq, sk, sv, fresh = batches[b % 2]
+        do_get(gq)
+        do_set(sk, sv)
+        do_remove(fresh)
+
+    for s in range(warmup):
+        step(s)
+    t0 = time.perf_counter()
+    done = 0
+    for s in range(steps):
+        step(s)
+        done += 1
+        if budget_s is not None and time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    mops = done * 2 * q / dt / 1e6
+    desc = {"value": mops, "unit": "Mops/s", "cores": cores, "kind": kind,
+            "sample": f"table of 2^{sample_keys_log2} keys at load {LOAD_FACTOR}, {done} steps of get 2^{sample_batch_log2} + "
+                      f"set 2^{sample_batch_log2} + remove of the inserted 20 %, kernels only (no Python-side pre-get / unique)"}
+    return mops, dt / max(done, 1) * 1e3, desc
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    mops, ms, desc = cpu_arm(args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": "hashmap get/set Mops/s", "value": mops, "unit": "Mops/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+        "config": workload_config(args, world=args.gpus),
+        "cpu_baseline": desc,
+        "e2e": {"value": mops, "unit": "Mops/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(args, world):
+    return {
+        "workload": "BASELINE configs[4]: hash-sharded CudaClosedHashmap, int64 keys uniform in [0,2^62) -> float32[2], "
+                    f"2^{args.keys_log2} keys per GPU at load {LOAD_FACTOR}, per GPU and step: get 2^{args.batch_log2} "
+                    f"(80% hits) + set 2^{args.batch_log2} (80% overwrite, 20% insert) + remove of the inserted rows",
+        "keys_per_gpu": 1 << args.keys_log2, "buckets_per_gpu": int((1 << args.keys_log2) / LOAD_FACTOR),
+        "batch_per_gpu": 1 << args.batch_log2, "shards": world,
+        "l2_policy": f"inputs larger than L2: {N_BATCHES} rotating batches of {(1 << args.batch_log2) * 8 >> 20} MiB keys, "
+                     f"table {(int((1 << args.keys_log2) / LOAD_FACTOR) * 16) >> 20} MiB per GPU",
+        "parallelism": f"hash-sharded x{world}, NCCL all-to-all" if world > 1 else "single GPU",
+    }
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# candidate arm
+# ---------------------------------------------------------------------------------------------------------------
+
+def run_candidate(args):
+    import torch
+    import torch.distributed as dist
+    from doksparse_b200 import _lib as L
+    from doksparse_b200.sharded import ShardedClosedHashmap
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+
+    n_keys, q = 1 << args.keys_log2, 1 << args.batch_log2
+    total_keys = n_keys * world
+    nb = int(n_keys / LOAD_FACTOR)
+    table = ShardedClosedHashmap(nb, device=device, rehash_threshold=0.95, **fixed_parameters())
+
+    # ---- build (untimed): rank r inserts key indices [r * n_keys, (r + 1) * n_keys), routed to their owners
+    chunk = min(n_keys, 1 << 25)
+    for lo in range(rank * n_keys, (rank + 1) * n_keys, chunk):
+        idx = torch.arange(lo, lo + chunk, device=device, dtype=torch.long)
+        table.set(mix62_torch(idx)[:, None], value_of_index(idx, torch), assume_unique=True)
+    del idx
+    assert table.n_elements == total_keys, "build lost keys"
+
+    # ---- batches
+    n_hit = int(q * HIT_FRACTION)
+    g = torch.Generator(device=device).manual_seed(1234 + rank)
+    batches = []
+    for b in range(N_BATCHES):
+        j = torch.arange(n_hit, device=device, dtype=torch.long)
+        hit_idx = (j * 7919 + 104729 * (b + 1) + 15485863 * rank) % total_keys
+        base = (b << 32) + (rank << 28)
+        miss_idx = (1 << 40) + base + torch.arange(q - n_hit, device=device, dtype=torch.long)
+        new_idx = (1 << 41) + base + torch.arange(q - n_hit, device=device, dtype=torch.long)
+        perm = torch.randperm(q, device=device, generator=g)
+        get_idx = torch.cat([hit_idx, miss_idx])[perm]
+        set_idx = torch.cat([hit_idx, new_idx])[perm]
+        batches.append({
+            "get_keys": mix62_torch(get_idx)[:, None].contiguous(), "get_idx": get_idx,
+            "set_keys": mix62_torch(set_idx)[:, None].contiguous(), "set_values": value_of_index(set_idx, torch).contiguous(),
+            "fresh_keys": mix62_torch(new_idx)[:, None].contiguous(),
+        })
+    del j, hit_idx, miss_idx, new_idx, perm, set_idx
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(b, events=None):
+        d = batches[b % N_BATCHES]
+        if events is not None:
+            events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
+        values, found = table.get(d["get_keys"])
+        if events is not None:
+            events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
+        table.set(d["set_keys"], d["set_values"])
+        if events is not None:
+            events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
+        table.remove(d["fresh_keys"])
+        if events is not None:
+            events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
+        return values, found
+
+    # ---- correctness of what is being timed (first batch, before any timing)
+    values, found = step(0)
+    d0 = batches[0]
+    expect_found = d0["get_idx"] < (1 << 40)
+    checks = {"found_flags_ok": bool(torch.equal(found, expect_found)),
+              "hit_values_ok": bool(torch.equal(values[expect_found], value_of_index(d0["get_idx"][expect_found], torch))),
+              "miss_values_zero": bool((values[~expect_found] == 0).all()),
+              "n_elements_stationary": table.n_elements == total_keys}
+    del values, found, expect_found
+
+    for s in range(1, args.warmup):
+        step(s)
+
+    # ---- timed region: exactly K steps, device-resident inputs
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = L.lib().dok_launch_count()
+    events = []
+    barrier()
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for s in range(args.steps):
+        step(s + args.warmup, events)
+    t_stop.record()
+    barrier()
+    launches = L.lib().dok_launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    elapsed_ms = torch.tensor([t_start.elapsed_time(t_stop)], device=device)
+    phase = torch.zeros(3, device=device)
+    for s in range(args.steps):
+        e = events[4 * s: 4 * s + 4]
+        phase += torch.tensor([e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), e[2].elapsed_time(e[3])], device=device)
+    phase /= args.steps
+    if world > 1:
+        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(phase, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(elapsed_ms.item())
+    get_ms, set_ms, remove_ms = (float(x) for x in phase.tolist())
+    ms_per_step = elapsed_ms / args.steps
+    ops_per_step = 2 * q * world                         # get rows + set rows over all GPUs
+    value = ops_per_step / (ms_per_step * 1e-3) / 1e6
+
+    # ---- end to end: host (pinned) buffers in, host buffers out, through the public API
+    e2e = None
+    if not args.no_e2e:
+        host = [{k: v.cpu().pin_memory() for k, v in d.items() if k != "get_idx"} for d in batches[:2]]
+        out_values = torch.empty(q, 2, dtype=torch.float32).pin_memory()
+        out_found = torch.empty(q, dtype=torch.bool).pin_memory()
+        h2d = sum(host[0][k].numel() * host[0][k].element_size() for k in ("get_keys", "set_keys", "set_values", "fresh_keys"))
+        d2h = out_values.numel() * 4 + out_found.numel()
+
+        def e2e_step(b):
+            h = host[b % 2]
+            gk = h["get_keys"].to(device, non_blocking=True)
+            values, found = table.get(gk)
+            out_values.copy_(values, non_blocking=True)
+            out_found.copy_(found, non_blocking=True)
+            table.set(h["set_keys"].to(device, non_blocking=True), h["set_values"].to(device, non_blocking=True))
+            table.remove(h["fresh_keys"].to(device, non_blocking=True))
+
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_step(0)
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for s in range(e2e_steps):
+            e2e_step(s + 1)
+        t1.record()
+        barrier()
+        e_ms = torch.tensor([t0.elapsed_time(t1)], device=device)
+        if world > 1:
+            dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
+        e2e = {"value": ops_per_step / (float(e_ms.item()) / e2e_steps * 1e-3) / 1e6, "unit": "Mops/s",
+               "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e2e_steps}
+
+    # ---- roofline of the dominant kernel and of the other two
+    peak, peak_source = measured_peak_gbs()
+    local_rows = {"get": q, "set": q, "remove": q - n_hit}       # rows each GPU processes per step (weak scaling)
+    kernel_ms = {"get": get_ms, "set": set_ms, "remove": remove_ms}
+    per_kernel = {}
+    for op in ("get", "set", "remove"):
+        achieved = algorithmic_bytes(op) * local_rows[op] / (kernel_ms[op] * 1e-3) / 1e9
+        per_kernel[op] = {"ms": kernel_ms[op], "mops_per_gpu": local_rows[op] / (kernel_ms[op] * 1e-3) / 1e6,
+                          "bytes_per_op": algorithmic_bytes(op), "achieved_gbs": achieved, "frac": achieved / peak}
+    top = max(kernel_ms, key=kernel_ms.get)
+    roofline = {"bound": "hbm", "kernel": {"get": "k_get", "set": "k_set_claim + k_set_write", "remove": "k_find<remove>"}[top],
+                "achieved": per_kernel[top]["achieved_gbs"], "peak": peak, "unit": "GB/s", "frac": per_kernel[top]["frac"],
+                "traffic": None, "peak_source": peak_source,
+                "note": "phase time includes routing and exchange when shards > 1" if world > 1 else "phase = kernel(s) of one op"}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        _, _, cpu_baseline = cpu_arm(steps=4, warmup=1, budget_s=25.0)
+
+    if rank == 0:
+        line = {
+            "metric": "hashmap get/set Mops/s", "value": value, "unit": "Mops/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int64", "data": "synthetic", "config": workload_config(args, world),
+            "roofline": roofline, "kernels": per_kernel, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": int(launches), "clocks": clocks, "checks": checks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_candidate(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -65,6 +65,7 @@ def _declare(lib):
     sig = {
         "dok_version": ([], I),
         "dok_last_cuda_error": ([], I),
+        "dok_launch_count": ([], I64),
         "dok_bucket_bytes": ([I], I),
         "dok_map_init": ([TP, P], I),
         "dok_map_uuid": ([TP, HP, P, I64, P, P, P], I),

@@ -17,7 +17,14 @@ inline int &dok_last_error_slot() {
   return last;
 }
 
+// number of kernels this library has launched in this process (every launch is followed by dok_check_launch)
+inline long long &dok_launch_counter() {
+  static long long count = 0;
+  return count;
+}
+
 inline int dok_check_launch() {
+  dok_launch_counter()++;
   const cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     dok_last_error_slot() = (int)err;

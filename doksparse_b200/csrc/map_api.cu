@@ -8,6 +8,7 @@ extern "C" {
 
 int dok_version(void) { return 1; }
 int dok_last_cuda_error(void) { return dok_last_error_slot(); }
+int64_t dok_launch_count(void) { return dok_launch_counter(); }
 
 int dok_bucket_bytes(int value_bytes) {
   if (value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES) return -1;

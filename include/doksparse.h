@@ -105,6 +105,7 @@ typedef struct dok_selectors {
 
 int dok_version(void);
 int dok_last_cuda_error(void);          /* cudaError_t of the last failed launch on this thread */
+int64_t dok_launch_count(void);         /* kernels launched by this library in this process so far */
 int dok_bucket_bytes(int value_bytes);  /* max(16, round_up(8 + value_bytes, 16)); -1 if unsupported */
 
 /* Fills tags with DOK_TAG_EMPTY (values untouched) and, if present, zeroes `stamp`.
