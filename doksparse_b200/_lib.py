@@ -16,6 +16,7 @@ MAX_VALUE_BYTES = 248
 MAX_SELECTOR_NDIM = 8
 MAX_SHARDS = 64
 N_COUNTERS = 8
+MAX_EPOCH = (1 << 30) - 1
 CNT_CLAIMED_EMPTY, CNT_REUSED_REMOVED, CNT_FAILED, CNT_HITS, CNT_DUPLICATES, CNT_PROBES = range(6)
 
 DTYPE_CODES = {
@@ -37,8 +38,17 @@ class HashParams(ctypes.Structure):
 
 class Table(ctypes.Structure):
     _fields_ = [
-        ("buckets", ctypes.c_void_p), ("keys", ctypes.c_void_p), ("stamp", ctypes.c_void_p),
-        ("n_buckets", ctypes.c_int64), ("bucket_bytes", ctypes.c_int32), ("value_bytes", ctypes.c_int32),
+        ("slots", ctypes.c_void_p), ("stamp", ctypes.c_void_p), ("n_buckets", ctypes.c_int64),
+        ("slot_bytes", ctypes.c_int32), ("value_bytes", ctypes.c_int32), ("key_bytes", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+    ]
+
+
+class LayoutInfo(ctypes.Structure):
+    _fields_ = [
+        ("slot_bytes", ctypes.c_int32), ("slots_per_group", ctypes.c_int32), ("value_offset", ctypes.c_int32),
+        ("key_offset", ctypes.c_int32), ("stamp_offset", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("n_slots", ctypes.c_int64), ("total_bytes", ctypes.c_int64),
     ]
 
 
@@ -66,7 +76,7 @@ def _declare(lib):
         "dok_version": ([], I),
         "dok_last_cuda_error": ([], I),
         "dok_launch_count": ([], I64),
-        "dok_bucket_bytes": ([I], I),
+        "dok_table_layout": ([I, I, I64, ctypes.POINTER(LayoutInfo)], I),
         "dok_map_init": ([TP, P], I),
         "dok_map_uuid": ([TP, HP, P, I64, P, P, P], I),
         "dok_map_get": ([TP, HP, P, I64, P, P, P, P, P], I),

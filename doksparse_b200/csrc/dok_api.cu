@@ -23,6 +23,13 @@ struct StridedValues {
   }
 };
 
+static bool prepare(const dok_table *t, const dok_hash_params *hp, DevTable *dt, DevHash *dh) {
+  if (!dok_make_hash(hp, dh) || !dok_make_table(t, dt)) return false;
+  return dt->kb == dh->ks * dh->elem_bytes;
+}
+
+static unsigned grid_for(ll_t n) { return (unsigned)((n + DOK_TPB - 1) / DOK_TPB); }
+
 static bool make_sel(const dok_selectors *sel, const DevHash &dh, SelKeys *out) {
   if (!sel || sel->ndim != dh.ks || dh.dtype != DOK_I64) return false;
   if (sel->selector_ndim < 0 || sel->selector_ndim > DOK_MAX_SELECTOR_NDIM) return false;
@@ -55,46 +62,50 @@ __global__ void __launch_bounds__(DOK_TPB) k_dense_count(const T *__restrict__ d
 
 struct DenseShape { int ndim; ll_t sizes[DOK_MAX_KEY_SIZE]; };
 
-template <typename T>
+template <int SB, typename T>
 __global__ void __launch_bounds__(DOK_TPB) k_dense_insert(DevTable t, DevHash hp, const T *__restrict__ dense, ll_t numel,
                                                           int is_float, DenseShape shape, ll_t *counters) {
-  int outcome = -1;
   const ll_t stride = (ll_t)gridDim.x * DOK_TPB;
-  for (ll_t base = (ll_t)blockIdx.x * DOK_TPB; base < numel; base += stride) {
+  for (ll_t base = (ll_t)blockIdx.x * DOK_TPB; base < numel; base += stride) {     // uniform over the block
     const ll_t i = base + threadIdx.x;
-    outcome = -1;
+    int outcome = -1;
+    T v = 0;
+    bool active = false;
     if (i < numel) {
-      const T v = __ldcs(dense + i);
-      if (dok_nonzero<T>(v, is_float)) {
-        // unravel the row-major position into the index tuple; each index is one factor of the uuid product
-        ll_t idx[DOK_MAX_KEY_SIZE];
-        ull_t rem = (ull_t)i;
+      v = __ldcs(dense + i);
+      active = dok_nonzero<T>(v, is_float);
+    }
+    ll_t idx[DOK_MAX_KEY_SIZE];
+    KeyHash kh{0, 0};
+    if (active) {
+      // unravel the row-major position into the index tuple; each index is one factor of the hash products
+      ull_t rem = (ull_t)i;
 #pragma unroll
-        for (int d = DOK_MAX_KEY_SIZE - 1; d >= 0; d--) {
-          idx[d] = 0;
-          if (d < shape.ndim) {
-            const ull_t size = (ull_t)shape.sizes[d];
-            const ull_t q = rem / size;
-            idx[d] = (ll_t)(rem - q * size);
-            rem = q;
-          }
-        }
-        ll_t u = dok_uuid_term(idx[0], hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
-        ll_t h = dok_uuid_term(idx[0], hp.a1[0], hp.b1[0], hp.p1[0], hp.m1[0]);
-#pragma unroll
-        for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
-          if (d < shape.ndim) {
-            u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
-            h = (ll_t)((ull_t)h * (ull_t)dok_uuid_term(idx[d], hp.a1[d], hp.b1[d], hp.p1[d], hp.m1[d]));
-          }
-        const ll_t slot = dok_find_or_claim(t, KeyHash{dok_llabs(u), dok_llabs(h)}, &outcome);
-        if (slot >= 0) {
-          ll_t *krow = (ll_t *)(t.keys + slot * (ll_t)t.kb);
-#pragma unroll
-          for (int d = 0; d < DOK_MAX_KEY_SIZE; d++) if (d < shape.ndim) krow[hp.perm[d]] = idx[d];
-          *(T *)(t.buckets + slot * (ll_t)t.bb + 8) = v;
+      for (int d = DOK_MAX_KEY_SIZE - 1; d >= 0; d--) {
+        idx[d] = 0;
+        if (d < shape.ndim) {
+          const ull_t size = (ull_t)shape.sizes[d];
+          const ull_t q = rem / size;
+          idx[d] = (ll_t)(rem - q * size);
+          rem = q;
         }
       }
+      ll_t u = dok_uuid_term(idx[0], hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+      ull_t h = (ull_t)idx[0] * (ull_t)hp.a1[0] + (ull_t)hp.b1[0];
+#pragma unroll
+      for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
+        if (d < shape.ndim) {
+          u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
+          h *= (ull_t)idx[d] * (ull_t)hp.a1[d] + (ull_t)hp.b1[d];
+        }
+      kh = KeyHash{dok_llabs(u), (ll_t)h};
+    }
+    const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
+    if (active && slot >= 0) {
+      ll_t *krow = (ll_t *)dok_key_row(t, slot);
+#pragma unroll
+      for (int d = 0; d < DOK_MAX_KEY_SIZE; d++) if (d < shape.ndim) krow[hp.perm[d]] = idx[d];
+      *(T *)dok_value_ptr(t, slot) = v;
     }
     if (counters) {
       dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
@@ -118,7 +129,7 @@ int dok_dok_get(const dok_table *t, const dok_hash_params *hp, const dok_selecto
   DevHash dh;
   DevTable dt;
   SelKeys sk;
-  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || !make_sel(sel, dh, &sk)) return DOK_BAD_ARG;
+  if (!prepare(t, hp, &dt, &dh) || !make_sel(sel, dh, &sk)) return DOK_BAD_ARG;
   if (sk.n > 0 && !out_values) return DOK_BAD_ARG;
   return launch_get(dt, dh, sk, out_values, out_found, fallback, counters, 0, (cudaStream_t)stream);
 }
@@ -128,9 +139,9 @@ int dok_dok_count_exists(const dok_table *t, const dok_hash_params *hp, const do
   DevHash dh;
   DevTable dt;
   SelKeys sk;
-  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || !make_sel(sel, dh, &sk) || !counters) return DOK_BAD_ARG;
+  if (!prepare(t, hp, &dt, &dh) || !make_sel(sel, dh, &sk) || !counters) return DOK_BAD_ARG;
   if (sk.n == 0) return DOK_OK;
-  k_find<0><<<(unsigned)((sk.n + DOK_TPB - 1) / DOK_TPB), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, nullptr, (ll_t *)counters);
+  DOK_DISPATCH_SB(dt, (k_find<SB, 0><<<grid_for(sk.n), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, nullptr, (ll_t *)counters)));
   return dok_check_launch();
 }
 
@@ -139,9 +150,9 @@ int dok_dok_zero_items(const dok_table *t, const dok_hash_params *hp, const dok_
   DevHash dh;
   DevTable dt;
   SelKeys sk;
-  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || !make_sel(sel, dh, &sk) || !counters) return DOK_BAD_ARG;
+  if (!prepare(t, hp, &dt, &dh) || !make_sel(sel, dh, &sk) || !counters) return DOK_BAD_ARG;
   if (sk.n == 0) return DOK_OK;
-  k_find<1><<<(unsigned)((sk.n + DOK_TPB - 1) / DOK_TPB), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, nullptr, (ll_t *)counters);
+  DOK_DISPATCH_SB(dt, (k_find<SB, 1><<<grid_for(sk.n), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, nullptr, (ll_t *)counters)));
   return dok_check_launch();
 }
 
@@ -151,9 +162,9 @@ int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_s
   DevHash dh;
   DevTable dt;
   SelKeys sk;
-  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || !make_sel(sel, dh, &sk)) return DOK_BAD_ARG;
+  if (!prepare(t, hp, &dt, &dh) || !make_sel(sel, dh, &sk)) return DOK_BAD_ARG;
   if (sk.n == 0) return DOK_OK;
-  if (!src || !src_strides || !slot_scratch || !dt.stamp || epoch < 1 || epoch > 0x7fffffffLL) return DOK_BAD_ARG;
+  if (!src || !src_strides || !slot_scratch || !dok_has_stamps(dt) || epoch < 1 || epoch > DOK_MAX_EPOCH) return DOK_BAD_ARG;
   StridedValues sv;
   sv.src = (const char *)src;
   sv.selector_ndim = sel->selector_ndim;
@@ -161,11 +172,13 @@ int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_s
     sv.sizes[j] = j < sel->selector_ndim ? sel->sizes[j] : 1;
     sv.strides[j] = j < sel->selector_ndim ? src_strides[j] : 0;
   }
-  const unsigned grid = (unsigned)((sk.n + DOK_TPB - 1) / DOK_TPB);
-  k_set_claim<<<grid, DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, (ll_t *)slot_scratch, (ll_t)epoch, (ll_t *)counters);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemsetAsync(slot_scratch + sk.n, 0, sizeof(int64_t), st) != cudaSuccess) return dok_check_launch();
+  DOK_DISPATCH_SB(dt, (k_set_claim<SB><<<grid_for(sk.n), DOK_TPB, 0, st>>>(dt, dh, sk, sv, (ll_t *)slot_scratch, (ll_t)epoch,
+                                                                           nullptr, (ll_t *)counters)));
   int rc = dok_check_launch();
   if (rc != DOK_OK) return rc;
-  k_set_write<<<grid, DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, sv, (const ll_t *)slot_scratch, (ll_t)epoch, nullptr);
+  k_set_resolve<<<grid_for(sk.n), DOK_TPB, 0, st>>>(dt, dh, sk, sv, (const ll_t *)slot_scratch, (ll_t)epoch);
   return dok_check_launch();
 }
 
@@ -189,7 +202,7 @@ int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, cons
                              int64_t numel, int is_float, int64_t *counters, void *stream) {
   DevHash dh;
   DevTable dt;
-  if (!dok_make_hash(hp, &dh) || !dok_make_table(t, &dh, &dt) || dh.dtype != DOK_I64 || !sizes || numel < 0) return DOK_BAD_ARG;
+  if (!prepare(t, hp, &dt, &dh) || dh.dtype != DOK_I64 || !sizes || numel < 0) return DOK_BAD_ARG;
   if (numel == 0) return DOK_OK;
   if (!dense) return DOK_BAD_ARG;
   DenseShape shape;
@@ -204,10 +217,10 @@ int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, cons
   const unsigned grid = streaming_grid(numel);
   cudaStream_t st = (cudaStream_t)stream;
   switch (dt.vb) {
-    case 1: k_dense_insert<unsigned char><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned char *)dense, numel, is_float, shape, (ll_t *)counters); break;
-    case 2: k_dense_insert<unsigned short><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned short *)dense, numel, is_float, shape, (ll_t *)counters); break;
-    case 4: k_dense_insert<unsigned><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned *)dense, numel, is_float, shape, (ll_t *)counters); break;
-    case 8: k_dense_insert<ull_t><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const ull_t *)dense, numel, is_float, shape, (ll_t *)counters); break;
+    case 1: DOK_DISPATCH_SB(dt, (k_dense_insert<SB, unsigned char><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned char *)dense, numel, is_float, shape, (ll_t *)counters))); break;
+    case 2: DOK_DISPATCH_SB(dt, (k_dense_insert<SB, unsigned short><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned short *)dense, numel, is_float, shape, (ll_t *)counters))); break;
+    case 4: DOK_DISPATCH_SB(dt, (k_dense_insert<SB, unsigned><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned *)dense, numel, is_float, shape, (ll_t *)counters))); break;
+    case 8: DOK_DISPATCH_SB(dt, (k_dense_insert<SB, ull_t><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const ull_t *)dense, numel, is_float, shape, (ll_t *)counters))); break;
     default: return DOK_BAD_ARG;
   }
   return dok_check_launch();

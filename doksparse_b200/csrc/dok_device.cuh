@@ -3,9 +3,18 @@
 // Semantics follow the reference's ClosedHashmap class
 // (sparse_dok/components/cuda/closed_hashmap_impl_class.cu): key identity is the 64-bit uuid, tags are
 // uuid / -1 (empty) / -3 (tombstone), probing is linear, a lookup stops at the first empty tag and steps
-// over tombstones.  What differs on purpose is the memory layout (tag and value share one bucket row so that
-// a hit costs one 32-byte sector) and the start bucket (a mixer of the uuid instead of the reference's first
-// hash, whose product form clusters badly on power-of-two tables).
+// over tombstones.  What differs on purpose is the memory layout and the start slot.
+//
+// Layout.  On B200, when the table is much larger than L2, every load / store / atomic INSTRUCTION-LANE that
+// touches it costs the same (~48 G per second over the whole GPU, measured; a second access to a sector that
+// was just read costs as much as a new random line), while lanes of one instruction that fall into the same
+// 128-byte line count once.  So an operation should touch its line with as few instructions as possible, and
+// adjacent lanes should share them.  A slot is {int64 tag | value | key row | stamp (if room)} padded to 32, 64
+// or 128 bytes (tag first, value right behind it), a 128-byte line is a GROUP of 4, 2 or 1 slots, and probing
+// starts at a group boundary.  The four
+// lanes of a quad read one group with ONE coalesced 128-byte request (32 bytes per lane) and resolve a lookup
+// from registers: tags, value and key of all its slots are then on chip.  The probe order is still plain linear
+// probing over slots (group after group); only the start is aligned.
 #pragma once
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
@@ -33,26 +42,30 @@ struct DevHash {
   ll_t b[DOK_MAX_KEY_SIZE];     // beta2[key_perm[i]]
   ull_t p[DOK_MAX_KEY_SIZE];    // |prime2[key_perm[i]]|  (>= 2)
   ull_t m[DOK_MAX_KEY_SIZE];    // floor(2^64 / p)
-  ll_t a1[DOK_MAX_KEY_SIZE];    // alpha1[key_perm[i]]   -- first hash: only decorrelates the probe chains of
-  ll_t b1[DOK_MAX_KEY_SIZE];    // beta1[key_perm[i]]       keys whose uuids collide (see dok_start_bucket)
-  ull_t p1[DOK_MAX_KEY_SIZE];   // |prime1[key_perm[i]]|
-  ull_t m1[DOK_MAX_KEY_SIZE];   // floor(2^64 / p1)
+  ll_t a1[DOK_MAX_KEY_SIZE];    // alpha1[key_perm[i]], forced odd -- first-hash terms: they only decorrelate the
+  ll_t b1[DOK_MAX_KEY_SIZE];    // beta1[key_perm[i]]                 probe chains of keys whose uuids collide
   int perm[DOK_MAX_KEY_SIZE];   // storage column of key element i
 };
 
-struct KeyHash { ll_t uuid; ll_t hash1; };
+struct KeyHash { ll_t uuid; ll_t hash1; };   // hash1: product of the linear first-hash terms (see dok_start_group)
 
 struct DevTable {
-  char *buckets;    // n_buckets * bb bytes: {int64 tag; value; pad}
-  char *keys;       // n_buckets * kb bytes
-  ll_t *stamp;      // n_buckets or nullptr
-  ll_t nb;
-  ull_t nb_magic;   // floor(2^64 / nb)
-  int bb;           // bucket bytes (multiple of 16)
+  char *slots;      // n_slots * sb bytes, 128-byte aligned
+  ll_t *stamp;      // [n_slots] duplicate-resolution stamps when they do not fit in the slot, else nullptr
+  ll_t nb;          // slots the caller sees (0 .. nb-1); slots nb .. n_slots-1 are blocked padding
+  ll_t n_slots;     // n_groups * spg
+  ll_t n_groups;    // probe groups: 128-byte lines of spg slots (sb <= 128), single slots otherwise
+  int sb;           // slot bytes: 32, 64, 128, or a larger multiple of 128
+  int spg;          // slots per group: 128 / sb, or 1 for sb > 128
   int vb;           // value bytes
   int kb;           // key row bytes
+  int val_off;      // slot offset of the value: always 8, right behind the tag
+  int key_off;      // slot offset of the key row: 8 + round_up(vb, 8)
+  int stamp_off;    // slot offset of the stamp (behind the key row), -1 when `stamp` is a separate array
   int vwords;       // ceil(vb / 8)
 };
+
+#define DOK_BLOCKED (-2LL)   // tag of padding slots: never empty, never a tombstone, never a uuid (uuids are >= 0)
 
 // One factor of the uuid product: ((int64)k * a + b) % p with wrapping arithmetic and the C remainder
 // (sign of the dividend), closed_hashmap_impl_class.cu:100,103.  q = mulhi(|x|, floor(2^64/p)) is
@@ -95,16 +108,14 @@ __device__ __forceinline__ ull_t dok_mix64(ull_t h) {
   h ^= h >> 33;
   return h;
 }
-// Start bucket.  In the reference two keys whose uuids collide are still told apart as long as their probe
+// Start group.  In the reference two keys whose uuids collide are still told apart as long as their probe
 // chains (first hash modulo n_buckets) do not meet; a uuid collision is not rare there, because alpha2 may be
 // drawn as 0 (cuda_closed_hashmap.py:100), which makes one key element drop out of the uuid.  To keep that
-// property the start bucket mixes the uuid with the reference's first hash reduced modulo n_buckets: keys
-// that collide in BOTH collide here too, keys that collide in the uuid only get unrelated chains.
-__device__ __forceinline__ ll_t dok_start_bucket(const KeyHash &h, ll_t nb, ull_t nb_magic) {
-  const ull_t h1 = (ull_t)h.hash1;
-  ull_t r = h1 - __umul64hi(h1, nb_magic) * (ull_t)nb;       // h1 % nb
-  if (r >= (ull_t)nb) r -= (ull_t)nb;
-  return (ll_t)__umul64hi(dok_mix64((ull_t)h.uuid ^ ((r + 1) * 0x9e3779b97f4a7c15ULL)), (ull_t)nb);
+// property the start group mixes the uuid with a second function of the key built from the first hash's
+// parameters, prod_i (key_i * (alpha1_i | 1) + beta1_i) (wrapping, no modulo: it only has to differ where the
+// keys differ): keys that collide in the uuid alone get unrelated chains.
+__device__ __forceinline__ ll_t dok_start_group(const KeyHash &h, const DevTable &t) {
+  return (ll_t)__umul64hi(dok_mix64((ull_t)h.uuid ^ ((ull_t)h.hash1 * 0x9e3779b97f4a7c15ULL)), (ull_t)t.n_groups);
 }
 #define DOK_SHARD_SALT 0x9e3779b97f4a7c15ULL
 __device__ __forceinline__ int dok_owner_shard(ll_t uuid, int n_shards) {
@@ -120,17 +131,23 @@ struct RowKeys {          // contiguous [n, ks] rows of the key dtype (closed_ha
   const void *keys;
   ll_t n;
   __device__ __forceinline__ ll_t count() const { return n; }
-  // get_uuid and get_hash of the reference (closed_hashmap_impl_class.cu:87-107) in one pass over the key
+  // get_uuid of the reference (closed_hashmap_impl_class.cu:98-107) and the chain-decorrelating product, in one
+  // pass over the key
   __device__ __forceinline__ KeyHash hash(const DevHash &hp, ll_t e) const {
+    if (hp.ks == 1 && hp.dtype == DOK_I64) {          // the common case, kept free of loops and type dispatch
+      const ll_t k = ((const ll_t *)keys)[e];
+      return KeyHash{dok_llabs(dok_uuid_term(k, hp.a[0], hp.b[0], hp.p[0], hp.m[0])),
+                     (ll_t)((ull_t)k * (ull_t)hp.a1[0] + (ull_t)hp.b1[0])};
+    }
     ll_t k = dok_key_elem(keys, hp.dtype, e * hp.ks);
     ll_t u = dok_uuid_term(k, hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
-    ll_t h = dok_uuid_term(k, hp.a1[0], hp.b1[0], hp.p1[0], hp.m1[0]);
+    ull_t h = (ull_t)k * (ull_t)hp.a1[0] + (ull_t)hp.b1[0];
     for (int i = 1; i < hp.ks; i++) {
       k = dok_key_elem(keys, hp.dtype, e * hp.ks + i);
       u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(k, hp.a[i], hp.b[i], hp.p[i], hp.m[i]));
-      h = (ll_t)((ull_t)h * (ull_t)dok_uuid_term(k, hp.a1[i], hp.b1[i], hp.p1[i], hp.m1[i]));
+      h *= (ull_t)k * (ull_t)hp.a1[i] + (ull_t)hp.b1[i];
     }
-    return KeyHash{dok_llabs(u), dok_llabs(h)};
+    return KeyHash{dok_llabs(u), (ll_t)h};
   }
   // set_key_permuted (closed_hashmap_impl_class.cu:144-150): storage column perm[i] <- key element i
   __device__ __forceinline__ void store_key(const DevHash &hp, ll_t e, char *dst_row) const {
@@ -183,15 +200,15 @@ struct SelKeys {
     offsets(e, off);
     ll_t k = s.ptr[0][off[0]];
     ll_t u = dok_uuid_term(k, hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
-    ll_t h = dok_uuid_term(k, hp.a1[0], hp.b1[0], hp.p1[0], hp.m1[0]);
+    ull_t h = (ull_t)k * (ull_t)hp.a1[0] + (ull_t)hp.b1[0];
 #pragma unroll
     for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
       if (d < s.ndim) {
         k = s.ptr[d][off[d]];
         u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(k, hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
-        h = (ll_t)((ull_t)h * (ull_t)dok_uuid_term(k, hp.a1[d], hp.b1[d], hp.p1[d], hp.m1[d]));
+        h *= (ull_t)k * (ull_t)hp.a1[d] + (ull_t)hp.b1[d];
       }
-    return KeyHash{dok_llabs(u), dok_llabs(h)};
+    return KeyHash{dok_llabs(u), (ll_t)h};
   }
   __device__ __forceinline__ void store_key(const DevHash &hp, ll_t e, char *dst_row) const {
     ll_t off[DOK_MAX_KEY_SIZE];
@@ -203,45 +220,208 @@ struct SelKeys {
 };
 
 // ---------------------------------------------------------------------------------------------------------
-// Bucket access
+// Slot access
 // ---------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ ll_t *dok_tag_ptr(const DevTable &t, ll_t slot) {
-  return (ll_t *)(t.buckets + slot * (ll_t)t.bb);
-}
+__device__ __forceinline__ char *dok_slot_ptr(const DevTable &t, ll_t slot) { return t.slots + slot * (ll_t)t.sb; }
+__device__ __forceinline__ ll_t *dok_tag_ptr(const DevTable &t, ll_t slot) { return (ll_t *)dok_slot_ptr(t, slot); }
 __device__ __forceinline__ ll_t dok_load_tag(const DevTable &t, ll_t slot) {
   return __ldcg(dok_tag_ptr(t, slot));   // L2 is the point of coherence for the CAS claims
 }
 __device__ __forceinline__ ll_t dok_cas_tag(const DevTable &t, ll_t slot, ll_t expect, ll_t desired) {
   return (ll_t)atomicCAS((ull_t *)dok_tag_ptr(t, slot), (ull_t)expect, (ull_t)desired);
 }
+__device__ __forceinline__ ll_t *dok_stamp_ptr(const DevTable &t, ll_t slot) {
+  return t.stamp_off >= 0 ? (ll_t *)(dok_slot_ptr(t, slot) + t.stamp_off) : t.stamp + slot;
+}
+__device__ __forceinline__ char *dok_value_ptr(const DevTable &t, ll_t slot) { return dok_slot_ptr(t, slot) + t.val_off; }
+__device__ __forceinline__ char *dok_key_row(const DevTable &t, ll_t slot) { return dok_slot_ptr(t, slot) + t.key_off; }
 
-// Lookup: returns the slot holding `uuid`, or -1 (ClosedHashmap::get / exists,
-// closed_hashmap_impl_class.cu:253-312).  The loop is bounded by n_buckets like the reference's.
-__device__ __forceinline__ ll_t dok_find(const DevTable &t, const KeyHash &kh, int *probes) {
-  const ll_t uuid = kh.uuid;
-  ll_t slot = dok_start_bucket(kh, t.nb, t.nb_magic);
-  for (ll_t i = 0; i < t.nb; i++) {
-    const ll_t tag = dok_load_tag(t, slot);
-    if (tag == uuid) { if (probes) *probes = (int)i + 1; return slot; }
-    if (tag == DOK_EMPTY) { if (probes) *probes = (int)i + 1; return -1; }
-    if (++slot == t.nb) slot = 0;
+// `nbytes` (1..8) of the little-endian word `w` to dst, with the widest stores the alignment `align` (a power
+// of two that divides both dst and nbytes' positions) allows
+__device__ __forceinline__ void dok_store_word(char *dst, ull_t w, int nbytes, int align) {
+  if (nbytes == 8 && align >= 8) { *(ull_t *)dst = w; return; }
+  if (align >= 4) {
+    *(unsigned *)dst = (unsigned)w;
+    if (nbytes > 4) *(unsigned *)(dst + 4) = (unsigned)(w >> 32);
+    return;
   }
-  if (probes) *probes = (int)t.nb;
-  return -1;
+  if (align >= 2) {
+    for (int i = 0; i < nbytes; i += 2) *(unsigned short *)(dst + i) = (unsigned short)(w >> (8 * i));
+    return;
+  }
+  for (int i = 0; i < nbytes; i++) dst[i] = (char)(w >> (8 * i));
+}
+
+// What a walk of one key's chain found.  found >= 0: the slot holding the uuid.  Otherwise `empty` is the first
+// empty slot of the chain (-1: the whole table was walked without meeting one) and `tomb` the first tombstone
+// met before it (-1: none) -- the two places ClosedHashmap::set may claim (closed_hashmap_impl_class.cu:368-427).
+struct Located { ll_t found, empty, tomb; };
+
+// Slot-by-slot walk by ONE lane: the reference's loop (closed_hashmap_impl_class.cu:280-312, 368-407) from this
+// library's start slot.  Used for slots wider than a line.
+__device__ __forceinline__ Located dok_locate_serial(const DevTable &t, const KeyHash &kh, int *probes) {
+  Located r{-1, -1, -1};
+  ll_t slot = dok_start_group(kh, t) * t.spg;
+  ll_t i = 0;
+  for (; i < t.n_slots; i++) {
+    const ll_t tag = dok_load_tag(t, slot);
+    if (tag == kh.uuid) { r.found = slot; i++; break; }
+    if (tag == DOK_EMPTY) { r.empty = slot; i++; break; }
+    if (tag == DOK_REMOVED && r.tomb < 0) r.tomb = slot;
+    if (++slot == t.n_slots) slot = 0;
+  }
+  if (probes) *probes = (int)i;
+  return r;
+}
+
+// No-op hit handler for walks that only need the slot.
+struct NoEmit {
+  template <int LW>
+  __device__ __forceinline__ void operator()(ll_t, int, const ull_t (&)[LW]) const {}
+};
+
+// LW 8-byte words of a line chunk with one load that allocates in L2 only (L2 is the point of coherence for the
+// CAS claims; the table is touched at random, so L1 lines would be dead on arrival)
+template <int LW>
+__device__ __forceinline__ void dok_load_words(const char *p, ull_t (&w)[LW]) {
+  if constexpr (LW == 4) {
+    asm volatile("ld.global.cg.v4.u64 {%0,%1,%2,%3}, [%4];" : "=l"(w[0]), "=l"(w[1]), "=l"(w[2]), "=l"(w[3]) : "l"(p));
+  } else if constexpr (LW == 2) {
+    const ulonglong2 v = __ldcg((const ulonglong2 *)p);
+    w[0] = v.x; w[1] = v.y;
+  } else {
+    w[0] = __ldcg((const ull_t *)p);
+  }
+}
+
+// The same walk for the 32 keys of a warp, one 128-byte group per request.  Lane i owns key i.  The four lanes of
+// a quad serve the quad's four keys in turn: each lane loads the first LW words of its 32 bytes of the key's
+// current group (one coalesced request for the line: 1 word = the tags only, 2 = tag and an 8-byte value, 4 =
+// everything), the quad ORs its match / empty / tombstone bits together, and the owner lane interprets them in
+// slot order.  The first groups of the quad's four keys are requested back to back before any is inspected; keys
+// whose chain runs into a further group (few below 90 % load) are finished in a loop.
+// On a hit, `emit(e_r, slot_in_group, words)` runs on all four lanes while they still hold the line: e_r is the
+// batch element of the key, words the calling lane's chunk.
+// Every lane of the warp must call this (inactive lanes pass active = false).  SB = slot bytes (32, 64, 128).
+template <int SB, int LW, class Emit>
+__device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyHash &kh, ll_t e, bool active,
+                                                   int *probes, const Emit &emit) {
+  constexpr int SPG = 128 / SB;
+  constexpr unsigned FULL = 0xffffffffu;
+  const unsigned lane = threadIdx.x & 31u, l = lane & 3u, base = lane & ~3u;
+  const bool has_tag = ((32u * l) % SB) == 0;       // does this lane's chunk start with a slot's tag?
+  const unsigned my_slot = (32u * l) / SB;          // slot (within the group) the chunk belongs to
+  Located res{-1, -1, -1};
+  ll_t group = active ? dok_start_group(kh, t) : -1;     // -1: nothing (left) to do for this lane's key
+  ll_t walked = 0;
+
+  // one step for the key owned by lane r of the quad: g_r is its current group (or -1), w this lane's chunk of it
+  auto resolve = [&](const ull_t (&w)[LW], ll_t g_r, ll_t uuid_r, ll_t e_r, unsigned r) {
+    const ll_t tag = (has_tag && g_r >= 0) ? (ll_t)w[0] : DOK_BLOCKED;
+    unsigned bits = ((unsigned)(tag == uuid_r) | ((unsigned)(tag == DOK_EMPTY) << 4) | ((unsigned)(tag == DOK_REMOVED) << 8)) << my_slot;
+    bits |= __shfl_xor_sync(FULL, bits, 1);
+    bits |= __shfl_xor_sync(FULL, bits, 2);
+    const unsigned m = bits & 0xfu, em = (bits >> 4) & 0xfu, tb = (bits >> 8) & 0xfu;
+    const int pos = (m | em) ? __ffs(m | em) - 1 : -1;
+    const bool hit = pos >= 0 && ((m >> pos) & 1u);
+    if (hit) emit(e_r, pos, w);
+    if (l == r && group >= 0) {
+      const ll_t first_slot = group * SPG;
+      walked++;
+      if (pos >= 0) {
+        const unsigned before = tb & ((1u << pos) - 1u);
+        if (hit) res.found = first_slot + pos;
+        else {
+          res.empty = first_slot + pos;
+          if (res.tomb < 0 && before) res.tomb = first_slot + __ffs(before) - 1;
+        }
+        group = -1;
+      } else {
+        if (res.tomb < 0 && tb) res.tomb = first_slot + __ffs(tb) - 1;
+        if (++group == t.n_groups) group = 0;
+        if (walked == t.n_groups) group = -1;           // every group inspected: no empty slot anywhere
+      }
+    }
+  };
+
+  ull_t w[4][LW];
+  ll_t g[4];
+#pragma unroll
+  for (unsigned r = 0; r < 4; r++) {
+    g[r] = __shfl_sync(FULL, group, base + r);
+    if (g[r] >= 0) dok_load_words<LW>(t.slots + g[r] * 128 + 32 * l, w[r]);
+  }
+#pragma unroll
+  for (unsigned r = 0; r < 4; r++)
+    resolve(w[r], g[r], __shfl_sync(FULL, kh.uuid, base + r), __shfl_sync(FULL, e, base + r), r);
+
+  for (;;) {
+    const unsigned pend = __ballot_sync(FULL, group >= 0);
+    if (pend == 0) break;
+    const unsigned quad = (pend >> base) & 0xfu;
+    const unsigned r = quad ? (unsigned)(__ffs(quad) - 1) : 0u;     // the quad's lowest unfinished key
+    const ll_t g_r = quad ? __shfl_sync(FULL, group, base + r) : (__shfl_sync(FULL, group, base + r), -1);
+    const ll_t uuid_r = __shfl_sync(FULL, kh.uuid, base + r);
+    const ll_t e_r = __shfl_sync(FULL, e, base + r);
+    ull_t wl[LW];
+    if (g_r >= 0) dok_load_words<LW>(t.slots + g_r * 128 + 32 * l, wl);
+    resolve(wl, g_r, uuid_r, e_r, r);
+  }
+  if (probes) *probes = (int)walked;
+  return res;
+}
+
+// Hit handler of `get`: the lanes of the quad write the value straight from the registers that hold the line, so
+// a hit needs no second access to the table.  LW = 2 serves 32-byte slots whose value is one word behind the tag.
+template <int SB, int LW>
+struct EmitValue {
+  const DevTable &t;
+  char *out_values;
+  __device__ __forceinline__ void operator()(ll_t e_r, int pos, const ull_t (&w)[LW]) const {
+    const int l = (int)(threadIdx.x & 3u);
+    char *dst = out_values + e_r * (ll_t)t.vb;
+    if constexpr (SB == 32 && LW == 2) {
+      if (l == pos) {
+        if (t.vb == 8) *(ull_t *)dst = w[1];
+        else dok_store_word(dst, w[1], t.vb, (t.vb & -t.vb));
+      }
+    } else {
+      const int start = pos * SB + 8 - 32 * l;             // offset of the value relative to this lane's chunk
+      const int align = (t.vb & -t.vb) < 8 ? (t.vb & -t.vb) : 8;
+#pragma unroll
+      for (int j = 0; j < LW; j++) {
+        const int rel = 8 * j - start;
+        if (rel >= 0 && rel < t.vb) dok_store_word(dst + rel, w[j], t.vb - rel < 8 ? t.vb - rel : 8, align);
+      }
+    }
+  }
+};
+
+// SB == 0 selects the serial walk (slots wider than one line); emit is not called there.
+template <int SB, int LW, class Emit>
+__device__ __forceinline__ Located dok_locate(const DevTable &t, const KeyHash &kh, ll_t e, bool active, int *probes,
+                                              const Emit &emit) {
+  if constexpr (SB == 0) {
+    if (active) return dok_locate_serial(t, kh, probes);
+    if (probes) *probes = 0;
+    return Located{-1, -1, -1};
+  } else {
+    return dok_locate_quad<SB, LW>(t, kh, e, active, probes, emit);
+  }
 }
 
 enum { DOK_OUT_FOUND = 0, DOK_OUT_CLAIMED_EMPTY = 1, DOK_OUT_REUSED = 2, DOK_OUT_FAILED = 3 };
 
-// Insert-or-find (ClosedHashmap::set, closed_hashmap_impl_class.cu:368-427, without the row stores).
-// Phase 1 walks the chain: a matching tag is a hit; the first tombstone is remembered; at the first empty
-// tag the slot is claimed by CAS unless a tombstone was seen.  Phase 2 starts at the remembered tombstone and
-// tries tombstone->uuid, then empty->uuid, slot by slot.  Unlike the reference, a CAS that loses to the SAME
-// uuid joins that slot instead of walking on, so that equal uuids of one batch always meet in one slot.
-__device__ __forceinline__ ll_t dok_find_or_claim(const DevTable &t, const KeyHash &kh, int *outcome) {
+// Insert-or-find by one lane, slot by slot (ClosedHashmap::set, closed_hashmap_impl_class.cu:368-427, without
+// the row stores).  Phase 1 walks the chain: a matching tag is a hit; the first tombstone is remembered; at the
+// first empty tag the slot is claimed by CAS unless a tombstone was seen.  Phase 2 starts at the remembered
+// tombstone and tries tombstone->uuid, then empty->uuid, slot by slot.  Unlike the reference, a CAS that loses
+// to the SAME uuid joins that slot instead of walking on, so equal uuids of one batch always meet in one slot.
+static __device__ __noinline__ ll_t dok_find_or_claim_serial(const DevTable &t, const KeyHash &kh, int *outcome) {
   const ll_t uuid = kh.uuid;
-  ll_t slot = dok_start_bucket(kh, t.nb, t.nb_magic);
+  ll_t slot = dok_start_group(kh, t) * t.spg;
   ll_t first_removed = -1;
-  for (ll_t i = 0; i < t.nb; i++) {
+  for (ll_t i = 0; i < t.n_slots; i++) {
     ll_t tag = dok_load_tag(t, slot);
     if (tag == DOK_EMPTY && first_removed < 0) {
       tag = dok_cas_tag(t, slot, DOK_EMPTY, uuid);
@@ -250,11 +430,11 @@ __device__ __forceinline__ ll_t dok_find_or_claim(const DevTable &t, const KeyHa
     if (tag == uuid) { *outcome = DOK_OUT_FOUND; return slot; }
     if (tag == DOK_EMPTY) break;                       // a tombstone was seen earlier: go reuse it
     if (tag == DOK_REMOVED && first_removed < 0) first_removed = slot;
-    if (++slot == t.nb) slot = 0;
+    if (++slot == t.n_slots) slot = 0;
   }
   if (first_removed >= 0) {
     slot = first_removed;
-    for (ll_t i = 0; i < t.nb; i++) {
+    for (ll_t i = 0; i < t.n_slots; i++) {
       ll_t old = dok_cas_tag(t, slot, DOK_REMOVED, uuid);
       if (old == DOK_REMOVED) { *outcome = DOK_OUT_REUSED; return slot; }
       if (old == DOK_EMPTY) {
@@ -262,16 +442,42 @@ __device__ __forceinline__ ll_t dok_find_or_claim(const DevTable &t, const KeyHa
         if (old == DOK_EMPTY) { *outcome = DOK_OUT_CLAIMED_EMPTY; return slot; }
       }
       if (old == uuid) { *outcome = DOK_OUT_FOUND; return slot; }
-      if (++slot == t.nb) slot = 0;
+      if (++slot == t.n_slots) slot = 0;
     }
   }
   *outcome = DOK_OUT_FAILED;
   return -1;
 }
 
-// value row (vb bytes at `src`, alignment of the widest power of two dividing vb, capped at 8) -> bucket
+// Insert-or-find for the 32 keys of a warp: one cooperative walk tells every owner lane where its uuid is or
+// where the chain offers a place (first tombstone, else first empty slot); the owner claims that place with one
+// CAS.  Losing the CAS to the same uuid means a twin row of the batch claimed it: join.  Losing it to another
+// uuid is rare; that lane redoes the whole operation with the serial walk.  Every lane of the warp must call.
+template <int SB>
+__device__ __forceinline__ ll_t dok_find_or_claim(const DevTable &t, const KeyHash &kh, bool active, int *outcome) {
+  const Located loc = dok_locate<SB, 1>(t, kh, 0, active, nullptr, NoEmit());   // the tags are all a claim needs
+  if (!active) return -1;
+  if (loc.found >= 0) { *outcome = DOK_OUT_FOUND; return loc.found; }
+  if (loc.tomb >= 0) {
+    const ll_t old = dok_cas_tag(t, loc.tomb, DOK_REMOVED, kh.uuid);
+    if (old == DOK_REMOVED) { *outcome = DOK_OUT_REUSED; return loc.tomb; }
+    if (old == kh.uuid) { *outcome = DOK_OUT_FOUND; return loc.tomb; }
+  } else if (loc.empty >= 0) {
+    const ll_t old = dok_cas_tag(t, loc.empty, DOK_EMPTY, kh.uuid);
+    if (old == DOK_EMPTY) { *outcome = DOK_OUT_CLAIMED_EMPTY; return loc.empty; }
+    if (old == kh.uuid) { *outcome = DOK_OUT_FOUND; return loc.empty; }
+  } else {
+    *outcome = DOK_OUT_FAILED;       // no match, no tombstone, no empty slot: the table is full
+    return -1;
+  }
+  return dok_find_or_claim_serial(t, kh, outcome);
+}
+
+// value row (vb bytes at `src`, alignment of the widest power of two dividing vb, capped at 8) -> slot
 __device__ __forceinline__ void dok_store_value(const DevTable &t, ll_t slot, const char *src) {
-  ull_t *dst = (ull_t *)(t.buckets + slot * (ll_t)t.bb + 8);
+  ull_t *dst = (ull_t *)dok_value_ptr(t, slot);
+  if (t.vb == 8) { *dst = *(const ull_t *)src; return; }
+  if (t.vb == 4) { *(unsigned *)dst = *(const unsigned *)src; return; }
   if ((t.vb & 7) == 0) {
     for (int w = 0; w < t.vwords; w++) dst[w] = ((const ull_t *)src)[w];
   } else if ((t.vb & 3) == 0) {
@@ -286,17 +492,19 @@ __device__ __forceinline__ void dok_store_value(const DevTable &t, ll_t slot, co
   }
 }
 
-// bucket -> value row
+// slot -> value row
 __device__ __forceinline__ void dok_load_value(const DevTable &t, ll_t slot, char *dst) {
-  const ull_t *src = (const ull_t *)(t.buckets + slot * (ll_t)t.bb + 8);
+  const ull_t *src = (const ull_t *)dok_value_ptr(t, slot);
+  if (t.vb == 8) { *(ull_t *)dst = __ldcg(src); return; }
+  if (t.vb == 4) { *(unsigned *)dst = __ldcg((const unsigned *)src); return; }
   if ((t.vb & 7) == 0) {
-    for (int w = 0; w < t.vwords; w++) ((ull_t *)dst)[w] = src[w];
+    for (int w = 0; w < t.vwords; w++) ((ull_t *)dst)[w] = __ldcg(src + w);
   } else if ((t.vb & 3) == 0) {
-    for (int w = 0; w < (t.vb >> 2); w++) ((unsigned *)dst)[w] = ((const unsigned *)src)[w];
+    for (int w = 0; w < (t.vb >> 2); w++) ((unsigned *)dst)[w] = __ldcg((const unsigned *)src + w);
   } else if ((t.vb & 1) == 0) {
-    for (int w = 0; w < (t.vb >> 1); w++) ((unsigned short *)dst)[w] = ((const unsigned short *)src)[w];
+    for (int w = 0; w < (t.vb >> 1); w++) ((unsigned short *)dst)[w] = __ldcg((const unsigned short *)src + w);
   } else {
-    for (int w = 0; w < t.vb; w++) dst[w] = ((const char *)src)[w];
+    for (int w = 0; w < t.vb; w++) dst[w] = __ldcg((const char *)src + w);
   }
 }
 
@@ -304,6 +512,8 @@ struct Fallback { ull_t w[DOK_MAX_VALUE_BYTES / 8]; };   // miss fill, passed by
 
 __device__ __forceinline__ void dok_store_fallback(const DevTable &t, const Fallback &fb, char *dst) {
   const char *src = (const char *)fb.w;
+  if (t.vb == 8) { *(ull_t *)dst = fb.w[0]; return; }
+  if (t.vb == 4) { *(unsigned *)dst = (unsigned)fb.w[0]; return; }
   if ((t.vb & 7) == 0) {
     for (int w = 0; w < t.vwords; w++) ((ull_t *)dst)[w] = fb.w[w];
   } else if ((t.vb & 3) == 0) {
@@ -315,7 +525,8 @@ __device__ __forceinline__ void dok_store_fallback(const DevTable &t, const Fall
   }
 }
 
-// warp sum + one atomicAdd per warp (replaces warp_sum + atomicAdd of sparse_dok_tensor_impl.cu:52-55)
+// warp sum + one atomicAdd per warp (replaces warp_sum + atomicAdd of sparse_dok_tensor_impl.cu:52-55).
+// Every lane of the warp must call it.
 __device__ __forceinline__ void dok_warp_add(ll_t *counter, int v) {
   if (counter == nullptr) return;
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

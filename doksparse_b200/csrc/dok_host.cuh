@@ -5,6 +5,7 @@
 #include "dok_device.cuh"
 
 #define DOK_MAX_BATCH 0xffffffffLL   // row indices are packed into 32 bits of the set stamp
+#define DOK_MAX_EPOCH 0x3fffffffLL   // 30 bits of the stamp above the row index and the conflict bit
 
 // contiguous value rows [n, value_bytes]
 struct RowValues {
@@ -61,35 +62,56 @@ inline bool dok_make_hash(const dok_hash_params *hp, DevHash *out) {
     const long long prime = hp->prime2[c];
     const unsigned long long p = prime < 0 ? (0ULL - (unsigned long long)prime) : (unsigned long long)prime;
     if (p < 2) return false;
-    const long long prime1 = hp->prime1[c];
-    const unsigned long long p1 = prime1 < 0 ? (0ULL - (unsigned long long)prime1) : (unsigned long long)prime1;
-    if (p1 < 2) return false;
     out->a[i] = hp->alpha2[c];
     out->b[i] = hp->beta2[c];
     out->p[i] = p;
     out->m[i] = (unsigned long long)((((unsigned __int128)1) << 64) / p);
-    out->a1[i] = hp->alpha1[c];
+    out->a1[i] = hp->alpha1[c] | 1;     // odd: the linear term is then injective in the key element
     out->b1[i] = hp->beta1[c];
-    out->p1[i] = p1;
-    out->m1[i] = (unsigned long long)((((unsigned __int128)1) << 64) / p1);
     out->perm[i] = c;
   }
   return true;
 }
 
-inline bool dok_make_table(const dok_table *t, const DevHash *dh, DevTable *out) {
-  if (!t || !t->buckets || t->n_buckets < 1) return false;
-  if (t->value_bytes < 1 || t->value_bytes > DOK_MAX_VALUE_BYTES) return false;
-  const int bb = (8 + t->value_bytes + 15) / 16 * 16;
-  if (t->bucket_bytes != bb) return false;
-  out->buckets = (char *)t->buckets;
-  out->keys = (char *)t->keys;
+// Slot geometry for (value_bytes, key_bytes): {tag 8 | value, padded to 8 | key row, padded to 8 | stamp 8 if it
+// fits without growing the slot}, padded to 32, 64 or 128 bytes (4, 2 or 1 slots per 128-byte line); wider rows
+// take a whole number of lines and always carry their stamp.
+struct DokLayout { int sb, spg, val_off, key_off, stamp_off; };
+
+inline bool dok_layout(int value_bytes, int key_bytes, DokLayout *out) {
+  if (value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES || key_bytes < 1 || key_bytes > 8 * DOK_MAX_KEY_SIZE) return false;
+  const int key_off = 8 + (value_bytes + 7) / 8 * 8;
+  const int need = key_off + (key_bytes + 7) / 8 * 8;      // without the stamp
+  int sb;
+  if (need <= 128) { sb = 32; while (sb < need) sb *= 2; }
+  else sb = (need + 8 + 127) / 128 * 128;
+  out->sb = sb;
+  out->spg = sb <= 128 ? 128 / sb : 1;
+  out->val_off = 8;
+  out->key_off = key_off;
+  out->stamp_off = need + 8 <= sb ? need : -1;
+  return true;
+}
+
+inline bool dok_make_table(const dok_table *t, DevTable *out) {
+  if (!t || !t->slots || t->n_buckets < 1) return false;
+  DokLayout lay;
+  if (!dok_layout(t->value_bytes, t->key_bytes, &lay) || t->slot_bytes != lay.sb) return false;
+  out->slots = (char *)t->slots;
   out->stamp = (ll_t *)t->stamp;
   out->nb = t->n_buckets;
-  out->nb_magic = t->n_buckets > 1 ? (unsigned long long)((((unsigned __int128)1) << 64) / (unsigned long long)t->n_buckets) : 0ULL;
-  out->bb = bb;
+  out->n_groups = (t->n_buckets + lay.spg - 1) / lay.spg;
+  out->n_slots = out->n_groups * lay.spg;
+  out->sb = lay.sb;
+  out->spg = lay.spg;
   out->vb = t->value_bytes;
-  out->kb = dh ? dh->ks * dh->elem_bytes : 0;
+  out->kb = t->key_bytes;
+  out->val_off = lay.val_off;
+  out->key_off = lay.key_off;
+  out->stamp_off = lay.stamp_off;
   out->vwords = (t->value_bytes + 7) / 8;
   return true;
 }
+
+// true when a general set can run on this table: the stamps are in the slots or the caller supplied the array
+inline bool dok_has_stamps(const DevTable &t) { return t.stamp_off >= 0 || t.stamp != nullptr; }

@@ -1,80 +1,34 @@
 // Kernel templates of the closed-hashing map: batched get / set / remove / exists / count-new and the
-// compaction of live slots.  They are templated on the key source (contiguous key rows, or index tensors of a
-// DOK selector) so that the map entry points (map_api.cu) and the fused DOK entry points (dok_api.cu) share them.
-// One CUDA thread handles one batch element, as in the reference kernels
-// (sparse_dok/components/cuda/closed_hashmap_impl.cu), but each hit costs one bucket row (tag + value in the
-// same 32-byte sector), misses write the fallback from the kernel, and counters are accumulated on the device
-// so that the host never has to synchronise.
+// compaction of live slots.  They are templated on the slot width SB (32, 64, 128 bytes: quad-cooperative walk,
+// one 128-byte group per request; 0: slots wider than a line, serial walk) and on the key source (contiguous key
+// rows, or the index tensors of a DOK selector), so that the map entry points (map_api.cu) and the fused DOK
+// entry points (dok_api.cu) share them.  One CUDA thread owns one batch element, as in the reference kernels
+// (sparse_dok/components/cuda/closed_hashmap_impl.cu); misses write the fallback from the kernel, and counters
+// are accumulated on the device so that the host never has to synchronise.
+//
+// No thread of a warp returns early: the cooperative walk needs all 32 lanes.
 #pragma once
 #include "dok_host.cuh"
 
 // ---------------------------------------------------------------------------------------------------------
 // get
 // ---------------------------------------------------------------------------------------------------------
-
-// 16-byte load that allocates in L2 only: the table is touched at random, L1 lines would be dead on arrival.
-__device__ __forceinline__ ulonglong2 dok_ld16(const char *p) {
-  return __ldcg((const ulonglong2 *)p);
-}
-
-// Writes `vb` bytes of a value held in the registers w[0..NW) to an output row.
-template <int NW>
-__device__ __forceinline__ void dok_store_out(char *dst, const ull_t (&w)[NW], int vb) {
-  if ((vb & 7) == 0) {
-#pragma unroll
-    for (int i = 0; i < NW; i++) if (i * 8 < vb) ((ull_t *)dst)[i] = w[i];
-  } else if ((vb & 3) == 0) {
-#pragma unroll
-    for (int i = 0; i < NW * 2; i++) if (i * 4 < vb) ((unsigned *)dst)[i] = (unsigned)(w[i >> 1] >> ((i & 1) * 32));
-  } else if ((vb & 1) == 0) {
-#pragma unroll
-    for (int i = 0; i < NW * 4; i++) if (i * 2 < vb) ((unsigned short *)dst)[i] = (unsigned short)(w[i >> 2] >> ((i & 3) * 16));
-  } else {
-#pragma unroll
-    for (int i = 0; i < NW * 8; i++) if (i < vb) dst[i] = (char)(w[i >> 3] >> ((i & 7) * 8));
-  }
-}
-
-// UNITS = bucket_bytes / 16 for 1 and 2 (the value then lives in registers after one or two 16-byte loads of
-// the probed row); UNITS = 0 is the generic path for wider rows.
-template <int UNITS, class Keys>
+template <int SB, int LW, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
                                                  uint8_t *__restrict__ out_found, Fallback fb, ll_t *counters,
                                                  int count_probes) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
-  int hit = 0, probes = 0;
-  if (e < keys.count()) {
-    const KeyHash kh = keys.hash(hp, e);
-    const ll_t uuid = kh.uuid;
+  const bool active = e < keys.count();
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
+  int probes = 0;
+  // on a hit the quad writes the value from the registers that hold the line
+  const Located loc = dok_locate<SB, LW>(t, kh, e, active, &probes, EmitValue<(SB == 0 ? 32 : SB), LW>{t, out_values});
+  const int hit = active && loc.found >= 0;
+  if (active) {
     char *dst = out_values + e * (ll_t)t.vb;
-    if (UNITS == 1 || UNITS == 2) {
-      constexpr int NW = UNITS == 1 ? 1 : 3;
-      ull_t w[NW];
-      ll_t slot = dok_start_bucket(kh, t.nb, t.nb_magic);
-      for (ll_t i = 0; i < t.nb; i++) {
-        const char *row = t.buckets + slot * (ll_t)(UNITS * 16);
-        const ulonglong2 u0 = dok_ld16(row);
-        ulonglong2 u1;
-        if (UNITS == 2) u1 = dok_ld16(row + 16);
-        probes++;
-        const ll_t tag = (ll_t)u0.x;
-        if (tag == uuid) {
-          w[0] = u0.y;
-          if (UNITS == 2) { w[1] = u1.x; w[2] = u1.y; }
-          hit = 1;
-          break;
-        }
-        if (tag == DOK_EMPTY) break;
-        if (++slot == t.nb) slot = 0;
-      }
-      if (hit) dok_store_out<NW>(dst, w, t.vb);
-      else dok_store_fallback(t, fb, dst);
-    } else {
-      const ll_t slot = dok_find(t, kh, &probes);
-      hit = slot >= 0;
-      if (hit) dok_load_value(t, slot, dst);
-      else dok_store_fallback(t, fb, dst);
-    }
+    if (SB == 0 && hit) dok_load_value(t, loc.found, dst);
+    if (!hit) dok_store_fallback(t, fb, dst);
     if (out_found) out_found[e] = (uint8_t)hit;
   }
   if (counters) {
@@ -82,6 +36,14 @@ __global__ void __launch_bounds__(DOK_TPB) k_get(DevTable t, DevHash hp, Keys ke
     if (count_probes) dok_warp_add(counters + DOK_CNT_PROBES, probes);
   }
 }
+
+#define DOK_DISPATCH_SB(t, CALL)                        \
+  switch ((t).sb) {                                     \
+    case 32: { constexpr int SB = 32; CALL; break; }    \
+    case 64: { constexpr int SB = 64; CALL; break; }    \
+    case 128: { constexpr int SB = 128; CALL; break; }  \
+    default: { constexpr int SB = 0; CALL; break; }     \
+  }
 
 template <class Keys>
 inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, void *out_values, uint8_t *out_found,
@@ -92,12 +54,11 @@ inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, vo
   memset(&fb, 0, sizeof(fb));
   if (fallback) memcpy(&fb, fallback, (size_t)t.vb);
   const unsigned grid = (unsigned)((n + DOK_TPB - 1) / DOK_TPB);
-  if (t.bb == 16)
-    k_get<1, Keys><<<grid, DOK_TPB, 0, st>>>(t, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes);
-  else if (t.bb == 32)
-    k_get<2, Keys><<<grid, DOK_TPB, 0, st>>>(t, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes);
+  if (t.sb == 32 && t.vb <= 8)      // tag and value fit the first 16 bytes of the slot: half the load width
+    k_get<32, 2, Keys><<<grid, DOK_TPB, 0, st>>>(t, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes);
   else
-    k_get<0, Keys><<<grid, DOK_TPB, 0, st>>>(t, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes);
+    DOK_DISPATCH_SB(t, (k_get<SB, 4, Keys><<<grid, DOK_TPB, 0, st>>>(t, hp, keys, (char *)out_values, out_found, fb,
+                                                                    (ll_t *)counters, count_probes)));
   return dok_check_launch();
 }
 
@@ -105,17 +66,26 @@ inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, vo
 // set
 // ---------------------------------------------------------------------------------------------------------
 
+// Key row and value row of batch element e into a claimed slot.
 template <class Keys, class Values>
+__device__ __forceinline__ void dok_write_row(const DevTable &t, const DevHash &hp, const Keys &keys, const Values &values,
+                                              ll_t e, ll_t slot) {
+  keys.store_key(hp, e, dok_key_row(t, slot));
+  dok_store_value(t, slot, values.row(t, e));
+}
+
+// One kernel, for batches whose rows have pairwise different uuids.
+template <int SB, class Keys, class Values>
 __global__ void __launch_bounds__(DOK_TPB) k_set_unique(DevTable t, DevHash hp, Keys keys, Values values,
                                                         uint8_t *__restrict__ out_stored, ll_t *counters) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
+  const bool active = e < keys.count();
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
   int outcome = -1;
-  if (e < keys.count()) {
-    const ll_t slot = dok_find_or_claim(t, keys.hash(hp, e), &outcome);
-    if (slot >= 0) {
-      keys.store_key(hp, e, t.keys + slot * (ll_t)t.kb);
-      dok_store_value(t, slot, values.row(t, e));
-    }
+  const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
+  if (active) {
+    if (slot >= 0) dok_write_row(t, hp, keys, values, e, slot);
     if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
   }
   if (counters) {
@@ -126,23 +96,40 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_unique(DevTable t, DevHash hp, 
   }
 }
 
-// First kernel of the general set: find or claim the slot, remember it, and raise the slot's stamp to
-// (epoch << 32 | row).  The stamp of a slot can only have been written with a smaller epoch before this
-// call, so after the kernel it names the LAST row of this batch that targets the slot.
-template <class Keys>
-__global__ void __launch_bounds__(DOK_TPB) k_set_claim(DevTable t, DevHash hp, Keys keys, ll_t *__restrict__ slot_out,
-                                                       ll_t epoch, ll_t *counters) {
+// Stamp word of a slot during a general set: (epoch << 33) | (row << 1) | conflict.  The epoch of a call is
+// larger than every epoch used on the table before, so an atomicMax leaves the LAST row of this batch that
+// targets the slot; the low bit records that more than one row of the batch did.
+__device__ __forceinline__ ll_t dok_stamp(ll_t epoch, ll_t row) { return (epoch << 33) | (row << 1); }
+
+// First kernel of the general set.  Find or claim the slot and raise its stamp.  The first row of the batch to
+// stamp a slot also writes its key and value there -- for a batch without equal uuids that is all there is to
+// do.  A later row that finds the slot already stamped in this epoch writes nothing, sets the conflict bit and
+// counts a duplicate (in slot_out[n], zeroed by the host before the launch); the second kernel then lets the
+// slot's last row rewrite it.
+template <int SB, class Keys, class Values>
+__global__ void __launch_bounds__(DOK_TPB) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
+                                                       ll_t *__restrict__ slot_out, ll_t epoch,
+                                                       uint8_t *__restrict__ out_stored, ll_t *counters) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
+  const bool active = e < keys.count();
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
   int outcome = -1, dup = 0;
-  if (e < keys.count()) {
-    const ll_t slot = dok_find_or_claim(t, keys.hash(hp, e), &outcome);
+  const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
+  if (active) {
     slot_out[e] = slot;
     if (slot >= 0) {
-      const ll_t mine = (epoch << 32) | e;
-      const ll_t old = (ll_t)atomicMax((ll_t *)&t.stamp[slot], mine);
-      dup = (old >> 32) == epoch;   // another row of this batch already stamped the slot
+      ll_t *stamp = dok_stamp_ptr(t, slot);
+      const ll_t old = (ll_t)atomicMax(stamp, dok_stamp(epoch, e));
+      if ((old >> 33) != epoch) dok_write_row(t, hp, keys, values, e, slot);
+      else {
+        atomicOr((ull_t *)stamp, 1ULL);
+        dup = 1;
+      }
     }
+    if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
   }
+  dok_warp_add(slot_out + keys.count(), dup);
   if (counters) {
     dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
     dok_warp_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
@@ -152,20 +139,19 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_claim(DevTable t, DevHash hp, K
   }
 }
 
-// Second kernel: the row whose index equals the slot's stamp writes key and value; every other row of the
-// batch that targeted the slot lost to a later duplicate.  One writer per slot: rows cannot tear.
+// Second kernel: does nothing unless the first one counted duplicates.  Then the row that owns a conflicted
+// slot's stamp (the last row of the batch for that slot) rewrites key and value: one writer per slot, after
+// every first-kernel write has completed, so rows cannot tear and the last row wins.
 template <class Keys, class Values>
-__global__ void __launch_bounds__(DOK_TPB) k_set_write(DevTable t, DevHash hp, Keys keys, Values values,
-                                                       const ll_t *__restrict__ slot_in, ll_t epoch,
-                                                       uint8_t *__restrict__ out_stored) {
+__global__ void __launch_bounds__(DOK_TPB) k_set_resolve(DevTable t, DevHash hp, Keys keys, Values values,
+                                                         const ll_t *__restrict__ slot_in, ll_t epoch) {
+  if (slot_in[keys.count()] == 0) return;        // the first kernel met no duplicate: every row is already in place
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   if (e >= keys.count()) return;
   const ll_t slot = slot_in[e];
-  if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
   if (slot < 0) return;
-  if (__ldcg(&t.stamp[slot]) != ((epoch << 32) | e)) return;
-  keys.store_key(hp, e, t.keys + slot * (ll_t)t.kb);
-  dok_store_value(t, slot, values.row(t, e));
+  if (__ldcg(dok_stamp_ptr(t, slot)) != (dok_stamp(epoch, e) | 1)) return;
+  dok_write_row(t, hp, keys, values, e, slot);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -174,18 +160,17 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_write(DevTable t, DevHash hp, K
 
 // REMOVE = 1: the tag is swapped to the tombstone by CAS so that equal uuids in one batch report exactly once
 // (ClosedHashmap::remove, closed_hashmap_impl_class.cu:459-484, stores it non-atomically).
-template <int REMOVE, class Keys>
+template <int SB, int REMOVE, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys keys, uint8_t *__restrict__ out_flags,
                                                   ll_t *counters) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
-  int hit = 0;
-  if (e < keys.count()) {
-    const KeyHash kh = keys.hash(hp, e);
-    const ll_t slot = dok_find(t, kh, nullptr);
-    hit = slot >= 0;
-    if (REMOVE && hit) hit = dok_cas_tag(t, slot, kh.uuid, DOK_REMOVED) == kh.uuid;
-    if (out_flags) out_flags[e] = (uint8_t)hit;
-  }
+  const bool active = e < keys.count();
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
+  const Located loc = dok_locate<SB, 1>(t, kh, e, active, nullptr, NoEmit());
+  int hit = active && loc.found >= 0;
+  if (REMOVE && hit) hit = dok_cas_tag(t, loc.found, kh.uuid, DOK_REMOVED) == kh.uuid;
+  if (active && out_flags) out_flags[e] = (uint8_t)hit;
   dok_warp_add(counters ? counters + DOK_CNT_HITS : nullptr, hit);
 }
 
@@ -195,25 +180,26 @@ static __global__ void k_fill_i64(ll_t *p, ll_t n, ll_t v) {
 
 // Rows absent from the table insert their uuid into a scratch tag set; the number of successful claims is the
 // number of distinct absent uuids.
-template <class Keys>
+template <int SB, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, Keys keys, ll_t *__restrict__ scratch,
                                                        ll_t scratch_slots, ll_t *counters) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
+  const bool active = e < keys.count();
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
+  const Located loc = dok_locate<SB, 1>(t, kh, e, active, nullptr, NoEmit());
   int claimed = 0;
-  if (e < keys.count()) {
-    const KeyHash kh = keys.hash(hp, e);
+  if (active && loc.found < 0) {
     const ll_t uuid = kh.uuid;
-    if (dok_find(t, kh, nullptr) < 0) {
-      ll_t slot = (ll_t)__umul64hi(dok_mix64((ull_t)uuid ^ 0x5851f42d4c957f2dULL), (ull_t)scratch_slots);
-      for (ll_t i = 0; i < scratch_slots; i++) {
-        ll_t tag = __ldcg(&scratch[slot]);
-        if (tag == DOK_EMPTY) {
-          tag = (ll_t)atomicCAS((ull_t *)&scratch[slot], (ull_t)DOK_EMPTY, (ull_t)uuid);
-          if (tag == DOK_EMPTY) { claimed = 1; break; }
-        }
-        if (tag == uuid) break;
-        if (++slot == scratch_slots) slot = 0;
+    ll_t slot = (ll_t)__umul64hi(dok_mix64((ull_t)uuid ^ 0x5851f42d4c957f2dULL), (ull_t)scratch_slots);
+    for (ll_t i = 0; i < scratch_slots; i++) {
+      ll_t tag = __ldcg(&scratch[slot]);
+      if (tag == DOK_EMPTY) {
+        tag = (ll_t)atomicCAS((ull_t *)&scratch[slot], (ull_t)DOK_EMPTY, (ull_t)uuid);
+        if (tag == DOK_EMPTY) { claimed = 1; break; }
       }
+      if (tag == uuid) break;
+      if (++slot == scratch_slots) slot = 0;
     }
   }
   dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, claimed);
@@ -225,19 +211,19 @@ __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, K
 
 static __global__ void k_init(DevTable t) {
   const ll_t stride = (ll_t)gridDim.x * blockDim.x;
-  for (ll_t i = (ll_t)blockIdx.x * blockDim.x + threadIdx.x; i < t.nb; i += stride) {
-    *dok_tag_ptr(t, i) = DOK_EMPTY;
-    if (t.stamp) t.stamp[i] = 0;
+  for (ll_t i = (ll_t)blockIdx.x * blockDim.x + threadIdx.x; i < t.n_slots; i += stride) {
+    *dok_tag_ptr(t, i) = i < t.nb ? DOK_EMPTY : DOK_BLOCKED;
+    if (t.stamp_off >= 0 || t.stamp) *dok_stamp_ptr(t, i) = 0;
   }
 }
 
 template <class Keys>
-__global__ void k_uuid(DevTable t, DevHash hp, Keys keys, ll_t *uuid_out, ll_t *bucket_out) {
+__global__ void k_uuid(DevTable t, DevHash hp, Keys keys, ll_t *uuid_out, ll_t *slot_out) {
   const ll_t e = (ll_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= keys.count()) return;
   const KeyHash kh = keys.hash(hp, e);
   if (uuid_out) uuid_out[e] = kh.uuid;
-  if (bucket_out) bucket_out[e] = t.nb > 0 ? dok_start_bucket(kh, t.nb, t.nb_magic) : 0;
+  if (slot_out) slot_out[e] = t.n_groups > 0 ? dok_start_group(kh, t) * t.spg : 0;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -246,7 +232,7 @@ __global__ void k_uuid(DevTable t, DevHash hp, Keys keys, ll_t *uuid_out, ll_t *
 #define DOK_COMPACT_ROUNDS 8
 #define DOK_COMPACT_TILE (DOK_TPB * DOK_COMPACT_ROUNDS)
 
-__device__ __forceinline__ bool dok_is_live(ll_t tag) { return tag != DOK_EMPTY && tag != DOK_REMOVED; }
+__device__ __forceinline__ bool dok_is_live(ll_t tag) { return tag != DOK_EMPTY && tag != DOK_REMOVED && tag != DOK_BLOCKED; }
 
 static __global__ void __launch_bounds__(DOK_TPB) k_compact_count(DevTable t, ll_t *tile_counts) {
   __shared__ int warp_sums[DOK_TPB / 32];
@@ -314,7 +300,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_compact_scatter(DevTable t, 
       if (values_out) dok_load_value(t, slot, values_out + pos * (ll_t)t.vb);
       if (keys_out) {
         // keys(): column i of the output is storage column key_perm[i] (cuda_closed_hashmap.py:165)
-        const char *src = t.keys + slot * (ll_t)t.kb;
+        const char *src = dok_key_row(t, slot);
         for (int i = 0; i < hp.ks; i++) {
           const ll_t o = keys_transposed ? ((ll_t)i * count + pos) : (pos * hp.ks + i);
           switch (hp.elem_bytes) {

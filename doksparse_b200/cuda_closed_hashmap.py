@@ -10,9 +10,10 @@ What is kept from the reference
     (:363-366), `remove` dedups with `unique(dim=0)` and returns flags for the sorted unique rows
     (:438-454), `set` returns None (:384), RuntimeError("store something first") (:391-392).
 What is different (the slot layout is not part of the contract)
-  * `_uuid` and `_values` are strided views of one interleaved bucket array; `_keys` is separate;
-  * the start bucket comes from a mixer of the uuid, not from prime1/alpha1/beta1 (which are still
-    drawn, to keep the random stream aligned with the reference);
+  * `_uuid`, `_values` and `_keys` are strided views (reference shapes) of ONE interleaved slot array: tag, value
+    and key row of a slot share a 128-byte line, the unit that a random access costs on B200;
+  * the start slot comes from a mixer of the uuid and of alpha1/beta1, not from the reference's first hash
+    (prime1 is still drawn, to keep the random stream aligned with the reference);
   * duplicates inside one `set` batch resolve deterministically to the last row.
 """
 import ctypes
@@ -49,9 +50,10 @@ class CudaClosedHashmap:
             raise L.DokError("CudaClosedHashmap needs a CUDA device: there is no CPU path")
         L.lib()  # fail loudly now if the extension is missing
         # before the first `set` only the tags exist (cuda_closed_hashmap.py:40)
-        self._buckets = None
+        self._slots = None           # uint8 storage of the slot array
+        self._key_shape = None
+        self._key_dtype = None
         self._uuid_only = torch.full((self._n_buckets,), self._empty_marker, device=self.device, dtype=torch.long)
-        self._key_store = None
         # state that shallow clones (views) must see together: the duplicate-resolution stamps with their epoch,
         # and the host-side upper bound of n_elements that lets `set` skip a device synchronisation
         self._shared = {"stamp": None, "epoch": 0, "bound": 0}
@@ -77,9 +79,9 @@ class CudaClosedHashmap:
 
     # ------------------------------------------------------------------ parameters (lazy, reference order)
     def _current_key_size(self):
-        assert self._key_store is not None or self._key_size is not None
-        if self._key_store is not None:
-            return int(np.prod(self._key_store.shape[1:]))
+        assert self._slots is not None or self._key_size is not None
+        if self._slots is not None:
+            return int(np.prod(self._key_shape))
         return int(self._key_size)
 
     def _as_param(self, values):
@@ -129,7 +131,7 @@ class CudaClosedHashmap:
     @property
     def key_perm(self):
         if self._key_perm is None:
-            assert self._key_store is not None
+            assert self._slots is not None
             self._key_perm = torch.arange(int(np.prod(self.key_shape)), device=self.device)
         else:
             assert self._key_perm.shape[0] == np.prod(self.key_shape)
@@ -158,11 +160,14 @@ class CudaClosedHashmap:
             raise L.DokError(f"keys may have 1..{L.MAX_KEY_SIZE} elements, got {key_size}")
         if not (1 <= value_bytes <= L.MAX_VALUE_BYTES):
             raise L.DokError(f"value rows may have 1..{L.MAX_VALUE_BYTES} bytes, got {value_bytes}")
-        bb = L.lib().dok_bucket_bytes(value_bytes)
-        self._bucket_bytes, self._value_bytes = bb, value_bytes
+        key_bytes = key_size * torch.empty((), dtype=key_dtype).element_size()
+        lay = L.LayoutInfo()
+        L.check(L.lib().dok_table_layout(value_bytes, key_bytes, self._n_buckets, ctypes.byref(lay)), "dok_table_layout")
+        self._layout = lay
+        self._value_bytes, self._key_bytes = value_bytes, key_bytes
         self._value_shape, self._value_dtype = torch.Size(value_shape), value_dtype
-        self._buckets = torch.empty(self._n_buckets * bb, device=self.device, dtype=torch.uint8)
-        self._key_store = torch.empty(self._n_buckets, *key_shape, device=self.device, dtype=key_dtype)
+        self._key_shape, self._key_dtype = torch.Size(key_shape), key_dtype
+        self._slots = torch.empty(lay.total_bytes, device=self.device, dtype=torch.uint8)
         self._uuid_only = None
         self._shared["stamp"] = None
         self._hp = None
@@ -173,7 +178,7 @@ class CudaClosedHashmap:
         """What `set` does to a never-used map before its kernel runs, for a batch known to hold `n_new` pairwise
         different new keys: allocate, draw the parameters, grow if the reference's trigger fires (which re-draws them,
         cuda_closed_hashmap.py:365-366, 456-468), account for the new elements.  The caller then inserts the rows."""
-        assert self._key_store is None
+        assert self._slots is None
         self._allocate(key_shape, key_dtype, value_shape, value_dtype)
         if n_new == 0:
             return
@@ -186,52 +191,57 @@ class CudaClosedHashmap:
         self._n_elements += n_new
         self._shared["bound"] = n_new
 
+    def _slot_view(self, dtype, inner_shape, byte_offset):
+        """[n_buckets, *inner_shape] strided view of one field of the slot array."""
+        es = torch.empty((), dtype=dtype).element_size()
+        strides, acc = [], 1
+        for extent in reversed(tuple(inner_shape)):
+            strides.append(acc)
+            acc *= int(extent)
+        strides = (self._layout.slot_bytes // es,) + tuple(reversed(strides))
+        return self._slots.view(dtype).as_strided((self._n_buckets,) + tuple(inner_shape), strides, byte_offset // es)
+
     @property
     def _uuid(self):
-        """[n_buckets] int64 tags: uuid, -1 empty, -3 removed (a strided view of the bucket array)."""
-        if self._buckets is None:
+        """[n_buckets] int64 tags: uuid, -1 empty, -3 removed (a strided view of the slot array)."""
+        if self._slots is None:
             return self._uuid_only
-        return self._buckets.view(torch.int64).as_strided((self._n_buckets,), (self._bucket_bytes // 8,), 0)
+        return self._slot_view(torch.int64, (), 0)
 
     @property
     def _values(self):
-        """[n_buckets, *value_shape] view of the value bytes inside the bucket array (None before the first set)."""
-        if self._buckets is None:
+        """[n_buckets, *value_shape] view of the value field of the slots (None before the first set)."""
+        if self._slots is None:
             return None
-        es = torch.empty((), dtype=self._value_dtype).element_size()
-        inner = []
-        acc = 1
-        for s in reversed(self._value_shape):
-            inner.append(acc)
-            acc *= s
-        strides = (self._bucket_bytes // es,) + tuple(reversed(inner))
-        return self._buckets.view(self._value_dtype).as_strided((self._n_buckets,) + tuple(self._value_shape), strides, 8 // es)
+        return self._slot_view(self._value_dtype, self._value_shape, self._layout.value_offset)
 
     @property
     def _keys(self):
-        """[n_buckets, *key_shape] key rows in storage-column order (None before the first set)."""
-        return self._key_store
+        """[n_buckets, *key_shape] view of the key rows, storage-column order (None before the first set)."""
+        if self._slots is None:
+            return None
+        return self._slot_view(self._key_dtype, self._key_shape, self._layout.key_offset)
 
-    def _ensure_stamp(self):
+    def _next_epoch(self):
+        """Epoch of the next general set: larger than every epoch stamped on this table before.  The stamps live in
+        the slots when the layout has room for them, else in a separate array allocated on first use."""
         sh = self._shared
-        if sh["stamp"] is None:
-            sh["stamp"] = torch.zeros(self._n_buckets, device=self.device, dtype=torch.long)
-            sh["epoch"] = 0
-        if sh["epoch"] >= 2 ** 31 - 2:
-            sh["stamp"].zero_()
-            sh["epoch"] = 0
+        if self._layout.stamp_offset < 0 and sh["stamp"] is None:
+            sh["stamp"] = torch.zeros(self._layout.n_slots, device=self.device, dtype=torch.long)
+        if sh["epoch"] >= L.MAX_EPOCH - 1:
+            raise L.DokError("stamp epochs exhausted: rehash() the map to start over")
         sh["epoch"] += 1
         return sh["epoch"]
 
     def _c_table(self):
         t = L.Table()
-        t.buckets = self._buckets.data_ptr()
-        t.keys = self._key_store.data_ptr()
+        t.slots = self._slots.data_ptr()
         stamp = self._shared["stamp"]
         t.stamp = stamp.data_ptr() if stamp is not None else None
         t.n_buckets = self._n_buckets
-        t.bucket_bytes = self._bucket_bytes
+        t.slot_bytes = self._layout.slot_bytes
         t.value_bytes = self._value_bytes
+        t.key_bytes = self._key_bytes
         self._table = t   # keeps the struct alive for the duration of the call
         return ctypes.byref(t)
 
@@ -241,7 +251,7 @@ class CudaClosedHashmap:
             hp = L.HashParams()
             ks = int(np.prod(self.key_shape))
             hp.key_size = ks
-            hp.key_dtype = L.DTYPE_CODES[self._key_store.dtype]
+            hp.key_dtype = L.DTYPE_CODES[self._key_dtype]
             names = ("alpha2", "beta2", "prime2", "alpha1", "beta1", "prime1")
             host = {name: getattr(self, name).cpu().tolist() for name in names}
             perm = self.key_perm.cpu().tolist()
@@ -266,7 +276,7 @@ class CudaClosedHashmap:
     # ------------------------------------------------------------------ compaction
     def items(self, keys=True, values=True, uuid=True, transposed_keys=False):
         """(keys, values, uuid) of the live slots in slot order, from one pass over the tags."""
-        assert self._buckets is not None
+        assert self._slots is not None
         lib = L.lib()
         with torch.cuda.device(self.device):
             st = L.stream_ptr(self.device)
@@ -278,7 +288,7 @@ class CudaClosedHashmap:
             k = v = u = None
             if keys:
                 shape = (ks, count) if transposed_keys else (count, ks)
-                k = torch.empty(shape, device=self.device, dtype=self._key_store.dtype)
+                k = torch.empty(shape, device=self.device, dtype=self._key_dtype)
             if values:
                 v = torch.empty((count,) + tuple(self._value_shape), device=self.device, dtype=self._value_dtype)
             if uuid:
@@ -294,17 +304,17 @@ class CudaClosedHashmap:
         return (self._uuid != self._empty_marker) & (self._uuid != self._removed_marker)
 
     def keys(self):
-        if self._key_store is None:
+        if self._slots is None:
             return None
         return self.items(values=False, uuid=False)[0]
 
     def values(self):
-        if self._buckets is None:
+        if self._slots is None:
             return None
         return self.items(keys=False, uuid=False)[1]
 
     def uuid(self):
-        if self._buckets is None:
+        if self._slots is None:
             return self._uuid_only[:0]
         return self.items(keys=False, values=False)[2]
 
@@ -314,15 +324,14 @@ class CudaClosedHashmap:
         self._values[self.nonempty_mask] = masked_values
 
     def permute_keys(self, ordering):
-        assert self._key_store is not None, "hashmap is empty"
+        assert self._slots is not None, "hashmap is empty"
         assert len(self.key_shape) == 1, "keys are not one dimensional"
         assert len(ordering) == self.key_shape[0]
         assert len(set(ordering)) == len(ordering), "duplicates are not allowed"
         self._materialise_parameters()
-        self._key_store = self._key_store[:, ordering].contiguous()
+        self._keys.copy_(self._keys[:, ordering].clone())
         for name in ("_alpha1", "_alpha2", "_beta1", "_beta2", "_prime1", "_prime2"):
             setattr(self, name, getattr(self, name)[ordering])
-        self._key_size = int(np.prod(self._key_store.shape[1:]))
         self._hp = None
 
     def clone(self, deepclone=False):
@@ -334,17 +343,20 @@ class CudaClosedHashmap:
             beta1=cp(self.beta1), beta2=cp(self.beta2), key_perm=cp(self._key_perm),
             rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
         )
-        if self._buckets is not None:
-            new._buckets = cp(self._buckets)
-            new._key_store = cp(self._key_store)
+        if self._slots is not None:
+            new._slots = cp(self._slots)
             new._uuid_only = None
-            new._bucket_bytes, new._value_bytes = self._bucket_bytes, self._value_bytes
+            new._layout = self._layout
+            new._value_bytes, new._key_bytes = self._value_bytes, self._key_bytes
             new._value_shape, new._value_dtype = self._value_shape, self._value_dtype
+            new._key_shape, new._key_dtype = self._key_shape, self._key_dtype
         else:
             new._uuid_only = cp(self._uuid_only)
         new._n_elements = cp(self._n_elements)
         if deepclone:
-            new._shared["bound"] = self._shared["bound"]
+            # in-slot stamps were copied with the slots: continue their epochs; a separate array is copied too
+            new._shared = {"stamp": None if self._shared["stamp"] is None else self._shared["stamp"].clone(),
+                           "epoch": self._shared["epoch"], "bound": self._shared["bound"]}
         else:
             new._shared = self._shared   # a view writes the same slots: same stamps, epoch and bound
         return new
@@ -370,17 +382,17 @@ class CudaClosedHashmap:
 
     @property
     def key_shape(self):
-        assert self._key_store is not None
-        return self._key_store.shape[1:]
+        assert self._slots is not None
+        return self._key_shape
 
     @property
     def value_shape(self):
-        assert self._buckets is not None
+        assert self._slots is not None
         return self._value_shape
 
     @property
     def key_type(self):
-        return self._key_store.dtype
+        return self._key_dtype
 
     @property
     def value_type(self):
@@ -429,7 +441,7 @@ class CudaClosedHashmap:
 
     def device_uuid(self, keys):
         """uuid of each key row exactly as the kernels compute it (value cast of the key elements)."""
-        assert self._key_store is not None
+        assert self._slots is not None
         keys = keys.contiguous()
         out = torch.empty(keys.shape[0], device=self.device, dtype=torch.long)
         with torch.cuda.device(self.device):
@@ -448,8 +460,8 @@ class CudaClosedHashmap:
                 L.check(lib.dok_map_set_unique(self._c_table(), self._c_hash(), L.ptr(keys), L.ptr(values), n, None,
                                                L.ptr(cnt), st), "dok_map_set_unique")
             else:
-                epoch = self._ensure_stamp()
-                scratch = torch.empty(n, device=self.device, dtype=torch.long)
+                epoch = self._next_epoch()
+                scratch = torch.empty(n + 1, device=self.device, dtype=torch.long)
                 L.check(lib.dok_map_set(self._c_table(), self._c_hash(), L.ptr(keys), L.ptr(values), n, L.ptr(scratch),
                                         epoch, None, L.ptr(cnt), st), "dok_map_set")
         return cnt
@@ -478,13 +490,13 @@ class CudaClosedHashmap:
         """Insert-or-assign a batch.  `assume_unique=True` promises pairwise different keys and runs one kernel
         instead of two.  Returns None like the reference."""
         assert new_keys.shape[0] == new_values.shape[0]
-        if self._key_store is None:
+        if self._slots is None:
             assert new_keys.device == new_values.device == self.device
             self._allocate(new_keys.shape[1:], new_keys.dtype, new_values.shape[1:], new_values.dtype)
         else:
-            assert new_keys.dtype == self._key_store.dtype
-            assert new_keys.device == self._key_store.device == self.device
-            assert new_keys.shape[1:] == self._key_store.shape[1:]
+            assert new_keys.dtype == self._key_dtype
+            assert new_keys.device == self.device
+            assert new_keys.shape[1:] == self._key_shape
             assert new_values.dtype == self._value_dtype
             assert new_values.device == self.device
             assert new_values.shape[1:] == self._value_shape
@@ -512,13 +524,13 @@ class CudaClosedHashmap:
 
     # ------------------------------------------------------------------ get
     def get(self, keys, fallback_value=None):
-        if self._key_store is None or self._buckets is None:
+        if self._slots is None:
             raise RuntimeError("store something first")
         if keys.shape[0] == 0:
             return (torch.empty(0, *self.value_shape, device=self.device, dtype=self._value_dtype),
                     torch.empty(0, device=self.device, dtype=torch.bool))
-        assert keys.dtype == self._key_store.dtype
-        assert keys.device == self._key_store.device
+        assert keys.dtype == self._key_dtype
+        assert keys.device == self.device
         assert keys.shape[1:] == self.key_shape
         fb = None
         if fallback_value is not None:
@@ -561,12 +573,12 @@ class CudaClosedHashmap:
         return is_removed
 
     def remove(self, keys):
-        if self._key_store is None or self._buckets is None:
+        if self._slots is None:
             raise RuntimeError("store something first")
         if keys.shape[0] == 0:
             return torch.zeros(0, device=keys.device, dtype=torch.bool)
-        assert keys.dtype == self._key_store.dtype
-        assert keys.device == self._key_store.device
+        assert keys.dtype == self._key_dtype
+        assert keys.device == self.device
         assert keys.shape[1:] == self.key_shape
         unique_keys = keys.unique(dim=0)
         return self.remove_rows(unique_keys)

@@ -120,7 +120,7 @@ class SparseDOKTensor(object):
         assert len(storage.key_shape) == 1
         ndims = storage.key_shape[0]
         if size is None:
-            size = tuple(storage._keys.max(dim=0).values.cpu().tolist())
+            size = tuple(storage.keys().max(dim=0).values.cpu().tolist())
         else:
             assert len(size) == ndims
             assert all(i >= 0 for i in size)
@@ -291,8 +291,8 @@ class SparseDOKTensor(object):
                 hashmap.rehash(math.ceil((n_elements + n_sel) * hashmap._rehash_factor))
         sel = _selectors_struct(selectors)
         src_strides = (ctypes.c_int64 * L.MAX_SELECTOR_NDIM)(*src.stride())
-        epoch = hashmap._ensure_stamp()
-        scratch = torch.empty(n_sel, device=self.device, dtype=torch.long)
+        epoch = hashmap._next_epoch()
+        scratch = torch.empty(n_sel + 1, device=self.device, dtype=torch.long)
         with torch.cuda.device(self.device):
             L.check(L.lib().dok_dok_set_dense(hashmap._c_table(), hashmap._c_hash(), ctypes.byref(sel), L.ptr(src),
                                               src_strides, L.ptr(scratch), epoch, None, L.stream_ptr(self.device)),

@@ -10,16 +10,19 @@
  *
  * Key identity is the reference's 64-bit "uuid" (second hash), not the key bytes
  * (closed_hashmap_impl_class.cu:280-312, 368-427, 459-484).  The uuid is reproduced bit for bit;
- * the start bucket is free (the slot layout is not part of the contract) and is derived from the
- * uuid and the reference's first hash with a 64-bit mixer.
+ * the start slot is free (the slot layout is not part of the contract) and is derived from the uuid
+ * and the first-hash parameters with a 64-bit mixer.
  *
- * Storage of a table with n_buckets slots (three arrays, owned by the caller):
- *   buckets : n_buckets rows of bucket_bytes = max(16, round_up(8 + value_bytes, 16)) bytes:
- *             { int64 tag; value_bytes of value; padding }.  tag = uuid, -1 empty, -3 tombstone
- *             (the reference's _uuid and _values arrays, interleaved so that a hit is one sector).
- *   keys    : n_buckets rows of key_size * key_elem_bytes bytes, storage-column order
- *             (the reference's _keys array; written by set, read only by compaction).
- *   stamp   : n_buckets int64, zero-initialised, only needed by dok_map_set (may be NULL elsewhere).
+ * Storage of a table (owned by the caller, 128-byte aligned, sized by dok_table_layout): n_slots slots of
+ * slot_bytes (32, 64, 128, or a larger multiple of 128 for very wide rows):
+ *     { int64 tag | int64 stamp (if it fits without growing the slot) | value (padded to 8) | key row (padded to 8) }
+ * tag = uuid, -1 empty, -3 tombstone, -2 blocked padding slot (slots n_buckets .. n_slots-1).  These are the
+ * reference's _uuid, _values and _keys arrays interleaved.  On B200 every access instruction that touches a table
+ * much larger than L2 costs the same, whatever it moves, while lanes that fall into one 128-byte line share the
+ * cost; so an operation's tag, value and key sit in one line, a line is a probe group of 4 / 2 / 1 slots, and four
+ * adjacent lanes read a group with one request.
+ *   stamp : separate n_slots int64 array, zero-initialised; needed by dok_map_set / dok_dok_set_dense only when
+ *           the layout reports stamp_offset == -1 (no room in the slot); NULL otherwise.
  */
 #ifndef DOKSPARSE_H
 #define DOKSPARSE_H
@@ -55,9 +58,10 @@ typedef enum dok_dtype {
  * Second hash = the uuid, the key's identity, reproduced bit for bit:
  *   uuid  = | prod_i ( ((int64)key_i * alpha2[c] + beta2[c]) % prime2[c] ) |,  c = key_perm[i],
  * wrapping int64, C remainder, value cast of key_i (closed_hashmap_impl_class.cu:98-107, parameters indexed
- * through keyPerm as in :54-63).  First hash (same form with alpha1/beta1/prime1, :87-96): the reference starts
- * probing at hash1 % n_buckets; this library starts at mix(uuid, hash1 % n_buckets), so keys that the reference
- * tells apart only by their first hash stay apart here as well.  |prime1[c]|, |prime2[c]| must be >= 2. */
+ * through keyPerm as in :54-63).  The first hash (:87-96) places rows in the reference; here alpha1 / beta1 only
+ * feed the start slot, mix(uuid, prod_i (key_i * (alpha1[c] | 1) + beta1[c])), so that keys whose uuids collide
+ * but whose first hashes differ -- which the reference tells apart -- stay apart here as well.  prime1 is not
+ * used.  |prime2[c]| must be >= 2. */
 typedef struct dok_hash_params {
   int32_t key_size;    /* 1..DOK_MAX_KEY_SIZE */
   int32_t key_dtype;   /* dok_dtype of the caller's key rows */
@@ -71,13 +75,25 @@ typedef struct dok_hash_params {
 } dok_hash_params;
 
 typedef struct dok_table {
-  void *buckets;
-  void *keys;
-  int64_t *stamp;      /* may be NULL except for dok_map_set / dok_dok_set_dense */
-  int64_t n_buckets;
-  int32_t bucket_bytes;
+  void *slots;
+  int64_t *stamp;      /* separate stamp array, or NULL (see above) */
+  int64_t n_buckets;   /* slots visible to the caller */
+  int32_t slot_bytes;  /* as reported by dok_table_layout */
   int32_t value_bytes;
+  int32_t key_bytes;   /* key_size * bytes per key element */
+  int32_t reserved;
 } dok_table;
+
+typedef struct dok_layout_info {
+  int32_t slot_bytes;
+  int32_t slots_per_group; /* slots per 128-byte probe group (1 for slots wider than 128 bytes) */
+  int32_t value_offset;    /* offsets inside a slot */
+  int32_t key_offset;
+  int32_t stamp_offset;    /* -1: the stamps need a separate array */
+  int32_t reserved;
+  int64_t n_slots;         /* n_buckets rounded up to whole groups */
+  int64_t total_bytes;     /* n_slots * slot_bytes */
+} dok_layout_info;
 
 /* Counters written by the mutating calls (device int64[DOK_N_COUNTERS], ADDED to, not reset). */
 enum {
@@ -106,17 +122,19 @@ typedef struct dok_selectors {
 int dok_version(void);
 int dok_last_cuda_error(void);          /* cudaError_t of the last failed launch on this thread */
 int64_t dok_launch_count(void);         /* kernels launched by this library in this process so far */
-int dok_bucket_bytes(int value_bytes);  /* max(16, round_up(8 + value_bytes, 16)); -1 if unsupported */
+/* slot geometry and allocation size for a table; DOK_BAD_ARG if the widths are unsupported */
+int dok_table_layout(int value_bytes, int key_bytes, int64_t n_buckets, dok_layout_info *out);
 
-/* Fills tags with DOK_TAG_EMPTY (values untouched) and, if present, zeroes `stamp`.
+/* Fills the tags (DOK_TAG_EMPTY, blocked for padding slots; values untouched) and zeroes the stamps.
  * Replaces `torch.zeros(n_buckets) + empty_marker`, cuda_closed_hashmap.py:40. */
 int dok_map_init(const dok_table *t, void *stream);
 
-/* uuid (and this library's start bucket) of each key row.  uuid_out / bucket_out may be NULL.
+/* uuid (and this library's start slot) of each key row.  uuid_out / slot_out may be NULL; t may be NULL when
+ * slot_out is.
  * Replaces nothing on the reference's hot path; CudaClosedHashmap.get_uuid
  * (cuda_closed_hashmap.py:302-319) is the closest relative but bit-casts floats, which the kernels do not. */
 int dok_map_uuid(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
-                 int64_t *uuid_out, int64_t *bucket_out, void *stream);
+                 int64_t *uuid_out, int64_t *slot_out, void *stream);
 
 /* Batched lookup.  out_values[n, value_bytes] receives the stored row on a hit and `fallback`
  * (HOST pointer to value_bytes bytes, NULL = zeros) on a miss; out_found[n] is 0/1.  counters may be NULL.
@@ -138,10 +156,11 @@ int dok_map_set_unique(const dok_table *t, const dok_hash_params *hp, const void
                        int64_t n, uint8_t *out_stored, int64_t *counters, void *stream);
 
 /* Insert-or-assign for any batch: rows with equal uuid resolve to the LAST row in batch order, exactly one
- * slot per uuid, rows never torn (what a serial run of the reference kernel produces).  Two kernels:
- * claim (find or claim the slot, atomicMax of (epoch<<32 | row) on t->stamp) then write (winners only).
- * slot_scratch: device int64[n], contents irrelevant.  epoch: 1..2^31-1, strictly larger than any epoch used
- * on this table since `stamp` was last zeroed.  n < 2^32. */
+ * slot per uuid, rows never torn (what a serial run of the reference kernel produces).  Two kernels: the first
+ * finds or claims each row's slot, raises the slot's stamp to (epoch, row) with atomicMax and lets the first row
+ * to arrive write key and value; the second runs only if the first met equal uuids, and lets each such slot's
+ * last row rewrite it.  slot_scratch: device int64[n + 1], contents irrelevant.  epoch: 1..2^30-1, strictly larger
+ * than any epoch used on this table since its stamps were last zeroed.  n < 2^32. */
 int dok_map_set(const dok_table *t, const dok_hash_params *hp, const void *keys, const void *values,
                 int64_t n, int64_t *slot_scratch, int64_t epoch, uint8_t *out_stored, int64_t *counters,
                 void *stream);
@@ -189,7 +208,7 @@ int dok_dok_count_exists(const dok_table *t, const dok_hash_params *hp, const do
                          int64_t *counters, void *stream);
 
 /* Insert-or-assign of a broadcast dense source, last selector element wins on duplicates, zeros stored.
- * src_strides in elements of value_bytes.  Replaces sparse_dok_set_items_dense
+ * src_strides in elements of value_bytes; slot_scratch int64[n + 1].  Replaces sparse_dok_set_items_dense
  * (sparse_dok_tensor_impl.cu:270-313, launcher sparse_dok_tensor_impl.py:412-474). */
 int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel,
                       const void *src, const int64_t *src_strides, int64_t *slot_scratch, int64_t epoch,

@@ -34,15 +34,31 @@ def test_library_exports_every_declared_symbol():
     assert set(_lib.EXPORTED) == set(declared_functions())
 
 
-def test_bucket_geometry():
+def test_slot_geometry():
     from doksparse_b200 import _lib
     lib = _lib.lib()
-    assert lib.dok_bucket_bytes(4) == 16 and lib.dok_bucket_bytes(8) == 16
-    assert lib.dok_bucket_bytes(16) == 32 and lib.dok_bucket_bytes(40) == 48
-    assert lib.dok_bucket_bytes(0) == -1 and lib.dok_bucket_bytes(249) == -1
+
+    def layout(vb, kb, nb):
+        out = _lib.LayoutInfo()
+        assert lib.dok_table_layout(vb, kb, nb, ctypes.byref(out)) == 0
+        return out
+
+    a = layout(8, 8, 1000)           # int64 -> float32[2]: tag + value + key + stamp fill a 32-byte slot
+    assert (a.slot_bytes, a.slots_per_group, a.value_offset, a.key_offset, a.stamp_offset) == (32, 4, 8, 16, 24)
+    assert (a.n_slots, a.total_bytes) == (1000, 32000)
+    b = layout(4, 16, 1001)          # 2-D DOK float32: 32-byte slot, no room for the stamp, 4 slots per group
+    assert (b.slot_bytes, b.value_offset, b.key_offset, b.stamp_offset, b.n_slots) == (32, 8, 16, -1, 1004)
+    c = layout(40, 12, 7)            # float32[3] -> int64[5]: 64-byte slot, 2 per group
+    assert (c.slot_bytes, c.slots_per_group, c.key_offset, c.stamp_offset, c.n_slots) == (64, 2, 48, -1, 8)
+    d = layout(4, 32, 10)            # 4-D DOK float32: 64-byte slot with the stamp inside
+    assert (d.slot_bytes, d.value_offset, d.key_offset, d.stamp_offset) == (64, 8, 16, 48)
+    e = layout(248, 64, 5)           # widest supported row: slots span several lines, probed one by one
+    assert (e.slot_bytes, e.slots_per_group, e.stamp_offset, e.n_slots) == (384, 1, 320, 5)
+    out = _lib.LayoutInfo()
+    assert lib.dok_table_layout(0, 8, 10, ctypes.byref(out)) != 0 and lib.dok_table_layout(249, 8, 10, ctypes.byref(out)) != 0
     assert lib.dok_compact_tiles(1) == 1 and lib.dok_compact_tiles(2049) == 2
     assert ctypes.sizeof(_lib.HashParams) == 8 + 6 * 64 + 32
-    assert ctypes.sizeof(_lib.Table) == 40
+    assert ctypes.sizeof(_lib.Table) == 40 and ctypes.sizeof(_lib.LayoutInfo) == 40
 
 
 def test_no_cpu_fallback():
