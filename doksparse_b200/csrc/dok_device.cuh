@@ -302,72 +302,80 @@ __device__ __forceinline__ void dok_load_words(const char *p, ull_t (&w)[LW]) {
 // whose chain runs into a further group (few below 90 % load) are finished in a loop.
 // On a hit, `emit(e_r, slot_in_group, words)` runs on all four lanes while they still hold the line: e_r is the
 // batch element of the key, words the calling lane's chunk.
-// Every lane of the warp must call this (inactive lanes pass active = false).  SB = slot bytes (32, 64, 128).
+// Every lane of the warp must call this (inactive lanes pass active = false), with CONSECUTIVE batch elements e in
+// consecutive lanes.  SB = slot bytes (32, 64, 128).  Slot indices are 32-bit here: the host refuses cooperative
+// tables of 2^32 - 1 slots or more.
 template <int SB, int LW, class Emit>
 __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyHash &kh, ll_t e, bool active,
                                                    int *probes, const Emit &emit) {
   constexpr int SPG = 128 / SB;
   constexpr unsigned FULL = 0xffffffffu;
+  constexpr unsigned NONE = 0xffffffffu;              // group index of a lane with nothing (left) to do
   const unsigned lane = threadIdx.x & 31u, l = lane & 3u, base = lane & ~3u;
-  const bool has_tag = ((32u * l) % SB) == 0;       // does this lane's chunk start with a slot's tag?
-  const unsigned my_slot = (32u * l) / SB;          // slot (within the group) the chunk belongs to
-  Located res{-1, -1, -1};
-  ll_t group = active ? dok_start_group(kh, t) : -1;     // -1: nothing (left) to do for this lane's key
-  ll_t walked = 0;
+  const bool has_tag = ((32u * l) % SB) == 0;         // does this lane's chunk start with a slot's tag?
+  const unsigned my_slot = (32u * l) / SB;            // slot (within the group) the chunk belongs to
+  const ll_t e_quad = e - l;                          // batch element of the quad's first lane (elements are consecutive)
+  const unsigned n_groups = (unsigned)t.n_groups;     // < 2^32 (checked on the host)
+  const char *my_base = t.slots + 32 * l;
+  // results as 32-bit group-relative codes until the end: slot = group * SPG + position
+  unsigned found = NONE, empty = NONE, tomb = NONE;
+  unsigned group = active ? (unsigned)dok_start_group(kh, t) : NONE;
+  unsigned walked = 0;
 
-  // one step for the key owned by lane r of the quad: g_r is its current group (or -1), w this lane's chunk of it
-  auto resolve = [&](const ull_t (&w)[LW], ll_t g_r, ll_t uuid_r, ll_t e_r, unsigned r) {
-    const ll_t tag = (has_tag && g_r >= 0) ? (ll_t)w[0] : DOK_BLOCKED;
+  // one step for the key owned by lane r of the quad: g_r is its current group (or NONE), w this lane's chunk of it
+  auto resolve = [&](const ull_t (&w)[LW], unsigned g_r, ll_t uuid_r, unsigned r) {
+    const ll_t tag = (has_tag && g_r != NONE) ? (ll_t)w[0] : DOK_BLOCKED;
     unsigned bits = ((unsigned)(tag == uuid_r) | ((unsigned)(tag == DOK_EMPTY) << 4) | ((unsigned)(tag == DOK_REMOVED) << 8)) << my_slot;
     bits |= __shfl_xor_sync(FULL, bits, 1);
     bits |= __shfl_xor_sync(FULL, bits, 2);
-    const unsigned m = bits & 0xfu, em = (bits >> 4) & 0xfu, tb = (bits >> 8) & 0xfu;
-    const int pos = (m | em) ? __ffs(m | em) - 1 : -1;
+    const unsigned m = bits & 0xfu, me = (bits | (bits >> 4)) & 0xfu, tb = (bits >> 8) & 0xfu;
+    const int pos = me ? __ffs(me) - 1 : -1;
     const bool hit = pos >= 0 && ((m >> pos) & 1u);
-    if (hit) emit(e_r, pos, w);
-    if (l == r && group >= 0) {
-      const ll_t first_slot = group * SPG;
+    if (hit) emit(e_quad + r, pos, w);
+    if (l == r && group != NONE) {
+      const unsigned first_slot = group * SPG;
       walked++;
+      if (tomb == NONE) {
+        const unsigned before = pos >= 0 ? (tb & ((1u << pos) - 1u)) : tb;
+        if (before) tomb = first_slot + __ffs(before) - 1;
+      }
       if (pos >= 0) {
-        const unsigned before = tb & ((1u << pos) - 1u);
-        if (hit) res.found = first_slot + pos;
-        else {
-          res.empty = first_slot + pos;
-          if (res.tomb < 0 && before) res.tomb = first_slot + __ffs(before) - 1;
-        }
-        group = -1;
+        if (hit) found = first_slot + pos; else empty = first_slot + pos;
+        group = NONE;
       } else {
-        if (res.tomb < 0 && tb) res.tomb = first_slot + __ffs(tb) - 1;
-        if (++group == t.n_groups) group = 0;
-        if (walked == t.n_groups) group = -1;           // every group inspected: no empty slot anywhere
+        group = (group + 1 == n_groups) ? 0u : group + 1;
+        if (walked == n_groups) group = NONE;           // every group inspected: no empty slot anywhere
       }
     }
   };
 
   ull_t w[4][LW];
-  ll_t g[4];
+  unsigned g[4];
 #pragma unroll
   for (unsigned r = 0; r < 4; r++) {
     g[r] = __shfl_sync(FULL, group, base + r);
-    if (g[r] >= 0) dok_load_words<LW>(t.slots + g[r] * 128 + 32 * l, w[r]);
+    if (g[r] != NONE) dok_load_words<LW>(my_base + (ull_t)g[r] * 128u, w[r]);
   }
 #pragma unroll
-  for (unsigned r = 0; r < 4; r++)
-    resolve(w[r], g[r], __shfl_sync(FULL, kh.uuid, base + r), __shfl_sync(FULL, e, base + r), r);
+  for (unsigned r = 0; r < 4; r++) resolve(w[r], g[r], __shfl_sync(FULL, kh.uuid, base + r), r);
 
   for (;;) {
-    const unsigned pend = __ballot_sync(FULL, group >= 0);
+    const unsigned pend = __ballot_sync(FULL, group != NONE);
     if (pend == 0) break;
     const unsigned quad = (pend >> base) & 0xfu;
     const unsigned r = quad ? (unsigned)(__ffs(quad) - 1) : 0u;     // the quad's lowest unfinished key
-    const ll_t g_r = quad ? __shfl_sync(FULL, group, base + r) : (__shfl_sync(FULL, group, base + r), -1);
+    unsigned g_r = __shfl_sync(FULL, group, base + r);
+    if (!quad) g_r = NONE;
     const ll_t uuid_r = __shfl_sync(FULL, kh.uuid, base + r);
-    const ll_t e_r = __shfl_sync(FULL, e, base + r);
     ull_t wl[LW];
-    if (g_r >= 0) dok_load_words<LW>(t.slots + g_r * 128 + 32 * l, wl);
-    resolve(wl, g_r, uuid_r, e_r, r);
+    if (g_r != NONE) dok_load_words<LW>(my_base + (ull_t)g_r * 128u, wl);
+    resolve(wl, g_r, uuid_r, r);
   }
   if (probes) *probes = (int)walked;
+  Located res;
+  res.found = found == NONE ? -1 : (ll_t)found;
+  res.empty = empty == NONE ? -1 : (ll_t)empty;
+  res.tomb = tomb == NONE ? -1 : (ll_t)tomb;
   return res;
 }
 
@@ -417,7 +425,7 @@ enum { DOK_OUT_FOUND = 0, DOK_OUT_CLAIMED_EMPTY = 1, DOK_OUT_REUSED = 2, DOK_OUT
 // first empty tag the slot is claimed by CAS unless a tombstone was seen.  Phase 2 starts at the remembered
 // tombstone and tries tombstone->uuid, then empty->uuid, slot by slot.  Unlike the reference, a CAS that loses
 // to the SAME uuid joins that slot instead of walking on, so equal uuids of one batch always meet in one slot.
-static __device__ __noinline__ ll_t dok_find_or_claim_serial(const DevTable &t, const KeyHash &kh, int *outcome) {
+static __device__ __forceinline__ ll_t dok_find_or_claim_serial(const DevTable &t, const KeyHash &kh, int *outcome) {
   const ll_t uuid = kh.uuid;
   ll_t slot = dok_start_group(kh, t) * t.spg;
   ll_t first_removed = -1;

@@ -110,6 +110,7 @@ inline bool dok_make_table(const dok_table *t, DevTable *out) {
   out->key_off = lay.key_off;
   out->stamp_off = lay.stamp_off;
   out->vwords = (t->value_bytes + 7) / 8;
+  if (lay.sb <= 128 && out->n_slots >= 0xffffffffLL) return false;    // the cooperative walk keeps slot indices in 32 bits
   return true;
 }
 

@@ -66,17 +66,21 @@ inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, vo
 // set
 // ---------------------------------------------------------------------------------------------------------
 
-// Key row and value row of batch element e into a claimed slot.
+// Value row of batch element e into its slot, and the key row too when this row claimed the slot.  A row that
+// found its uuid already stored leaves the stored key alone: the reference rewrites it
+// (closed_hashmap_impl_class.cu:384-386), but with the same bytes unless two different keys share a uuid, and every
+// store to the table costs a request.  Floating-point keys are the exception -- their value cast makes different
+// keys share a uuid as a rule -- so they are rewritten like in the reference.
 template <class Keys, class Values>
 __device__ __forceinline__ void dok_write_row(const DevTable &t, const DevHash &hp, const Keys &keys, const Values &values,
-                                              ll_t e, ll_t slot) {
-  keys.store_key(hp, e, dok_key_row(t, slot));
+                                              ll_t e, ll_t slot, bool with_key) {
+  if (with_key) keys.store_key(hp, e, dok_key_row(t, slot));
   dok_store_value(t, slot, values.row(t, e));
 }
 
 // One kernel, for batches whose rows have pairwise different uuids.
 template <int SB, class Keys, class Values>
-__global__ void __launch_bounds__(DOK_TPB) k_set_unique(DevTable t, DevHash hp, Keys keys, Values values,
+__global__ void __launch_bounds__(DOK_TPB, 4) k_set_unique(DevTable t, DevHash hp, Keys keys, Values values,
                                                         uint8_t *__restrict__ out_stored, ll_t *counters) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   const bool active = e < keys.count();
@@ -85,7 +89,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_unique(DevTable t, DevHash hp, 
   int outcome = -1;
   const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
   if (active) {
-    if (slot >= 0) dok_write_row(t, hp, keys, values, e, slot);
+    if (slot >= 0) dok_write_row(t, hp, keys, values, e, slot, outcome != DOK_OUT_FOUND || hp.dtype >= DOK_F16);
     if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
   }
   if (counters) {
@@ -107,7 +111,7 @@ __device__ __forceinline__ ll_t dok_stamp(ll_t epoch, ll_t row) { return (epoch 
 // counts a duplicate (in slot_out[n], zeroed by the host before the launch); the second kernel then lets the
 // slot's last row rewrite it.
 template <int SB, class Keys, class Values>
-__global__ void __launch_bounds__(DOK_TPB) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
+__global__ void __launch_bounds__(DOK_TPB, 4) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
                                                        ll_t *__restrict__ slot_out, ll_t epoch,
                                                        uint8_t *__restrict__ out_stored, ll_t *counters) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
@@ -121,7 +125,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_claim(DevTable t, DevHash hp, K
     if (slot >= 0) {
       ll_t *stamp = dok_stamp_ptr(t, slot);
       const ll_t old = (ll_t)atomicMax(stamp, dok_stamp(epoch, e));
-      if ((old >> 33) != epoch) dok_write_row(t, hp, keys, values, e, slot);
+      if ((old >> 33) != epoch) dok_write_row(t, hp, keys, values, e, slot, outcome != DOK_OUT_FOUND || hp.dtype >= DOK_F16);
       else {
         atomicOr((ull_t *)stamp, 1ULL);
         dup = 1;
@@ -151,7 +155,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_resolve(DevTable t, DevHash hp,
   const ll_t slot = slot_in[e];
   if (slot < 0) return;
   if (__ldcg(dok_stamp_ptr(t, slot)) != (dok_stamp(epoch, e) | 1)) return;
-  dok_write_row(t, hp, keys, values, e, slot);
+  dok_write_row(t, hp, keys, values, e, slot, true);
 }
 
 // ---------------------------------------------------------------------------------------------------------
