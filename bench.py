@@ -34,6 +34,10 @@ KEY_BYTES, VALUE_BYTES = 8, 8
 HIT_FRACTION = 0.8
 LOAD_FACTOR = 0.6
 N_BATCHES = 4          # distinct query/update batches rotated over the steps (each is larger than L2)
+# DRAM bytes per operation of the kernels, dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture divided by
+# the rows of the launch (profiles/k_*_c5_shard_2e26keys.md; the capture ran at 2^26 keys and 2^24 rows, traffic per row
+# does not depend on the size once the table is much larger than L2)
+TRAFFIC_BYTES_PER_OP = {"get": 171.5, "set": 210.4, "remove": 230.3}
 
 
 def parse_args():
@@ -328,11 +332,14 @@ def run_candidate(args):
               "n_elements_stationary": table.n_elements == total_keys}
     del values, found, expect_found
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None      # started early: its start-up must not fall into the timed region
     for s in range(1, args.warmup):
         step(s)
+    if sampler:
+        time.sleep(0.5)
+        sampler.rows.clear()
 
     # ---- timed region: exactly K steps, device-resident inputs
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     launches0 = L.lib().dok_launch_count()
     events = []
     barrier()
@@ -392,6 +399,19 @@ def run_candidate(args):
         e2e = {"value": ops_per_step / (float(e_ms.item()) / e2e_steps * 1e-3) / 1e6, "unit": "Mops/s",
                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e2e_steps}
 
+    # ---- what the hardware gives a probing kernel: independent random 16-byte reads over this GPU's slot array
+    slots = table.ops.local._slots
+    n_reads = 1 << 26
+    lib = L.lib()
+    lib.dok_diag_random_reads(L.ptr(slots), slots.numel(), n_reads, 1, None, L.stream_ptr(device))
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for rep in range(3):
+        lib.dok_diag_random_reads(L.ptr(slots), slots.numel(), n_reads, 100 + rep, None, L.stream_ptr(device))
+    r1.record()
+    torch.cuda.synchronize()
+    request_ceiling = 3 * n_reads / (r0.elapsed_time(r1) * 1e-3) / 1e9          # G requests/s, this GPU
+
     # ---- roofline of the dominant kernel and of the other two
     peak, peak_source = measured_peak_gbs()
     local_rows = {"get": q, "set": q, "remove": q - n_hit}       # rows each GPU processes per step (weak scaling)
@@ -399,13 +419,20 @@ def run_candidate(args):
     per_kernel = {}
     for op in ("get", "set", "remove"):
         achieved = algorithmic_bytes(op) * local_rows[op] / (kernel_ms[op] * 1e-3) / 1e9
-        per_kernel[op] = {"ms": kernel_ms[op], "mops_per_gpu": local_rows[op] / (kernel_ms[op] * 1e-3) / 1e6,
-                          "bytes_per_op": algorithmic_bytes(op), "achieved_gbs": achieved, "frac": achieved / peak}
+        gops = local_rows[op] / (kernel_ms[op] * 1e-3) / 1e9
+        per_kernel[op] = {"ms": kernel_ms[op], "mops_per_gpu": gops * 1e3, "bytes_per_op": algorithmic_bytes(op),
+                          "achieved_gbs": achieved, "frac": achieved / peak,
+                          "frac_of_random_request_ceiling": gops / request_ceiling}
     top = max(kernel_ms, key=kernel_ms.get)
-    roofline = {"bound": "hbm", "kernel": {"get": "k_get", "set": "k_set_claim + k_set_write", "remove": "k_find<remove>"}[top],
+    roofline = {"bound": "hbm", "kernel": {"get": "k_get", "set": "k_set_claim (+ k_set_resolve, idle without duplicates)",
+                                           "remove": "k_find<remove>"}[top],
                 "achieved": per_kernel[top]["achieved_gbs"], "peak": peak, "unit": "GB/s", "frac": per_kernel[top]["frac"],
-                "traffic": None, "peak_source": peak_source,
-                "note": "phase time includes routing and exchange when shards > 1" if world > 1 else "phase = kernel(s) of one op"}
+                "traffic": TRAFFIC_BYTES_PER_OP.get(top, 0) * local_rows[top] if TRAFFIC_BYTES_PER_OP.get(top) else None,
+                "peak_source": peak_source,
+                "random_request_ceiling_greq_s": request_ceiling,
+                "note": ("phase time includes routing and exchange when shards > 1; " if world > 1 else "") +
+                        "a table much larger than L2 serves ~48 G random requests/s whatever their size, so one "
+                        "request per operation caps a probing kernel well below the byte roofline"}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -100,6 +100,7 @@ def _declare(lib):
         "dok_shard_partition_scatter": ([HP, P, P, I, I64, I, P, P, P, P, P], I),
         "dok_shard_unpermute": ([P, P, P, I, I64, P, P, P], I),
         "dok_shard_owner": ([HP, P, I64, I, P, P], I),
+        "dok_diag_random_reads": ([P, I64, I64, ctypes.c_uint64, P, P], I),
     }
     for name, (argtypes, restype) in sig.items():
         fn = getattr(lib, name)

@@ -56,7 +56,7 @@ class CudaClosedHashmap:
         self._uuid_only = torch.full((self._n_buckets,), self._empty_marker, device=self.device, dtype=torch.long)
         # state that shallow clones (views) must see together: the duplicate-resolution stamps with their epoch,
         # and the host-side upper bound of n_elements that lets `set` skip a device synchronisation
-        self._shared = {"stamp": None, "epoch": 0, "bound": 0}
+        self._shared = {"stamp": None, "epoch": 0, "bound": 0, "snapshots": []}
         self._value_shape = None
         self._value_dtype = None
 
@@ -273,6 +273,36 @@ class CudaClosedHashmap:
     def _counters(self):
         return torch.zeros(L.N_COUNTERS, device=self.device, dtype=torch.long)
 
+    # The rehash decision of `set` needs n_elements on the host, which the reference gets with a blocking .item()
+    # per call.  Here the host keeps an UPPER BOUND instead: after every mutation the device count is copied to
+    # pinned memory without waiting, and the bound is the newest copy that has landed plus the sizes of the set
+    # batches enqueued after it.  Only when that bound crosses the threshold is the exact value fetched.
+    def _after_mutation(self, added):
+        sh = self._shared
+        sh["bound"] += added
+        snaps = sh["snapshots"]
+        for s in snaps:
+            s[2] += added                       # rows that may have been inserted after that snapshot was taken
+        host = torch.empty((), dtype=torch.long, pin_memory=True)
+        with torch.cuda.device(self.device):
+            host.copy_(self._n_elements, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+        snaps.append([event, host, 0])
+        if len(snaps) > 8:
+            del snaps[0]
+
+    def _element_bound(self):
+        sh = self._shared
+        snaps = sh["snapshots"]
+        newest = None
+        while snaps and snaps[0][0].query():
+            newest = snaps.pop(0)
+        if newest is not None:
+            sh["bound"] = min(sh["bound"], int(newest[1].item()) + newest[2])
+            snaps.insert(0, newest)             # keep it: it stays the newest completed one until another lands
+        return sh["bound"]
+
     # ------------------------------------------------------------------ compaction
     def items(self, keys=True, values=True, uuid=True, transposed_keys=False):
         """(keys, values, uuid) of the live slots in slot order, from one pass over the tags."""
@@ -356,7 +386,7 @@ class CudaClosedHashmap:
         if deepclone:
             # in-slot stamps were copied with the slots: continue their epochs; a separate array is copied too
             new._shared = {"stamp": None if self._shared["stamp"] is None else self._shared["stamp"].clone(),
-                           "epoch": self._shared["epoch"], "bound": self._shared["bound"]}
+                           "epoch": self._shared["epoch"], "bound": self._shared["bound"], "snapshots": []}
         else:
             new._shared = self._shared   # a view writes the same slots: same stamps, epoch and bound
         return new
@@ -365,6 +395,7 @@ class CudaClosedHashmap:
     @property
     def n_elements(self):
         n = int(self._n_elements.item())
+        self._shared["snapshots"].clear()
         self._shared["bound"] = n
         return n
 
@@ -508,11 +539,11 @@ class CudaClosedHashmap:
         self._materialise_parameters()
         limit = int(self._rehash_threshold * self.n_buckets)
         row_counted = new_keys.dtype in L.FLOAT_DTYPES
-        if not row_counted and self._shared["bound"] + n <= limit:
+        if not row_counted and self._element_bound() + n <= limit:
             # whatever the number of new keys is, the reference would not rehash: insert and count on the device
             cnt = self._launch_set(new_keys, new_values, assume_unique)
             self._n_elements += cnt[L.CNT_CLAIMED_EMPTY] + cnt[L.CNT_REUSED_REMOVED]
-            self._shared["bound"] += n
+            self._after_mutation(n)
             return
         n_new = self._count_new(new_keys)
         n_elements = self.n_elements
@@ -520,6 +551,7 @@ class CudaClosedHashmap:
             self.rehash(int((n_elements + n_new) * self._rehash_factor))
         self._launch_set(new_keys, new_values, assume_unique)
         self._n_elements += n_new
+        self._shared["snapshots"].clear()
         self._shared["bound"] = n_elements + n_new
 
     # ------------------------------------------------------------------ get
@@ -570,6 +602,7 @@ class CudaClosedHashmap:
             L.check(L.lib().dok_map_remove(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(is_removed), L.ptr(cnt),
                                            L.stream_ptr(self.device)), "dok_map_remove")
         self._n_elements -= cnt[L.CNT_HITS]
+        self._after_mutation(0)
         return is_removed
 
     def remove(self, keys):

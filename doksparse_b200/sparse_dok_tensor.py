@@ -285,7 +285,7 @@ class SparseDOKTensor(object):
             hashmap.set(first_key, src[first].reshape(1, 1))
         n_existing = self._count_existing(selectors)          # device scalar, no sync
         # rehash decision of the reference (:461-462) depends on n_elements and the batch size only
-        if hashmap._shared["bound"] + n_sel > hashmap.n_buckets * hashmap._rehash_threshold:
+        if hashmap._element_bound() + n_sel > hashmap.n_buckets * hashmap._rehash_threshold:
             n_elements = hashmap.n_elements
             if n_elements + n_sel > hashmap.n_buckets * hashmap._rehash_threshold:
                 hashmap.rehash(math.ceil((n_elements + n_sel) * hashmap._rehash_factor))
@@ -298,7 +298,7 @@ class SparseDOKTensor(object):
                                               src_strides, L.ptr(scratch), epoch, None, L.stream_ptr(self.device)),
                     "dok_dok_set_dense")
         hashmap._n_elements += n_sel - n_existing             # duplicates over-count, like the reference (:474)
-        hashmap._shared["bound"] += n_sel
+        hashmap._after_mutation(n_sel)
 
     def zero_items(self, selectors):
         """Removes the selected positions that are stored; returns how many (sparse_dok_tensor_impl.py:110-146)."""
@@ -312,6 +312,7 @@ class SparseDOKTensor(object):
             L.check(L.lib().dok_dok_zero_items(hashmap._c_table(), hashmap._c_hash(), ctypes.byref(sel), L.ptr(cnt),
                                                L.stream_ptr(self.device)), "dok_dok_zero_items")
         hashmap._n_elements -= cnt[L.CNT_HITS]
+        hashmap._after_mutation(0)
         return int(cnt[L.CNT_HITS].item())
 
     # ------------------------------------------------------------------ views and reshapes

@@ -248,6 +248,11 @@ int dok_shard_partition_scatter(const dok_hash_params *hp, const void *keys, con
 int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found, const int64_t *dest_index,
                         int value_bytes, int64_t n, void *out_values, uint8_t *out_found, void *stream);
 
+/* Diagnostic: n_reads independent random 16-byte reads over buf[0, bytes) (one per thread).  Timed by the caller,
+ * it gives the rate at which this GPU serves random requests; for buffers much larger than L2 that rate bounds
+ * every probing kernel.  sink may be NULL.  No counterpart in the reference. */
+int dok_diag_random_reads(const void *buf, int64_t bytes, int64_t n_reads, uint64_t seed, int64_t *sink, void *stream);
+
 /* owner_out[i] = owner shard of row i (diagnostics; the partition computes the same value internally) */
 int dok_shard_owner(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, int32_t *owner_out,
                     void *stream);
