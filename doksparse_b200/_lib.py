@@ -86,6 +86,8 @@ def _declare(lib):
         "dok_map_remove": ([TP, HP, P, I64, P, P, P], I),
         "dok_map_count_exists": ([TP, HP, P, I64, P, P, P], I),
         "dok_map_count_new": ([TP, HP, P, I64, P, I64, P, P], I),
+        "dok_static_scratch_max_rows": ([], I64),
+        "dok_map_count_new_static": ([TP, HP, P, I64, P, P], I),
         "dok_compact_tiles": ([I64], I64),
         "dok_map_compact_count": ([TP, P, P], I),
         "dok_map_compact_scatter": ([TP, HP, P, P, I, P, P, P], I),

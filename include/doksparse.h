@@ -184,6 +184,17 @@ int dok_map_count_exists(const dok_table *t, const dok_hash_params *hp, const vo
 int dok_map_count_new(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
                       int64_t *scratch_tags, int64_t scratch_slots, int64_t *counters, void *stream);
 
+/* dok_map_count_new without a caller-supplied scratch buffer (no counterpart in the reference, and none among
+ * the entry points above: it exists for hosts that cannot allocate).  The tag set lives in a fixed 8 MiB array
+ * inside the library image, held by every GPU that loads the library.  n may not exceed
+ * dok_static_scratch_max_rows() (2^19): larger batches return DOK_TOO_LARGE and launch nothing.  The first call
+ * on a device resolves the array's device address; make it before any stream capture.  All calls on a device
+ * share the array: each refills what it uses, and calls that overlap on the GPU race.  Never calls cudaMalloc,
+ * cudaFree or another allocating routine.  Adds the count to counters[DOK_CNT_CLAIMED_EMPTY]. */
+int64_t dok_static_scratch_max_rows(void);
+int dok_map_count_new_static(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
+                             int64_t *counters, void *stream);
+
 /* Live-slot compaction in slot order (replaces nonempty_mask + the boolean-mask gathers of
  * cuda_closed_hashmap.py:157-172, 233-234).  Step 1 counts per tile and scans:
  *   tile_offsets: device int64[dok_compact_tiles(n_buckets) + 1]; the last element is the live count.
