@@ -6,6 +6,10 @@
 
 #define DOK_PART_ROUNDS 8
 #define DOK_PART_TILE (DOK_TPB * DOK_PART_ROUNDS)
+// Every owner's segment starts on a multiple of this many rows, so that it starts 16-byte aligned whatever the row
+// width (NCCL moves unaligned segments several times slower).  The rows of the gap behind a segment are not
+// written; the receiver learns the exact row count of each segment and ignores them.
+#define DOK_SEGMENT_ALIGN_ROWS 16
 
 __device__ __forceinline__ void dok_copy_row(char *dst, const char *src, int bytes) {
   if ((bytes & 7) == 0) for (int i = 0; i < (bytes >> 3); i++) ((ull_t *)dst)[i] = ((const ull_t *)src)[i];
@@ -48,17 +52,31 @@ static __global__ void __launch_bounds__(1024) k_part_scan(ll_t *a, ll_t n) {
   for (ll_t i = lo; i < hi; i++) { const ll_t v = a[i]; a[i] = run; run += v; }
 }
 
+// shard_counts[0 .. P) = rows per owner, shard_counts[P .. 2P) = the same rounded up to whole alignment units
 static __global__ void k_part_shard_counts(const ll_t *tile_offsets, int n_shards, ll_t tiles, ll_t *shard_counts) {
   const int o = threadIdx.x;
-  if (o < n_shards) shard_counts[o] = tile_offsets[(ll_t)(o + 1) * tiles] - tile_offsets[(ll_t)o * tiles];
+  if (o < n_shards) {
+    const ll_t c = tile_offsets[(ll_t)(o + 1) * tiles] - tile_offsets[(ll_t)o * tiles];
+    shard_counts[o] = c;
+    shard_counts[n_shards + o] = (c + DOK_SEGMENT_ALIGN_ROWS - 1) / DOK_SEGMENT_ALIGN_ROWS * DOK_SEGMENT_ALIGN_ROWS;
+  }
 }
 
 static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(DevHash hp, RowKeys keys, const char *__restrict__ values,
                                                                  int vb, int n_shards, ll_t tiles,
-                                                                 const ll_t *__restrict__ tile_offsets, char *keys_out,
+                                                                 const ll_t *__restrict__ tile_offsets,
+                                                                 const ll_t *__restrict__ shard_counts, char *keys_out,
                                                                  char *values_out, ll_t *__restrict__ dest_index) {
   __shared__ int warp_count[DOK_TPB / 32][DOK_MAX_SHARDS];
   __shared__ int running[DOK_MAX_SHARDS];
+  __shared__ ll_t seg_shift[DOK_MAX_SHARDS];      // padded start of an owner's segment minus its unpadded start
+  if (threadIdx.x == 0) {
+    ll_t padded = 0;
+    for (int o = 0; o < n_shards; o++) {
+      seg_shift[o] = padded - tile_offsets[(ll_t)o * tiles];
+      padded += shard_counts[n_shards + o];
+    }
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kb = hp.ks * hp.elem_bytes;
   for (int i = threadIdx.x; i < (DOK_TPB / 32) * DOK_MAX_SHARDS; i += DOK_TPB) (&warp_count[0][0])[i] = 0;
@@ -75,7 +93,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(DevHash hp, Row
     if (owner >= 0) {
       int before = running[owner] + rank;
       for (int w = 0; w < warp; w++) before += warp_count[w][owner];
-      const ll_t dest = tile_offsets[(ll_t)owner * tiles + blockIdx.x] + before;
+      const ll_t dest = tile_offsets[(ll_t)owner * tiles + blockIdx.x] + seg_shift[owner] + before;
       dest_index[e] = dest;
       dok_copy_row(keys_out + dest * kb, (const char *)keys.keys + e * kb, kb);
       if (values) dok_copy_row(values_out + dest * vb, values + e * vb, vb);
@@ -104,6 +122,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_unpermute(const char *__rest
 extern "C" {
 
 int64_t dok_partition_tiles(int64_t n) { return (n + DOK_PART_TILE - 1) / DOK_PART_TILE; }
+int64_t dok_partition_capacity(int64_t n, int n_shards) { return n + (int64_t)n_shards * (DOK_SEGMENT_ALIGN_ROWS - 1); }
 
 int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards,
                               int64_t *tile_offsets, int64_t *shard_counts, void *stream) {
@@ -126,18 +145,18 @@ int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64
 }
 
 int dok_shard_partition_scatter(const dok_hash_params *hp, const void *keys, const void *values, int value_bytes,
-                                int64_t n, int n_shards, const int64_t *tile_offsets, void *keys_out, void *values_out,
-                                int64_t *dest_index, void *stream) {
+                                int64_t n, int n_shards, const int64_t *tile_offsets, const int64_t *shard_counts,
+                                void *keys_out, void *values_out, int64_t *dest_index, void *stream) {
   DevHash dh;
   if (!dok_make_hash(hp, &dh) || n < 0 || n > DOK_MAX_BATCH || n_shards < 1 || n_shards > DOK_MAX_SHARDS) return DOK_BAD_ARG;
   if (n == 0) return DOK_OK;
-  if (!keys || !tile_offsets || !keys_out || !dest_index) return DOK_BAD_ARG;
+  if (!keys || !tile_offsets || !shard_counts || !keys_out || !dest_index) return DOK_BAD_ARG;
   if (values && (!values_out || value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES)) return DOK_BAD_ARG;
   const ll_t tiles = dok_partition_tiles(n);
   RowKeys rk{keys, n};
   k_part_scatter<<<(unsigned)tiles, DOK_TPB, 0, (cudaStream_t)stream>>>(
-      dh, rk, (const char *)values, value_bytes, n_shards, tiles, (const ll_t *)tile_offsets, (char *)keys_out,
-      (char *)values_out, (ll_t *)dest_index);
+      dh, rk, (const char *)values, value_bytes, n_shards, tiles, (const ll_t *)tile_offsets, (const ll_t *)shard_counts,
+      (char *)keys_out, (char *)values_out, (ll_t *)dest_index);
   return dok_check_launch();
 }
 

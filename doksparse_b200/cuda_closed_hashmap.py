@@ -283,14 +283,18 @@ class CudaClosedHashmap:
         snaps = sh["snapshots"]
         for s in snaps:
             s[2] += added                       # rows that may have been inserted after that snapshot was taken
-        host = torch.empty((), dtype=torch.long, pin_memory=True)
+        ring = sh.get("ring")
+        if ring is None:
+            ring = sh["ring"] = torch.zeros(8, dtype=torch.long, pin_memory=True)
+        free = set(range(ring.numel())) - {s[1] for s in snaps}
+        if not free:
+            return                              # eight copies still in flight: skip this one, the bound stays valid
+        slot = free.pop()
         with torch.cuda.device(self.device):
-            host.copy_(self._n_elements, non_blocking=True)
+            ring[slot:slot + 1].copy_(self._n_elements.reshape(1), non_blocking=True)
             event = torch.cuda.Event()
             event.record()
-        snaps.append([event, host, 0])
-        if len(snaps) > 8:
-            del snaps[0]
+        snaps.append([event, slot, 0])
 
     def _element_bound(self):
         sh = self._shared
@@ -299,8 +303,7 @@ class CudaClosedHashmap:
         while snaps and snaps[0][0].query():
             newest = snaps.pop(0)
         if newest is not None:
-            sh["bound"] = min(sh["bound"], int(newest[1].item()) + newest[2])
-            snaps.insert(0, newest)             # keep it: it stays the newest completed one until another lands
+            sh["bound"] = min(sh["bound"], int(sh["ring"][newest[1]]) + newest[2])
         return sh["bound"]
 
     # ------------------------------------------------------------------ compaction
@@ -539,7 +542,12 @@ class CudaClosedHashmap:
         self._materialise_parameters()
         limit = int(self._rehash_threshold * self.n_buckets)
         row_counted = new_keys.dtype in L.FLOAT_DTYPES
-        if not row_counted and self._element_bound() + n <= limit:
+        fast = not row_counted and self._element_bound() + n <= limit
+        if not fast and not row_counted:
+            # the bound may only be stale (the host runs ahead of the device): fetch the exact count before paying
+            # for a pass that counts the distinct new keys
+            fast = self.n_elements + n <= limit
+        if fast:
             # whatever the number of new keys is, the reference would not rehash: insert and count on the device
             cnt = self._launch_set(new_keys, new_values, assume_unique)
             self._n_elements += cnt[L.CNT_CLAIMED_EMPTY] + cnt[L.CNT_REUSED_REMOVED]

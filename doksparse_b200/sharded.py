@@ -5,7 +5,7 @@ table that received the ranks' batches concatenated in rank order.
 
 Per batch and rank:
   1. stable partition of the local rows by owner shard, owner = mulhi(mix(uuid ^ salt), world)  (CUDA kernels)
-  2. exchange of the per-owner row counts                                   (all_to_all_single, world int64)
+  2. exchange of the per-owner row counts (exact and padded to 16 rows)        (all_to_all_single, 2*world int64)
   3. exchange of key rows (and value rows for set)                          (all_to_all_single, NCCL over NVLink)
   4. the owner runs the local get / set / remove on what it received -- rows arrive grouped by source rank, in
      the source's order, so "last row wins" on the owner is "last row wins" of the concatenated batch
@@ -54,28 +54,32 @@ class CudaShardOps:
         return ctypes.byref(self._hp)
 
     def partition(self, keys, values, world):
-        """-> (grouped_keys, grouped_values or None, dest_index, counts[world] on the device)"""
+        """-> (grouped_keys, grouped_values or None, dest_index, counts[2, world] on the device): rows per owner, and
+        the same rounded up to multiples of 16 rows.  Owner o's segment starts at the sum of the ROUNDED counts before
+        it, so that every segment is 16-byte aligned for the exchange (NCCL moves unaligned segments ~2.6x slower);
+        the rows of the gap are never used by the receiver."""
         lib = L.lib()
         n = keys.shape[0]
         keys = keys.contiguous()
         with torch.cuda.device(self.device):
             st = L.stream_ptr(self.device)
             tiles = lib.dok_partition_tiles(n)
+            cap = lib.dok_partition_capacity(n, world)
             offsets = torch.empty(world * tiles + 1, device=self.device, dtype=torch.long)
-            counts = torch.empty(world, device=self.device, dtype=torch.long)
+            counts = torch.empty(2 * world, device=self.device, dtype=torch.long)
             L.check(lib.dok_shard_partition_count(self._routing_hash(keys), L.ptr(keys), n, world, L.ptr(offsets),
                                                   L.ptr(counts), st), "dok_shard_partition_count")
-            grouped_keys = torch.empty_like(keys)
+            grouped_keys = torch.empty((cap,) + tuple(keys.shape[1:]), device=self.device, dtype=keys.dtype)
             grouped_values, vb = None, 0
             if values is not None:
                 values = values.contiguous()
-                grouped_values = torch.empty_like(values)
-                vb = values[0].numel() * values.element_size() if n else values.element_size()
+                grouped_values = torch.empty((cap,) + tuple(values.shape[1:]), device=self.device, dtype=values.dtype)
+                vb = int(np.prod(values.shape[1:])) * values.element_size()
             dest = torch.empty(n, device=self.device, dtype=torch.long)
             L.check(lib.dok_shard_partition_scatter(self._routing_hash(keys), L.ptr(keys), L.ptr(values), vb, n, world,
-                                                    L.ptr(offsets), L.ptr(grouped_keys), L.ptr(grouped_values),
-                                                    L.ptr(dest), st), "dok_shard_partition_scatter")
-        return grouped_keys, grouped_values, dest, counts
+                                                    L.ptr(offsets), L.ptr(counts), L.ptr(grouped_keys),
+                                                    L.ptr(grouped_values), L.ptr(dest), st), "dok_shard_partition_scatter")
+        return grouped_keys, grouped_values, dest, counts.view(2, world)
 
     def unpermute(self, grouped_values, grouped_flags, dest):
         lib = L.lib()
@@ -84,23 +88,38 @@ class CudaShardOps:
         vb = 0
         with torch.cuda.device(self.device):
             if grouped_values is not None:
-                out_v = torch.empty_like(grouped_values)
-                vb = grouped_values[0].numel() * grouped_values.element_size() if n else 1
+                out_v = torch.empty((n,) + tuple(grouped_values.shape[1:]), device=self.device, dtype=grouped_values.dtype)
+                vb = int(np.prod(grouped_values.shape[1:])) * grouped_values.element_size()
             if grouped_flags is not None:
-                out_f = torch.empty_like(grouped_flags)
+                out_f = torch.empty(n, device=self.device, dtype=grouped_flags.dtype)
             L.check(lib.dok_shard_unpermute(L.ptr(grouped_values), L.ptr(grouped_flags), L.ptr(dest), vb, n, L.ptr(out_v),
                                             L.ptr(out_f), L.stream_ptr(self.device)), "dok_shard_unpermute")
         return out_v, out_f
 
-    # local table ops on the rows this rank owns
-    def local_get(self, keys, fallback_value):
-        return self.local.get(keys, fallback_value)
+    # local table ops on the rows this rank owns.  `segments` = [(start, rows)] per source rank inside the received
+    # buffer (starts are aligned, the gaps hold nothing); sources are processed in rank order, which is what makes
+    # "last row wins" global.
+    def local_get(self, keys, segments, fallback_value):
+        values = torch.empty((keys.shape[0],) + tuple(self.local.value_shape), device=self.device, dtype=self.local.value_type)
+        found = torch.zeros(keys.shape[0], device=self.device, dtype=torch.bool)
+        for start, rows in segments:
+            if rows:
+                v, f = self.local.get(keys[start:start + rows], fallback_value)
+                values[start:start + rows] = v
+                found[start:start + rows] = f
+        return values, found
 
-    def local_set(self, keys, values, assume_unique):
-        self.local.set(keys, values, assume_unique=assume_unique)
+    def local_set(self, keys, values, segments, assume_unique):
+        for start, rows in segments:
+            if rows:
+                self.local.set(keys[start:start + rows], values[start:start + rows], assume_unique=assume_unique)
 
-    def local_remove(self, keys):
-        return self.local.remove_rows(keys)
+    def local_remove(self, keys, segments):
+        flags = torch.zeros(keys.shape[0], device=self.device, dtype=torch.bool)
+        for start, rows in segments:
+            if rows:
+                flags[start:start + rows] = self.local.remove_rows(keys[start:start + rows])
+        return flags
 
     def local_n_elements(self):
         return self.local._n_elements
@@ -137,15 +156,14 @@ class ShardedClosedHashmap:
         self._value_dtype = None
 
     # ------------------------------------------------------------------ exchange plumbing
-    def _exchange_counts(self, send_counts):
-        """send_counts[world] (device) -> (send list, recv list) on the host; one synchronisation per batch."""
-        if self.world == 1:
-            c = [int(send_counts[0].item())]
-            return c, c
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        both = torch.stack([send_counts, recv_counts]).cpu().tolist()
-        return [int(x) for x in both[0]], [int(x) for x in both[1]]
+    def _exchange_counts(self, counts):
+        """counts[2, world] (device; rows and padded rows per owner) -> (send_padded, recv_rows, recv_padded) as host
+        lists; one synchronisation per batch."""
+        send = counts.t().contiguous()                       # [world, 2]: what goes to each owner
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        both = torch.stack([send, recv]).cpu().tolist()
+        return [int(c[1]) for c in both[0]], [int(c[0]) for c in both[1]], [int(c[1]) for c in both[1]]
 
     def _all_to_all_rows(self, rows, send, recv):
         """rows grouped by destination -> rows grouped by source."""
@@ -156,30 +174,32 @@ class ShardedClosedHashmap:
         return out
 
     def _route(self, keys, values=None):
+        """-> (owned_keys, owned_values, segments, dest, send, recv); segments = [(start, rows)] per source rank."""
         if self.world == 1:        # one shard owns everything: no partition, no exchange, no permutation
-            return keys, values, None, None, None
+            return keys, values, [(0, keys.shape[0])], None, None, None
         grouped_keys, grouped_values, dest, counts = self.ops.partition(keys, values, self.world)
-        send, recv = self._exchange_counts(counts)
-        assert sum(send) == keys.shape[0], "partition lost rows"
-        owned_keys = self._all_to_all_rows(grouped_keys, send, recv)
-        owned_values = None if values is None else self._all_to_all_rows(grouped_values, send, recv)
-        return owned_keys, owned_values, dest, send, recv
+        send, recv_rows, recv = self._exchange_counts(counts)
+        assert keys.shape[0] <= sum(send) <= grouped_keys.shape[0], "partition lost rows"
+        owned_keys = self._all_to_all_rows(grouped_keys[:sum(send)], send, recv)
+        owned_values = None if values is None else self._all_to_all_rows(grouped_values[:sum(send)], send, recv)
+        starts = [sum(recv[:i]) for i in range(self.world)]
+        return owned_keys, owned_values, list(zip(starts, recv_rows)), dest, send, recv
 
     # ------------------------------------------------------------------ operations
     def set(self, keys, values, assume_unique=False):
         """Collective insert-or-assign.  `assume_unique` promises pairwise different keys across ALL ranks' batches."""
         if self._value_shape is None:
             self._value_shape, self._value_dtype = tuple(values.shape[1:]), values.dtype
-        owned_keys, owned_values, _, _, _ = self._route(keys, values)
-        self.ops.local_set(owned_keys, owned_values, assume_unique)
+        owned_keys, owned_values, segments, _, _, _ = self._route(keys, values)
+        self.ops.local_set(owned_keys, owned_values, segments, assume_unique)
 
     def get(self, keys, fallback_value=None):
         """Collective lookup -> (values[n, *value_shape], is_found[n]) in the caller's row order."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
-        owned_keys, _, dest, send, recv = self._route(keys)
+        owned_keys, _, segments, dest, send, recv = self._route(keys)
         if self.ops.ready() and owned_keys.shape[0]:
-            owned_values, owned_found = self.ops.local_get(owned_keys, fallback_value)
+            owned_values, owned_found = self.ops.local_get(owned_keys, segments, fallback_value)
         else:
             # this shard holds nothing yet (or received nothing): every row it was asked about is a miss
             owned_values = self.ops.empty((owned_keys.shape[0],) + self._value_shape, self._value_dtype)
@@ -199,9 +219,9 @@ class ShardedClosedHashmap:
         """Collective removal -> is_removed[n] aligned to the caller's rows (equal keys report once)."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
-        owned_keys, _, dest, send, recv = self._route(keys)
+        owned_keys, _, segments, dest, send, recv = self._route(keys)
         if self.ops.ready() and owned_keys.shape[0]:
-            owned_flags = self.ops.local_remove(owned_keys)
+            owned_flags = self.ops.local_remove(owned_keys, segments)
         else:
             owned_flags = self.ops.empty((owned_keys.shape[0],), torch.bool)
             owned_flags[:] = False

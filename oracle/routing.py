@@ -63,21 +63,26 @@ class OracleShardOps:
         owner = owners(self._uuids(keys), world)
         order, dest, counts = stable_partition(owner, world)
         order_t = torch.from_numpy(order)
+        counts_t = torch.from_numpy(counts)
+        # the host stand-in does not pad segments (gloo needs no alignment): exact and padded counts coincide
         return (keys[order_t], None if values is None else values[order_t], torch.from_numpy(dest),
-                torch.from_numpy(counts))
+                torch.stack([counts_t, counts_t]))
 
     def unpermute(self, grouped_values, grouped_flags, dest):
         return (None if grouped_values is None else grouped_values[dest],
                 None if grouped_flags is None else grouped_flags[dest])
 
-    def local_get(self, keys, fallback_value):
+    def local_get(self, keys, segments, fallback_value):
+        assert sum(rows for _, rows in segments) == keys.shape[0]
         v, f = self.local.get(keys.numpy(), fallback_value)
         return torch.from_numpy(v), torch.from_numpy(f)
 
-    def local_set(self, keys, values, assume_unique):
-        self.local.set(keys.numpy(), values.numpy())
+    def local_set(self, keys, values, segments, assume_unique):
+        for start, rows in segments:            # sources in rank order
+            if rows:
+                self.local.set(keys[start:start + rows].numpy(), values[start:start + rows].numpy())
 
-    def local_remove(self, keys):
+    def local_remove(self, keys, segments):
         return torch.from_numpy(self.local.remove_rows(keys.numpy()))
 
     def local_n_elements(self):

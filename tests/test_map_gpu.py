@@ -278,6 +278,33 @@ def test_duplicates_last_row_wins_across_blocks():
     p.check_items()
 
 
+def test_mixed_churn_skewed_keys_high_load():
+    """BASELINE config 4 at reduced size: int64 ids with a heavy-tailed (Pareto, shape 0.99) distribution -> float32[4],
+    table driven to ~0.85 load with rehash_threshold 0.95, then batches of 70 % get / 20 % set / 10 % remove.  Batches
+    are full of repeated ids, so this exercises last-row-wins, tombstone reuse and long chains; everything observable
+    equals the serial oracle after every batch.  (The NUMBER of tombstones may differ: which tombstone a set reuses
+    depends on the slot layout.)"""
+    rng = np.random.default_rng(4)
+    nb = 1 << 16
+    p = Pair(seed=44, n_buckets=nb, rehash_threshold=0.95)
+    fill = rng.permutation(1 << 22)[: int(0.85 * nb)].astype(np.int64)[:, None]
+    p.set(fill, rng.standard_normal((len(fill), 4)).astype(np.float32))
+    assert p.c.n_buckets == nb
+
+    def skewed(n):
+        return (rng.pareto(0.99, size=n) * 50).astype(np.int64)[:, None] % (1 << 22)
+
+    for batch in range(6):
+        p.get(np.concatenate([skewed(14_000), fill[rng.integers(0, len(fill), 14_000)]]))
+        sk = skewed(8_000)
+        p.set(sk, rng.standard_normal((len(sk), 4)).astype(np.float32))
+        p.remove(np.concatenate([skewed(2_000), fill[rng.integers(0, len(fill), 2_000)]]))
+        p.check_items()
+        assert p.c.n_buckets == nb and p.c.n_tombstones > 0
+    probes, hit_rate = p.c.probe_stats(dev(fill))
+    assert probes >= 1.0 and 0.5 < hit_rate <= 1.0
+
+
 def test_key_perm_views_share_storage():
     """A shallow clone with another key_perm sees the same slots with permuted key columns
     (cuda_closed_hashmap.py:213-231, closed_hashmap_impl_class.cu:54-63, 144-150)."""
