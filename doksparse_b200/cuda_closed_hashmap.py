@@ -563,7 +563,9 @@ class CudaClosedHashmap:
         self._shared["bound"] = n_elements + n_new
 
     # ------------------------------------------------------------------ get
-    def get(self, keys, fallback_value=None):
+    def get(self, keys, fallback_value=None, values=None, is_found=None):
+        """`values` / `is_found`: optional preallocated outputs (contiguous, [n, *value_shape] and bool [n]), like the
+        `values=` argument of the reference launcher (closed_hashmap_impl.py:63)."""
         if self._slots is None:
             raise RuntimeError("store something first")
         if keys.shape[0] == 0:
@@ -580,8 +582,15 @@ class CudaClosedHashmap:
             fb = ctypes.c_void_p(fb_host.data_ptr())
         keys = keys.contiguous()
         n = keys.shape[0]
-        values = torch.empty(n, *self.value_shape, device=self.device, dtype=self._value_dtype)
-        is_found = torch.empty(n, device=self.device, dtype=torch.bool)
+        if values is None:
+            values = torch.empty(n, *self.value_shape, device=self.device, dtype=self._value_dtype)
+        else:
+            assert values.dtype == self._value_dtype and values.device == self.device and values.is_contiguous()
+            assert values.shape == (n, *self.value_shape)
+        if is_found is None:
+            is_found = torch.empty(n, device=self.device, dtype=torch.bool)
+        else:
+            assert is_found.dtype == torch.bool and is_found.shape == (n,) and is_found.is_contiguous()
         with torch.cuda.device(self.device):
             L.check(L.lib().dok_map_get(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(values), L.ptr(is_found),
                                         fb, None, L.stream_ptr(self.device)), "dok_map_get")
