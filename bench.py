@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--impl", choices=["candidate", "reference"], default="candidate")
     ap.add_argument("--keys-log2", type=int, default=28, help="stored keys per GPU (default 2^28)")
     ap.add_argument("--batch-log2", type=int, default=25, help="queries per GPU and step (default 2^25 = 32 Mi)")
+    ap.add_argument("--no-ref-gpu", action="store_true",
+                    help="reference arm: skip the extra leg that runs the reference's kernels on the GPU")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -220,11 +222,85 @@ def cpu_arm(steps, warmup, sample_keys_log2=24, sample_batch_log2=22, budget_s=N
     return mops, dt / max(done, 1) * 1e3, desc
 
 
+def reference_kernels_on_gpu(args, steps=5, warmup=3):
+    """The reference's own get / set / remove kernels (its kernel text compiled ahead of time by nvcc, since CuPy is
+    not available) on cuda:0, on this bench's per-GPU workload: same table size and load, same batch construction,
+    same operation order.  Kernels only -- the reference's Python bookkeeping around them (a pre-get, a row-sort
+    unique and host synchronisations per set; a unique per remove) is left out, which favours the reference.
+    Returns a dict for the JSON line, or a reason string when it cannot run here."""
+    try:
+        import torch
+        from oracle import ref_gpu
+    except Exception as exc:                                    # pragma: no cover
+        return f"import failed: {exc}"
+    if not torch.cuda.is_available():
+        return "no GPU"
+    if not ref_gpu.available(torch.int64, 1, torch.float32, 2):
+        return "oracle/_ref/refgpu_map_i64x1_f32x2.so not built"
+    device = torch.device("cuda", 0)
+    n_keys, q = 1 << args.keys_log2, 1 << args.batch_log2
+    nb = int(n_keys / LOAD_FACTOR)
+    if nb * 2 > ref_gpu.RefGpuMap.MAX_ELEMENTS:
+        return "table beyond the reference's 32-bit bucket indices"
+    table = ref_gpu.RefGpuMap(nb, torch.int64, 1, torch.float32, 2, dict(fixed_parameters(), key_perm=[0]), device)
+    chunk = min(n_keys, 1 << 25)
+    for lo in range(0, n_keys, chunk):
+        idx = torch.arange(lo, lo + chunk, device=device, dtype=torch.long)
+        table.set(mix62_torch(idx)[:, None].contiguous(), value_of_index(idx, torch).contiguous())
+    n_hit = int(q * HIT_FRACTION)
+    g = torch.Generator(device=device).manual_seed(1234)
+    batches = []
+    for b in range(N_BATCHES):
+        j = torch.arange(n_hit, device=device, dtype=torch.long)
+        hit_idx = (j * 7919 + 104729 * (b + 1)) % n_keys
+        miss_idx = (1 << 40) + (b << 32) + torch.arange(q - n_hit, device=device, dtype=torch.long)
+        new_idx = (1 << 41) + (b << 32) + torch.arange(q - n_hit, device=device, dtype=torch.long)
+        perm = torch.randperm(q, device=device, generator=g)
+        get_idx, set_idx = torch.cat([hit_idx, miss_idx])[perm], torch.cat([hit_idx, new_idx])[perm]
+        batches.append((mix62_torch(get_idx)[:, None].contiguous(), get_idx, mix62_torch(set_idx)[:, None].contiguous(),
+                        value_of_index(set_idx, torch).contiguous(), mix62_torch(new_idx)[:, None].contiguous()))
+
+    def step(b, events=None):
+        gk, _, sk, sv, fk = batches[b % N_BATCHES]
+        marks = []
+        for fn in (lambda: table.get(gk), lambda: table.set(sk, sv), lambda: table.remove(fk), None):
+            if events is not None:
+                marks.append(torch.cuda.Event(enable_timing=True)); marks[-1].record()
+            if fn is not None:
+                fn()
+        if events is not None:
+            events.append(marks)
+
+    values, found = table.get(batches[0][0])
+    expect = batches[0][1] < (1 << 40)
+    ok = bool(torch.equal(found, expect)) and bool(torch.equal(values[expect], value_of_index(batches[0][1][expect], torch)))
+    for s in range(warmup):
+        step(s)
+    torch.cuda.synchronize()
+    events = []
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for s in range(steps):
+        step(warmup + s, events)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    phase = [sum(m[i].elapsed_time(m[i + 1]) for m in events) / steps for i in range(3)]
+    live = int(((table.all_uuids != -1) & (table.all_uuids != -3)).sum().item())
+    return {"value": 2 * q / (ms * 1e-3) / 1e6, "unit": "Mops/s", "ms_per_step": ms,
+            "get_ms": phase[0], "set_ms": phase[1], "remove_ms": phase[2], "steps": steps, "results_ok": ok,
+            "live_keys_after": live, "live_keys_expected": n_keys,
+            "what": "the reference's closed_hashmap_get/set/remove kernels (closed_hashmap_impl.cu), nvcc -O3 for sm_100a, "
+                    "launched like closed_hashmap_impl.py does, incl. its output allocation and fallback fill; "
+                    "no Python-side pre-get / unique / rehash logic"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     mops, ms, desc = cpu_arm(args.steps, args.warmup)
+    gpu_leg = None if args.no_ref_gpu else reference_kernels_on_gpu(args)
     line = {
         "impl": "reference", "metric": "hashmap get/set Mops/s", "value": mops, "unit": "Mops/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -233,6 +309,8 @@ def run_reference(args):
         "cpu_baseline": desc,
         "e2e": {"value": mops, "unit": "Mops/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        # extra: the same reference kernel text run on this box's GPU (kernel-only, 1 GPU); not the line's value
+        "reference_kernels_gpu": gpu_leg,
     }
     print(json.dumps(line))
 

@@ -295,17 +295,21 @@ __device__ __forceinline__ void dok_load_words(const char *p, ull_t (&w)[LW]) {
 }
 
 // The same walk for the 32 keys of a warp, one 128-byte group per request.  Lane i owns key i.  The four lanes of
-// a quad serve the quad's four keys in turn: each lane loads the first LW words of its 32 bytes of the key's
-// current group (one coalesced request for the line: 1 word = the tags only, 2 = tag and an 8-byte value, 4 =
-// everything), the quad ORs its match / empty / tombstone bits together, and the owner lane interprets them in
-// slot order.  The first groups of the quad's four keys are requested back to back before any is inspected; keys
-// whose chain runs into a further group (few below 90 % load) are finished in a loop.
+// a quad serve the quad's four keys together, in PASSES: in a pass each lane loads, for every key of the quad that
+// is still unresolved, the first LW words of its 32 bytes of that key's current group (one coalesced request per
+// line: 1 word = the tags only, 2 = tag and an 8-byte value, 4 = everything; all requests of a pass are issued
+// before any answer is looked at), compares its tag, and packs one match bit and one empty bit per key and slot
+// into ONE 32-bit word (byte r = key r: bits 0-3 match, bits 4-7 empty, by slot).  Two xor-shuffles OR the quad's
+// words together; every lane then knows the outcome of all four keys, and the owner lanes advance their own
+// state once per pass.  With TOMB the tombstone bits travel in a second word (set needs them, lookups do not).
+// The number of dependent memory round trips of a warp is the longest chain among its 32 keys (in groups), and
+// rounds in which no quad of the warp has work are skipped (the decision is warp-uniform).
 // On a hit, `emit(e_r, slot_in_group, words)` runs on all four lanes while they still hold the line: e_r is the
 // batch element of the key, words the calling lane's chunk.
 // Every lane of the warp must call this (inactive lanes pass active = false), with CONSECUTIVE batch elements e in
 // consecutive lanes.  SB = slot bytes (32, 64, 128).  Slot indices are 32-bit here: the host refuses cooperative
 // tables of 2^32 - 1 slots or more.
-template <int SB, int LW, class Emit>
+template <int SB, int LW, bool TOMB, class Emit>
 __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyHash &kh, ll_t e, bool active,
                                                    int *probes, const Emit &emit) {
   constexpr int SPG = 128 / SB;
@@ -322,43 +326,65 @@ __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyH
   unsigned group = active ? (unsigned)dok_start_group(kh, t) : NONE;
   unsigned walked = 0;
 
-  // one step for the key owned by lane r of the quad: g_r is its current group (or NONE), w this lane's chunk of it
-  auto resolve = [&](const ull_t (&w)[LW], unsigned g_r, ll_t uuid_r, unsigned r) {
-    const ll_t tag = (has_tag && g_r != NONE) ? (ll_t)w[0] : DOK_BLOCKED;
-    unsigned bits = ((unsigned)(tag == uuid_r) | ((unsigned)(tag == DOK_EMPTY) << 4) | ((unsigned)(tag == DOK_REMOVED) << 8)) << my_slot;
-    bits |= __shfl_xor_sync(FULL, bits, 1);
-    bits |= __shfl_xor_sync(FULL, bits, 2);
-    const unsigned m = bits & 0xfu, me = (bits | (bits >> 4)) & 0xfu, tb = (bits >> 8) & 0xfu;
+  // what the owner lane does with the outcome of one inspected group: m / me / tb = match, match-or-empty and
+  // tombstone bits by slot
+  auto advance = [&](unsigned m, unsigned me, unsigned tb) {
     const int pos = me ? __ffs(me) - 1 : -1;
-    const bool hit = pos >= 0 && ((m >> pos) & 1u);
-    if (hit) emit(e_quad + r, pos, w);
-    if (l == r && group != NONE) {
-      const unsigned first_slot = group * SPG;
-      walked++;
-      if (tomb == NONE) {
-        const unsigned before = pos >= 0 ? (tb & ((1u << pos) - 1u)) : tb;
-        if (before) tomb = first_slot + __ffs(before) - 1;
-      }
-      if (pos >= 0) {
-        if (hit) found = first_slot + pos; else empty = first_slot + pos;
-        group = NONE;
-      } else {
-        group = (group + 1 == n_groups) ? 0u : group + 1;
-        if (walked == n_groups) group = NONE;           // every group inspected: no empty slot anywhere
-      }
+    const unsigned first_slot = group * SPG;
+    walked++;
+    if (TOMB && tomb == NONE) {
+      const unsigned before = pos >= 0 ? (tb & ((1u << pos) - 1u)) : tb;
+      if (before) tomb = first_slot + __ffs(before) - 1;
+    }
+    if (pos >= 0) {
+      if ((m >> pos) & 1u) found = first_slot + pos; else empty = first_slot + pos;
+      group = NONE;
+    } else {
+      group = (group + 1 == n_groups) ? 0u : group + 1;
+      if (walked == n_groups) group = NONE;           // every group inspected: no empty slot anywhere
     }
   };
 
-  ull_t w[4][LW];
-  unsigned g[4];
+  // ---- first groups of the quad's four keys: four requests in flight, one packed exchange
+  {
+    ull_t w[4][LW];
+    unsigned g[4];
 #pragma unroll
-  for (unsigned r = 0; r < 4; r++) {
-    g[r] = __shfl_sync(FULL, group, base + r);
-    if (g[r] != NONE) dok_load_words<LW>(my_base + (ull_t)g[r] * 128u, w[r]);
+    for (unsigned r = 0; r < 4; r++) {
+      g[r] = __shfl_sync(FULL, group, base + r);
+      if (g[r] != NONE) dok_load_words<LW>(my_base + (ull_t)g[r] * 128u, w[r]);
+    }
+    unsigned bits = 0, tbits = 0;
+#pragma unroll
+    for (unsigned r = 0; r < 4; r++) {
+      const ll_t uuid_r = __shfl_sync(FULL, kh.uuid, base + r);
+      if (has_tag && g[r] != NONE) {
+        const ll_t tag = (ll_t)w[r][0];
+        bits |= ((unsigned)(tag == uuid_r) | ((unsigned)(tag == DOK_EMPTY) << 4)) << (8u * r + my_slot);
+        if (TOMB) tbits |= (unsigned)(tag == DOK_REMOVED) << (4u * r + my_slot);
+      }
+    }
+    bits |= __shfl_xor_sync(FULL, bits, 1);
+    bits |= __shfl_xor_sync(FULL, bits, 2);
+    if (TOMB) {
+      tbits |= __shfl_xor_sync(FULL, tbits, 1);
+      tbits |= __shfl_xor_sync(FULL, tbits, 2);
+    }
+#pragma unroll
+    for (unsigned r = 0; r < 4; r++) {                // hits: hand the line to the emitter while it is in registers
+      const unsigned m = (bits >> (8u * r)) & 0xfu, me = (m | (bits >> (8u * r + 4u))) & 0xfu;
+      if (me) {
+        const int pos = __ffs(me) - 1;
+        if ((m >> pos) & 1u) emit(e_quad + r, pos, w[r]);
+      }
+    }
+    if (group != NONE) {
+      const unsigned mine = bits >> (8u * l);
+      advance(mine & 0xfu, (mine | (mine >> 4)) & 0xfu, TOMB ? (tbits >> (4u * l)) & 0xfu : 0u);
+    }
   }
-#pragma unroll
-  for (unsigned r = 0; r < 4; r++) resolve(w[r], g[r], __shfl_sync(FULL, kh.uuid, base + r), r);
 
+  // ---- keys whose chain runs into further groups (few below 90 % load): one key per quad and iteration
   for (;;) {
     const unsigned pend = __ballot_sync(FULL, group != NONE);
     if (pend == 0) break;
@@ -369,7 +395,17 @@ __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyH
     const ll_t uuid_r = __shfl_sync(FULL, kh.uuid, base + r);
     ull_t wl[LW];
     if (g_r != NONE) dok_load_words<LW>(my_base + (ull_t)g_r * 128u, wl);
-    resolve(wl, g_r, uuid_r, r);
+    const ll_t tag = (has_tag && g_r != NONE) ? (ll_t)wl[0] : DOK_BLOCKED;
+    unsigned bits = ((unsigned)(tag == uuid_r) | ((unsigned)(tag == DOK_EMPTY) << 4) |
+                     (TOMB ? (unsigned)(tag == DOK_REMOVED) << 8 : 0u)) << my_slot;
+    bits |= __shfl_xor_sync(FULL, bits, 1);
+    bits |= __shfl_xor_sync(FULL, bits, 2);
+    const unsigned m = bits & 0xfu, me = (bits | (bits >> 4)) & 0xfu;
+    if (me) {
+      const int pos = __ffs(me) - 1;
+      if ((m >> pos) & 1u) emit(e_quad + r, pos, wl);
+    }
+    if (l == r && group != NONE) advance(m, me, (bits >> 8) & 0xfu);
   }
   if (probes) *probes = (int)walked;
   Located res;
@@ -406,7 +442,7 @@ struct EmitValue {
 };
 
 // SB == 0 selects the serial walk (slots wider than one line); emit is not called there.
-template <int SB, int LW, class Emit>
+template <int SB, int LW, bool TOMB, class Emit>
 __device__ __forceinline__ Located dok_locate(const DevTable &t, const KeyHash &kh, ll_t e, bool active, int *probes,
                                               const Emit &emit) {
   if constexpr (SB == 0) {
@@ -414,7 +450,7 @@ __device__ __forceinline__ Located dok_locate(const DevTable &t, const KeyHash &
     if (probes) *probes = 0;
     return Located{-1, -1, -1};
   } else {
-    return dok_locate_quad<SB, LW>(t, kh, e, active, probes, emit);
+    return dok_locate_quad<SB, LW, TOMB>(t, kh, e, active, probes, emit);
   }
 }
 
@@ -463,7 +499,7 @@ static __device__ __forceinline__ ll_t dok_find_or_claim_serial(const DevTable &
 // uuid is rare; that lane redoes the whole operation with the serial walk.  Every lane of the warp must call.
 template <int SB>
 __device__ __forceinline__ ll_t dok_find_or_claim(const DevTable &t, const KeyHash &kh, bool active, int *outcome) {
-  const Located loc = dok_locate<SB, 1>(t, kh, 0, active, nullptr, NoEmit());   // the tags are all a claim needs
+  const Located loc = dok_locate<SB, 1, true>(t, kh, 0, active, nullptr, NoEmit());   // the tags are all a claim needs
   if (!active) return -1;
   if (loc.found >= 0) { *outcome = DOK_OUT_FOUND; return loc.found; }
   if (loc.tomb >= 0) {

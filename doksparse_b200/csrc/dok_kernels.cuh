@@ -14,23 +14,23 @@
 // get
 // ---------------------------------------------------------------------------------------------------------
 template <int SB, int LW, class Keys>
-__global__ void __launch_bounds__(DOK_TPB) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
-                                                 uint8_t *__restrict__ out_found, Fallback fb, ll_t *counters,
-                                                 int count_probes) {
+__global__ void __launch_bounds__(DOK_TPB, 6) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
+                                                    uint8_t *__restrict__ out_found, Fallback fb, ll_t *counters,
+                                                    int count_probes) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   const bool active = e < keys.count();
   KeyHash kh{0, 0};
   if (active) kh = keys.hash(hp, e);
   int probes = 0;
   // on a hit the quad writes the value from the registers that hold the line
-  const Located loc = dok_locate<SB, LW>(t, kh, e, active, &probes, EmitValue<(SB == 0 ? 32 : SB), LW>{t, out_values});
+  const Located loc = dok_locate<SB, LW, false>(t, kh, e, active, &probes, EmitValue<(SB == 0 ? 32 : SB), LW>{t, out_values});
   const int hit = active && loc.found >= 0;
   if (active) {
     char *dst = out_values + e * (ll_t)t.vb;
     if (SB == 0 && hit) dok_load_value(t, loc.found, dst);
     if (!hit) dok_store_fallback(t, fb, dst);
-    if (out_found) out_found[e] = (uint8_t)hit;
   }
+  if (active && out_found) out_found[e] = (uint8_t)hit;
   if (counters) {
     dok_warp_add(counters + DOK_CNT_HITS, hit);
     if (count_probes) dok_warp_add(counters + DOK_CNT_PROBES, probes);
@@ -105,11 +105,10 @@ __global__ void __launch_bounds__(DOK_TPB, 4) k_set_unique(DevTable t, DevHash h
 // targets the slot; the low bit records that more than one row of the batch did.
 __device__ __forceinline__ ll_t dok_stamp(ll_t epoch, ll_t row) { return (epoch << 33) | (row << 1); }
 
-// First kernel of the general set.  Find or claim the slot and raise its stamp.  The first row of the batch to
-// stamp a slot also writes its key and value there -- for a batch without equal uuids that is all there is to
-// do.  A later row that finds the slot already stamped in this epoch writes nothing, sets the conflict bit and
-// counts a duplicate (in slot_out[n], zeroed by the host before the launch); the second kernel then lets the
-// slot's last row rewrite it.
+// First kernel of the general set.  Find or claim the slot, store the row there and raise the slot's stamp --
+// for a batch without equal uuids that is all there is to do.  A row that finds the slot already stamped in
+// this epoch sets the conflict bit and counts a duplicate (in slot_out[n], zeroed by the host before the
+// launch); the second kernel then lets the slot's last row rewrite it.
 template <int SB, class Keys, class Values>
 __global__ void __launch_bounds__(DOK_TPB, 4) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
                                                        ll_t *__restrict__ slot_out, ll_t epoch,
@@ -123,10 +122,12 @@ __global__ void __launch_bounds__(DOK_TPB, 4) k_set_claim(DevTable t, DevHash hp
   if (active) {
     slot_out[e] = slot;
     if (slot >= 0) {
+      // the row is stored without waiting for the stamp's answer: the two requests travel together.  If the slot
+      // turns out to be shared, whatever the racing stores left is rewritten by the second kernel.
       ll_t *stamp = dok_stamp_ptr(t, slot);
+      dok_write_row(t, hp, keys, values, e, slot, outcome != DOK_OUT_FOUND || hp.dtype >= DOK_F16);
       const ll_t old = (ll_t)atomicMax(stamp, dok_stamp(epoch, e));
-      if ((old >> 33) != epoch) dok_write_row(t, hp, keys, values, e, slot, outcome != DOK_OUT_FOUND || hp.dtype >= DOK_F16);
-      else {
+      if ((old >> 33) == epoch) {
         atomicOr((ull_t *)stamp, 1ULL);
         dup = 1;
       }
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys k
   const bool active = e < keys.count();
   KeyHash kh{0, 0};
   if (active) kh = keys.hash(hp, e);
-  const Located loc = dok_locate<SB, 1>(t, kh, e, active, nullptr, NoEmit());
+  const Located loc = dok_locate<SB, 1, false>(t, kh, e, active, nullptr, NoEmit());
   int hit = active && loc.found >= 0;
   if (REMOVE && hit) hit = dok_cas_tag(t, loc.found, kh.uuid, DOK_REMOVED) == kh.uuid;
   if (active && out_flags) out_flags[e] = (uint8_t)hit;
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, K
   const bool active = e < keys.count();
   KeyHash kh{0, 0};
   if (active) kh = keys.hash(hp, e);
-  const Located loc = dok_locate<SB, 1>(t, kh, e, active, nullptr, NoEmit());
+  const Located loc = dok_locate<SB, 1, false>(t, kh, e, active, nullptr, NoEmit());
   int claimed = 0;
   if (active && loc.found < 0) {
     const ll_t uuid = kh.uuid;
