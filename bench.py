@@ -286,10 +286,34 @@ def reference_kernels_on_gpu(args, steps=5, warmup=3):
     torch.cuda.synchronize()
     ms = t0.elapsed_time(t1) / steps
     phase = [sum(m[i].elapsed_time(m[i + 1]) for m in events) / steps for i in range(3)]
+
+    # the same step the way a user of the reference calls it: with the Python bookkeeping of its set / remove
+    # (pre-get, row-wise unique, host read of n_elements) around the kernels
+    def api_step(b):
+        gk, _, sk, sv, fk = batches[b % N_BATCHES]
+        table.get(gk)
+        table.api_set(sk, sv, rehash_threshold=0.95)
+        table.api_remove(fk)
+
+    table.n_elements = torch.tensor(n_keys, device=device)
+    api_step(0)
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    api_steps = 3
+    a0.record()
+    for s in range(api_steps):
+        api_step(1 + s)
+    a1.record()
+    torch.cuda.synchronize()
+    api_ms = a0.elapsed_time(a1) / api_steps
     live = int(((table.all_uuids != -1) & (table.all_uuids != -3)).sum().item())
     return {"value": 2 * q / (ms * 1e-3) / 1e6, "unit": "Mops/s", "ms_per_step": ms,
             "get_ms": phase[0], "set_ms": phase[1], "remove_ms": phase[2], "steps": steps, "results_ok": ok,
             "live_keys_after": live, "live_keys_expected": n_keys,
+            "api_path": {"value": 2 * q / (api_ms * 1e-3) / 1e6, "unit": "Mops/s", "ms_per_step": api_ms, "steps": api_steps,
+                         "what": "the same kernels with the reference's Python bookkeeping restated around them "
+                                 "(cuda_closed_hashmap.py:321-384, 423-454: pre-get + unique(dim=0) + n_elements.item() "
+                                 "per set, unique(dim=0) per remove), i.e. what a caller of the reference API pays"},
             "what": "the reference's closed_hashmap_get/set/remove kernels (closed_hashmap_impl.cu), nvcc -O3 for sm_100a, "
                     "launched like closed_hashmap_impl.py does, incl. its output allocation and fallback fill; "
                     "no Python-side pre-get / unique / rehash logic"}

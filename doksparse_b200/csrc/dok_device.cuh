@@ -569,6 +569,16 @@ __device__ __forceinline__ void dok_store_fallback(const DevTable &t, const Fall
   }
 }
 
+// Number of threads of the block with `pred` set, added to a device counter by ONE atomic per block: the counters
+// of a launch are a handful of addresses, and atomics on one address are served one after the other, so their
+// number per launch matters (a million per-warp atomics on one word cost about as much as the probing itself).
+// Every thread of the block must call it, with the same `counter`.
+__device__ __forceinline__ void dok_block_add(ll_t *counter, int pred) {
+  if (counter == nullptr) return;
+  const int c = __syncthreads_count(pred);
+  if (threadIdx.x == 0 && c) atomicAdd((ull_t *)counter, (ull_t)c);
+}
+
 // warp sum + one atomicAdd per warp (replaces warp_sum + atomicAdd of sparse_dok_tensor_impl.cu:52-55).
 // Every lane of the warp must call it.
 __device__ __forceinline__ void dok_warp_add(ll_t *counter, int v) {

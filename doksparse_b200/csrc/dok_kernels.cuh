@@ -14,7 +14,7 @@
 // get
 // ---------------------------------------------------------------------------------------------------------
 template <int SB, int LW, class Keys>
-__global__ void __launch_bounds__(DOK_TPB, 6) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
+__global__ void __launch_bounds__(DOK_TPB, (LW == 2 ? 8 : 1)) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
                                                     uint8_t *__restrict__ out_found, Fallback fb, ll_t *counters,
                                                     int count_probes) {
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(DOK_TPB, 6) k_get(DevTable t, DevHash hp, Keys
   }
   if (active && out_found) out_found[e] = (uint8_t)hit;
   if (counters) {
-    dok_warp_add(counters + DOK_CNT_HITS, hit);
+    dok_block_add(counters + DOK_CNT_HITS, hit);
     if (count_probes) dok_warp_add(counters + DOK_CNT_PROBES, probes);
   }
 }
@@ -93,10 +93,10 @@ __global__ void __launch_bounds__(DOK_TPB, 4) k_set_unique(DevTable t, DevHash h
     if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
   }
   if (counters) {
-    dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
-    dok_warp_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
-    dok_warp_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
-    dok_warp_add(counters + DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
+    dok_block_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
+    dok_block_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
+    dok_block_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
+    dok_block_add(counters + DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
   }
 }
 
@@ -134,13 +134,13 @@ __global__ void __launch_bounds__(DOK_TPB, 4) k_set_claim(DevTable t, DevHash hp
     }
     if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
   }
-  dok_warp_add(slot_out + keys.count(), dup);
+  dok_block_add(slot_out + keys.count(), dup);
   if (counters) {
-    dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
-    dok_warp_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
-    dok_warp_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
-    dok_warp_add(counters + DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
-    dok_warp_add(counters + DOK_CNT_DUPLICATES, dup);
+    dok_block_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
+    dok_block_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
+    dok_block_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
+    dok_block_add(counters + DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
+    dok_block_add(counters + DOK_CNT_DUPLICATES, dup);
   }
 }
 
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys k
   int hit = active && loc.found >= 0;
   if (REMOVE && hit) hit = dok_cas_tag(t, loc.found, kh.uuid, DOK_REMOVED) == kh.uuid;
   if (active && out_flags) out_flags[e] = (uint8_t)hit;
-  dok_warp_add(counters ? counters + DOK_CNT_HITS : nullptr, hit);
+  dok_block_add(counters ? counters + DOK_CNT_HITS : nullptr, hit);
 }
 
 static __global__ void k_fill_i64(ll_t *p, ll_t n, ll_t v) {
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, K
       if (++slot == scratch_slots) slot = 0;
     }
   }
-  dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, claimed);
+  dok_block_add(counters + DOK_CNT_CLAIMED_EMPTY, claimed);
 }
 
 // ---------------------------------------------------------------------------------------------------------

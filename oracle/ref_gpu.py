@@ -102,6 +102,26 @@ class RefGpuMap:
         assert rc == 0, f"reference remove launch failed: cudaError {rc}"
         return removed
 
+    # ---- the reference's Python bookkeeping around the kernels, restated (cuda_closed_hashmap.py:321-384, 423-454):
+    # `set` first looks the batch up, counts the distinct absent rows with a row-wise unique and reads n_elements on
+    # the host for the rehash decision; `remove` de-duplicates the batch with a row-wise unique and returns flags for
+    # the sorted unique rows.  Rehashing itself is not restated: callers size the table so that it never triggers.
+    def api_set(self, keys, values, rehash_threshold=0.75):
+        if not hasattr(self, "n_elements"):
+            self.n_elements = torch.zeros((), device=self.device, dtype=torch.long)
+        _, found = self.get(keys)
+        n_new = keys[~found].unique(dim=0).shape[0]
+        assert int(self.n_elements.item()) + n_new <= int(rehash_threshold * self.n_buckets), "would rehash"
+        self.set(keys, values)
+        self.n_elements += n_new
+
+    def api_remove(self, keys):
+        unique_keys = keys.unique(dim=0)
+        removed = self.remove(unique_keys)
+        if hasattr(self, "n_elements"):
+            self.n_elements -= removed.sum()
+        return removed
+
     def items(self):
         """(keys, values, uuid) of the live buckets in bucket order."""
         live = (self.all_uuids != -1) & (self.all_uuids != -3)
