@@ -481,13 +481,12 @@ def run_candidate(args):
 
         from doksparse_b200.host_batch import HostBatch
         # chunks of 4 Mi rows on three streams (copy in | kernels | copy out); routed batches use larger chunks
-        pipe = HostBatch(table, device, chunk_rows=(1 << 22) if world == 1 else (1 << 24))
+        pipe = HostBatch(table, device, chunk_rows=(1 << 22) if world == 1 else (1 << 23))
 
         def e2e_step(b):
             h = host[b % 2]
-            pipe.get(h["get_keys"], out_values, out_found)
-            pipe.set(h["set_keys"], h["set_values"])
-            pipe.remove_rows(h["fresh_keys"])
+            pipe.run([("get", h["get_keys"], out_values, out_found), ("set", h["set_keys"], h["set_values"]),
+                      ("remove_rows", h["fresh_keys"])])
 
         e2e_steps = max(3, min(args.steps, 10))
         e2e_step(0)

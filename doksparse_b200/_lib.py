@@ -98,10 +98,11 @@ def _declare(lib):
         "dok_dense_count_nonzero": ([P, I64, I, I, P, P], I),
         "dok_dense_insert_nonzero": ([TP, HP, P, P, I64, I, P, P], I),
         "dok_partition_tiles": ([I64], I64),
-        "dok_shard_partition_count": ([HP, P, I64, I, P, P, P], I),
+        "dok_shard_partition_count": ([HP, P, I64, I, P, P, P, P], I),
         "dok_partition_capacity": ([I64, I], I64),
-        "dok_shard_partition_scatter": ([HP, P, P, I, I64, I, P, P, P, P, P, P], I),
+        "dok_shard_partition_scatter": ([P, I, P, I, I64, I, P, P, P, P, P, P, P], I),
         "dok_shard_unpermute": ([P, P, P, I, I64, P, P, P], I),
+        "dok_words_to_pinned": ([P, P, I, P], I),
         "dok_shard_owner": ([HP, P, I64, I, P, P], I),
         "dok_diag_random_reads": ([P, I64, I64, ctypes.c_uint64, P, P], I),
     }

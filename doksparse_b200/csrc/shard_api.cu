@@ -18,16 +18,30 @@ __device__ __forceinline__ void dok_copy_row(char *dst, const char *src, int byt
   else for (int i = 0; i < bytes; i++) dst[i] = src[i];
 }
 
+// Tile = DOK_PART_TILE consecutive rows; thread t of the block owns rows base + r * DOK_TPB + t, r = 0 .. ROUNDS-1,
+// so the row order inside a tile is (round, warp, lane).
+//
+// Pass 1: owner shard of every row, kept as one byte per row for the second pass (the uuid is the expensive part
+// of routing: one 64-bit remainder per key element), and the rows per owner of each tile.  The lanes of a warp
+// that share an owner are found with one match; their first lane adds the group's size to the tile's histogram.
 static __global__ void __launch_bounds__(DOK_TPB) k_part_count(DevHash hp, RowKeys keys, int n_shards, ll_t tiles,
+                                                               uint8_t *__restrict__ owners,
                                                                ll_t *__restrict__ tile_counts) {
   __shared__ int hist[DOK_MAX_SHARDS];
   if (threadIdx.x < DOK_MAX_SHARDS) hist[threadIdx.x] = 0;
   __syncthreads();
+  const int lane = threadIdx.x & 31;
   const ll_t base = (ll_t)blockIdx.x * DOK_PART_TILE;
 #pragma unroll
   for (int r = 0; r < DOK_PART_ROUNDS; r++) {
     const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    if (e < keys.n) atomicAdd(&hist[dok_owner_shard(keys.hash(hp, e).uuid, n_shards)], 1);
+    int owner = -1;
+    if (e < keys.n) {
+      owner = dok_owner_shard(keys.hash(hp, e).uuid, n_shards);
+      owners[e] = (uint8_t)owner;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, owner);
+    if (owner >= 0 && (peers & ((1u << lane) - 1u)) == 0) atomicAdd(&hist[owner], __popc(peers));
   }
   __syncthreads();
   if (threadIdx.x < n_shards) tile_counts[(ll_t)threadIdx.x * tiles + blockIdx.x] = hist[threadIdx.x];
@@ -62,49 +76,65 @@ static __global__ void k_part_shard_counts(const ll_t *tile_offsets, int n_shard
   }
 }
 
-static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(DevHash hp, RowKeys keys, const char *__restrict__ values,
-                                                                 int vb, int n_shards, ll_t tiles,
+// Pass 2: every row to its place.  Rows of one owner keep their batch order: inside a tile the place of a row is
+// the number of same-owner rows before it in (round, warp, lane) order -- per-(round, warp) counts from warp
+// matches, one exclusive scan per owner over the ROUNDS * warps counts, and the row's rank among its warp's
+// same-owner lanes -- behind the tile's offset from pass 1.  Three block barriers per tile.
+static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, int kb, const char *__restrict__ values,
+                                                                 int vb, const uint8_t *__restrict__ owners,
+                                                                 int n_shards, ll_t tiles,
                                                                  const ll_t *__restrict__ tile_offsets,
                                                                  const ll_t *__restrict__ shard_counts, char *keys_out,
                                                                  char *values_out, ll_t *__restrict__ dest_index) {
-  __shared__ int warp_count[DOK_TPB / 32][DOK_MAX_SHARDS];
-  __shared__ int running[DOK_MAX_SHARDS];
-  __shared__ ll_t seg_shift[DOK_MAX_SHARDS];      // padded start of an owner's segment minus its unpadded start
+  constexpr int WARPS = DOK_TPB / 32, CELLS = DOK_PART_ROUNDS * WARPS;        // cells of one owner, in row order
+  __shared__ int before[DOK_MAX_SHARDS][CELLS];   // same-owner rows of the tile before cell (round, warp)
+  __shared__ ll_t tile_start[DOK_MAX_SHARDS];     // first output row of this tile's rows for each owner
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < n_shards * CELLS; i += DOK_TPB) (&before[0][0])[i] = 0;
   if (threadIdx.x == 0) {
-    ll_t padded = 0;
+    ll_t padded = 0;                              // owner o's segment starts at the sum of the padded counts before it
     for (int o = 0; o < n_shards; o++) {
-      seg_shift[o] = padded - tile_offsets[(ll_t)o * tiles];
+      tile_start[o] = padded + tile_offsets[(ll_t)o * tiles + blockIdx.x] - tile_offsets[(ll_t)o * tiles];
       padded += shard_counts[n_shards + o];
     }
   }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int kb = hp.ks * hp.elem_bytes;
-  for (int i = threadIdx.x; i < (DOK_TPB / 32) * DOK_MAX_SHARDS; i += DOK_TPB) (&warp_count[0][0])[i] = 0;
-  if (threadIdx.x < DOK_MAX_SHARDS) running[threadIdx.x] = 0;
   __syncthreads();
   const ll_t base = (ll_t)blockIdx.x * DOK_PART_TILE;
+  int owner[DOK_PART_ROUNDS];
+  int rank[DOK_PART_ROUNDS];                      // same-owner lanes of the warp below this one
+#pragma unroll
   for (int r = 0; r < DOK_PART_ROUNDS; r++) {
     const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    const int owner = e < keys.n ? dok_owner_shard(keys.hash(hp, e).uuid, n_shards) : -1;
-    const unsigned peers = __match_any_sync(0xffffffffu, owner);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    if (owner >= 0 && rank == 0) warp_count[warp][owner] = __popc(peers);
-    __syncthreads();
-    if (owner >= 0) {
-      int before = running[owner] + rank;
-      for (int w = 0; w < warp; w++) before += warp_count[w][owner];
-      const ll_t dest = tile_offsets[(ll_t)owner * tiles + blockIdx.x] + seg_shift[owner] + before;
-      dest_index[e] = dest;
-      dok_copy_row(keys_out + dest * kb, (const char *)keys.keys + e * kb, kb);
-      if (values) dok_copy_row(values_out + dest * vb, values + e * vb, vb);
+    owner[r] = e < keys.n ? (int)owners[e] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, owner[r]);
+    rank[r] = __popc(peers & ((1u << lane) - 1u));
+    if (owner[r] >= 0 && rank[r] == 0) before[owner[r]][r * WARPS + warp] = __popc(peers);
+  }
+  __syncthreads();
+  for (int o = warp; o < n_shards; o += WARPS) {  // exclusive scan of the owner's CELLS counts by one warp
+    int run = 0;
+#pragma unroll
+    for (int c0 = 0; c0 < CELLS; c0 += 32) {
+      const int v = before[o][c0 + lane];
+      int inc = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += up;
+      }
+      before[o][c0 + lane] = run + inc - v;
+      run += __shfl_sync(0xffffffffu, inc, 31);
     }
-    __syncthreads();
-    if (threadIdx.x < n_shards) {
-      int s = 0;
-      for (int w = 0; w < DOK_TPB / 32; w++) { s += warp_count[w][threadIdx.x]; warp_count[w][threadIdx.x] = 0; }
-      running[threadIdx.x] += s;
-    }
-    __syncthreads();
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < DOK_PART_ROUNDS; r++) {
+    if (owner[r] < 0) continue;
+    const ll_t e = base + r * DOK_TPB + threadIdx.x;
+    const ll_t dest = tile_start[owner[r]] + before[owner[r]][r * WARPS + warp] + rank[r];
+    if (dest_index) dest_index[e] = dest;
+    dok_copy_row(keys_out + dest * kb, (const char *)keys.keys + e * kb, kb);
+    if (values) dok_copy_row(values_out + dest * vb, values + e * vb, vb);
   }
 }
 
@@ -124,16 +154,16 @@ extern "C" {
 int64_t dok_partition_tiles(int64_t n) { return (n + DOK_PART_TILE - 1) / DOK_PART_TILE; }
 int64_t dok_partition_capacity(int64_t n, int n_shards) { return n + (int64_t)n_shards * (DOK_SEGMENT_ALIGN_ROWS - 1); }
 
-int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards,
+int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, uint8_t *owners,
                               int64_t *tile_offsets, int64_t *shard_counts, void *stream) {
   DevHash dh;
   if (!dok_make_hash(hp, &dh) || n < 0 || n > DOK_MAX_BATCH || n_shards < 1 || n_shards > DOK_MAX_SHARDS) return DOK_BAD_ARG;
-  if (!tile_offsets || !shard_counts || (n > 0 && !keys)) return DOK_BAD_ARG;
+  if (!tile_offsets || !shard_counts || (n > 0 && (!keys || !owners))) return DOK_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const ll_t tiles = dok_partition_tiles(n);
   if (tiles > 0) {
     RowKeys rk{keys, n};
-    k_part_count<<<(unsigned)tiles, DOK_TPB, 0, st>>>(dh, rk, n_shards, tiles, (ll_t *)tile_offsets);
+    k_part_count<<<(unsigned)tiles, DOK_TPB, 0, st>>>(dh, rk, n_shards, tiles, owners, (ll_t *)tile_offsets);
     int rc = dok_check_launch();
     if (rc != DOK_OK) return rc;
   }
@@ -144,19 +174,19 @@ int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64
   return dok_check_launch();
 }
 
-int dok_shard_partition_scatter(const dok_hash_params *hp, const void *keys, const void *values, int value_bytes,
-                                int64_t n, int n_shards, const int64_t *tile_offsets, const int64_t *shard_counts,
-                                void *keys_out, void *values_out, int64_t *dest_index, void *stream) {
-  DevHash dh;
-  if (!dok_make_hash(hp, &dh) || n < 0 || n > DOK_MAX_BATCH || n_shards < 1 || n_shards > DOK_MAX_SHARDS) return DOK_BAD_ARG;
+int dok_shard_partition_scatter(const void *keys, int key_bytes, const void *values, int value_bytes, int64_t n,
+                                int n_shards, const uint8_t *owners, const int64_t *tile_offsets,
+                                const int64_t *shard_counts, void *keys_out, void *values_out, int64_t *dest_index,
+                                void *stream) {
+  if (n < 0 || n > DOK_MAX_BATCH || n_shards < 1 || n_shards > DOK_MAX_SHARDS) return DOK_BAD_ARG;
   if (n == 0) return DOK_OK;
-  if (!keys || !tile_offsets || !shard_counts || !keys_out || !dest_index) return DOK_BAD_ARG;
+  if (!keys || key_bytes < 1 || !owners || !tile_offsets || !shard_counts || !keys_out) return DOK_BAD_ARG;
   if (values && (!values_out || value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES)) return DOK_BAD_ARG;
   const ll_t tiles = dok_partition_tiles(n);
   RowKeys rk{keys, n};
   k_part_scatter<<<(unsigned)tiles, DOK_TPB, 0, (cudaStream_t)stream>>>(
-      dh, rk, (const char *)values, value_bytes, n_shards, tiles, (const ll_t *)tile_offsets, (const ll_t *)shard_counts,
-      (char *)keys_out, (char *)values_out, (ll_t *)dest_index);
+      rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, tiles, (const ll_t *)tile_offsets,
+      (const ll_t *)shard_counts, (char *)keys_out, (char *)values_out, (ll_t *)dest_index);
   return dok_check_launch();
 }
 
@@ -167,6 +197,21 @@ int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found
   if (!dest_index || (out_values && (!grouped_values || value_bytes < 1)) || (out_found && !grouped_found)) return DOK_BAD_ARG;
   k_unpermute<<<(unsigned)((n + DOK_TPB - 1) / DOK_TPB), DOK_TPB, 0, (cudaStream_t)stream>>>(
       (const char *)grouped_values, grouped_found, (const ll_t *)dest_index, value_bytes, n, (char *)out_values, out_found);
+  return dok_check_launch();
+}
+
+/* A few words from device memory into PINNED host memory by a kernel store (pinned memory is mapped into the
+ * device's address space), not by a copy: a copy would queue on the device-to-host copy engine behind whatever
+ * bulk result transfer another stream has in flight, and the host waits for these words (the per-owner row counts)
+ * before it can size the exchange. */
+static __global__ void k_words_to_host(const ll_t *__restrict__ src, volatile ll_t *dst, int n) {
+  if ((int)threadIdx.x < n) dst[threadIdx.x] = src[threadIdx.x];
+  __threadfence_system();
+}
+
+int dok_words_to_pinned(const int64_t *src, int64_t *pinned_dst, int n_words, void *stream) {
+  if (!src || !pinned_dst || n_words < 1 || n_words > 1024) return DOK_BAD_ARG;
+  k_words_to_host<<<1, 1024, 0, (cudaStream_t)stream>>>((const ll_t *)src, (volatile ll_t *)pinned_dst, n_words);
   return dok_check_launch();
 }
 

@@ -9,7 +9,12 @@ its callers hand it CUDA tensors (`sparse_dok/components/cuda_closed_hashmap.py:
 Works on a `CudaClosedHashmap` and on a `ShardedClosedHashmap` (whose calls are collective: every rank must then use
 the same chunking, i.e. equal batch sizes).  Chunks are applied in order, so a chunked `set` resolves duplicates like
 one big `set` (last row wins).  Staging buffers are allocated once per row shape and reused (two per direction), so
-the steady state makes no allocator calls.  Calls only enqueue work; `join()` makes the caller's current stream wait.
+the steady state makes no allocator calls.
+
+The copy-in of a chunk is enqueued one chunk AHEAD of its kernels: map operations may block the host (the sharded map
+reads row counts back before each exchange), and a copy that is already queued keeps PCIe busy meanwhile.  `run()`
+takes several operations at once so that this look-ahead also bridges the boundary between them.  Calls only enqueue
+work; `join()` makes the caller's current stream wait for it.
 """
 import torch
 
@@ -38,8 +43,10 @@ class HostBatch:
         with torch.cuda.device(self.device):
             self.s_in, self.s_run, self.s_out = (torch.cuda.Stream() for _ in range(3))
         self._rings = {}
+        self._takes_outputs = hasattr(table, "_slots")      # a plain map writes straight into the staging buffers
         self.begin()
 
+    # ------------------------------------------------------------------ stream plumbing
     def begin(self):
         """Side streams start after whatever the caller's current stream has enqueued so far."""
         with torch.cuda.device(self.device):
@@ -57,14 +64,10 @@ class HostBatch:
                 ev.record(s)
                 cur.wait_event(ev)
 
-    def _chunks(self, n):
-        for lo in range(0, n, self.chunk_rows):
-            yield lo, min(n, lo + self.chunk_rows)
-
-    def _ring(self, tag, like_rows, dtype):
-        key = (tag, tuple(like_rows), dtype)
+    def _ring(self, tag, row_shape, dtype):
+        key = (tag, tuple(row_shape), dtype)
         if key not in self._rings:
-            self._rings[key] = _Ring(self.chunk_rows, like_rows, dtype, self.device)
+            self._rings[key] = _Ring(self.chunk_rows, row_shape, dtype, self.device)
         return self._rings[key]
 
     def _stage_in(self, tag, host_slice):
@@ -76,19 +79,6 @@ class HostBatch:
             view.copy_(host_slice, non_blocking=True)
         return ring, i, view
 
-    def _run(self, staged, fn):
-        """fn() on the kernel stream once the staged inputs have arrived; marks them reusable afterwards"""
-        ready = torch.cuda.Event()
-        ready.record(self.s_in)
-        with torch.cuda.stream(self.s_run):
-            self.s_run.wait_event(ready)
-            result = fn()
-            done = torch.cuda.Event()
-            done.record(self.s_run)
-        for ring, i, _ in staged:
-            ring.free_after[i] = done
-        return result, done
-
     def _copy_out(self, done, pairs, rings):
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(done)
@@ -99,43 +89,96 @@ class HostBatch:
         for ring, i in rings:
             ring.free_after[i] = copied
 
-    def get(self, keys_host, out_values_host, out_found_host, fallback_value=None):
-        takes_outputs = hasattr(self.table, "_slots")       # a plain map writes straight into the staging buffers
+    # ------------------------------------------------------------------ chunk programs
+    # A chunk is (inputs, body): inputs = [(tag, pinned host slice)], body(device views) runs on the kernel stream and
+    # returns (pairs, rings) for the copy-out: [(host slice, device tensor)], [(ring, index)] of result buffers.
+    def _chunks(self, n):
+        for lo in range(0, n, self.chunk_rows):
+            yield lo, min(n, lo + self.chunk_rows)
+
+    def _get_chunks(self, keys_host, out_values_host, out_found_host, fallback_value=None):
         vr = self._ring("ov", out_values_host.shape[1:], out_values_host.dtype)
         fr = self._ring("of", (), torch.bool)
         for lo, hi in self._chunks(keys_host.shape[0]):
-            staged = self._stage_in("k", keys_host[lo:hi])
-            keys = staged[2]
-            vi, vbuf = vr.take(self.s_run)
-            fi, fbuf = fr.take(self.s_run)
-            values, found = vbuf[: hi - lo], fbuf[: hi - lo]
-
-            def lookup():
-                if takes_outputs:
+            def body(keys, lo=lo, hi=hi):
+                vi, vbuf = vr.take(self.s_run)
+                fi, fbuf = fr.take(self.s_run)
+                values, found = vbuf[: hi - lo], fbuf[: hi - lo]
+                if self._takes_outputs:
                     self.table.get(keys, fallback_value, values=values, is_found=found)
                 else:                       # results come back in tensors of the kernel stream's pool: move them over
                     v, f = self.table.get(keys, fallback_value)
                     values.copy_(v)
                     found.copy_(f)
+                return [(out_values_host[lo:hi], values), (out_found_host[lo:hi], found)], [(vr, vi), (fr, fi)]
+            yield [("k", keys_host[lo:hi])], body
 
-            _, done = self._run([staged], lookup)
-            self._copy_out(done, [(out_values_host[lo:hi], values), (out_found_host[lo:hi], found)], [(vr, vi), (fr, fi)])
-
-    def set(self, keys_host, values_host, assume_unique=False):
+    def _set_chunks(self, keys_host, values_host, assume_unique=False):
         for lo, hi in self._chunks(keys_host.shape[0]):
-            sk = self._stage_in("k", keys_host[lo:hi])
-            sv = self._stage_in("v", values_host[lo:hi])
-            self._run([sk, sv], lambda: self.table.set(sk[2], sv[2], assume_unique=assume_unique))
+            def body(keys, values):
+                self.table.set(keys, values, assume_unique=assume_unique)
+                return [], []
+            yield [("k", keys_host[lo:hi]), ("v", values_host[lo:hi])], body
 
-    def remove_rows(self, keys_host, out_flags_host=None):
-        """Kernel-level removal: flags aligned to the rows given (no dedup, no sort)."""
+    def _remove_chunks(self, keys_host, out_flags_host=None):
         remove = getattr(self.table, "remove_rows", None) or self.table.remove
         fr = self._ring("rf", (), torch.bool)
         for lo, hi in self._chunks(keys_host.shape[0]):
-            staged = self._stage_in("k", keys_host[lo:hi])
-            if out_flags_host is None:
-                self._run([staged], lambda: remove(staged[2]))
-                continue
-            fi, fbuf = fr.take(self.s_run)
-            _, done = self._run([staged], lambda: fbuf[: hi - lo].copy_(remove(staged[2])))
-            self._copy_out(done, [(out_flags_host[lo:hi], fbuf[: hi - lo])], [(fr, fi)])
+            def body(keys, lo=lo, hi=hi):
+                flags = remove(keys)
+                if out_flags_host is None:
+                    return [], []
+                fi, fbuf = fr.take(self.s_run)
+                fbuf[: hi - lo].copy_(flags)
+                return [(out_flags_host[lo:hi], fbuf[: hi - lo])], [(fr, fi)]
+            yield [("k", keys_host[lo:hi])], body
+
+    def _execute(self, chunks):
+        """Copy-in of chunk i + 1 is enqueued before the kernels of chunk i."""
+        chunks = iter(chunks)
+
+        def stage(chunk):
+            if chunk is None:
+                return None
+            inputs, body = chunk
+            staged = [self._stage_in(tag, host_slice) for tag, host_slice in inputs]
+            ready = torch.cuda.Event()
+            ready.record(self.s_in)
+            return staged, ready, body
+
+        ahead = stage(next(chunks, None))
+        while ahead is not None:
+            staged, ready, body = ahead
+            # a staging buffer is reused every second chunk of its kind, so the copy-in of the NEXT chunk never waits
+            # for kernels that are not enqueued yet
+            ahead = stage(next(chunks, None))
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(ready)
+                pairs, out_rings = body(*[view for _, _, view in staged])
+                done = torch.cuda.Event()
+                done.record(self.s_run)
+            for ring, i, _ in staged:
+                ring.free_after[i] = done
+            if pairs:
+                self._copy_out(done, pairs, out_rings)
+
+    # ------------------------------------------------------------------ public operations
+    def get(self, keys_host, out_values_host, out_found_host, fallback_value=None):
+        self._execute(self._get_chunks(keys_host, out_values_host, out_found_host, fallback_value))
+
+    def set(self, keys_host, values_host, assume_unique=False):
+        self._execute(self._set_chunks(keys_host, values_host, assume_unique))
+
+    def remove_rows(self, keys_host, out_flags_host=None):
+        """Kernel-level removal: flags aligned to the rows given (no dedup, no sort)."""
+        self._execute(self._remove_chunks(keys_host, out_flags_host))
+
+    def run(self, operations):
+        """Several operations as one pipeline: [("get", keys, out_values, out_found[, fallback]),
+        ("set", keys, values[, assume_unique]), ("remove_rows", keys[, out_flags]), ...], applied in order."""
+        makers = {"get": self._get_chunks, "set": self._set_chunks, "remove_rows": self._remove_chunks}
+
+        def all_chunks():
+            for name, *args in operations:
+                yield from makers[name](*args)
+        self._execute(all_chunks())

@@ -37,6 +37,7 @@ class CudaShardOps:
                                        rehash_threshold=rehash_threshold, **params)
         self._routing = {k: torch.as_tensor(v).cpu().tolist() for k, v in params.items()}
         self._hp = None
+        self._pinned = None
 
     def _routing_hash(self, keys):
         if self._hp is None:
@@ -53,7 +54,7 @@ class CudaShardOps:
             self._hp = hp
         return ctypes.byref(self._hp)
 
-    def partition(self, keys, values, world):
+    def partition(self, keys, values, world, want_dest=True):
         """-> (grouped_keys, grouped_values or None, dest_index, counts[2, world] on the device): rows per owner, and
         the same rounded up to multiples of 16 rows.  Owner o's segment starts at the sum of the ROUNDED counts before
         it, so that every segment is 16-byte aligned for the exchange (NCCL moves unaligned segments ~2.6x slower);
@@ -67,46 +68,53 @@ class CudaShardOps:
             cap = lib.dok_partition_capacity(n, world)
             offsets = torch.empty(world * tiles + 1, device=self.device, dtype=torch.long)
             counts = torch.empty(2 * world, device=self.device, dtype=torch.long)
-            L.check(lib.dok_shard_partition_count(self._routing_hash(keys), L.ptr(keys), n, world, L.ptr(offsets),
-                                                  L.ptr(counts), st), "dok_shard_partition_count")
+            owners = torch.empty(n, device=self.device, dtype=torch.uint8)
+            L.check(lib.dok_shard_partition_count(self._routing_hash(keys), L.ptr(keys), n, world, L.ptr(owners),
+                                                  L.ptr(offsets), L.ptr(counts), st), "dok_shard_partition_count")
             grouped_keys = torch.empty((cap,) + tuple(keys.shape[1:]), device=self.device, dtype=keys.dtype)
+            kb = int(np.prod(keys.shape[1:])) * keys.element_size()
             grouped_values, vb = None, 0
             if values is not None:
                 values = values.contiguous()
                 grouped_values = torch.empty((cap,) + tuple(values.shape[1:]), device=self.device, dtype=values.dtype)
                 vb = int(np.prod(values.shape[1:])) * values.element_size()
-            dest = torch.empty(n, device=self.device, dtype=torch.long)
-            L.check(lib.dok_shard_partition_scatter(self._routing_hash(keys), L.ptr(keys), L.ptr(values), vb, n, world,
+            dest = torch.empty(n, device=self.device, dtype=torch.long) if want_dest else None
+            L.check(lib.dok_shard_partition_scatter(L.ptr(keys), kb, L.ptr(values), vb, n, world, L.ptr(owners),
                                                     L.ptr(offsets), L.ptr(counts), L.ptr(grouped_keys),
                                                     L.ptr(grouped_values), L.ptr(dest), st), "dok_shard_partition_scatter")
         return grouped_keys, grouped_values, dest, counts.view(2, world)
 
-    def unpermute(self, grouped_values, grouped_flags, dest):
+    def unpermute(self, grouped_values, grouped_flags, dest, out_values=None, out_flags=None):
+        """out[i] = grouped[dest[i]]; writes into out_values / out_flags (contiguous, dest.shape[0] rows) when given."""
         lib = L.lib()
         n = dest.shape[0]
-        out_v = out_f = None
         vb = 0
         with torch.cuda.device(self.device):
             if grouped_values is not None:
-                out_v = torch.empty((n,) + tuple(grouped_values.shape[1:]), device=self.device, dtype=grouped_values.dtype)
+                if out_values is None:
+                    out_values = torch.empty((n,) + tuple(grouped_values.shape[1:]), device=self.device, dtype=grouped_values.dtype)
+                assert out_values.is_contiguous() and out_values.shape[0] == n
                 vb = int(np.prod(grouped_values.shape[1:])) * grouped_values.element_size()
             if grouped_flags is not None:
-                out_f = torch.empty(n, device=self.device, dtype=grouped_flags.dtype)
-            L.check(lib.dok_shard_unpermute(L.ptr(grouped_values), L.ptr(grouped_flags), L.ptr(dest), vb, n, L.ptr(out_v),
-                                            L.ptr(out_f), L.stream_ptr(self.device)), "dok_shard_unpermute")
-        return out_v, out_f
+                if out_flags is None:
+                    out_flags = torch.empty(n, device=self.device, dtype=grouped_flags.dtype)
+                assert out_flags.is_contiguous() and out_flags.shape[0] == n
+            L.check(lib.dok_shard_unpermute(L.ptr(grouped_values), L.ptr(grouped_flags), L.ptr(dest), vb, n,
+                                            L.ptr(out_values) if grouped_values is not None else None,
+                                            L.ptr(out_flags) if grouped_flags is not None else None,
+                                            L.stream_ptr(self.device)), "dok_shard_unpermute")
+        return (out_values if grouped_values is not None else None), (out_flags if grouped_flags is not None else None)
 
     # local table ops on the rows this rank owns.  `segments` = [(start, rows)] per source rank inside the received
     # buffer (starts are aligned, the gaps hold nothing); sources are processed in rank order, which is what makes
     # "last row wins" global.
     def local_get(self, keys, segments, fallback_value):
         values = torch.empty((keys.shape[0],) + tuple(self.local.value_shape), device=self.device, dtype=self.local.value_type)
-        found = torch.zeros(keys.shape[0], device=self.device, dtype=torch.bool)
+        found = torch.empty(keys.shape[0], device=self.device, dtype=torch.bool)
         for start, rows in segments:
-            if rows:
-                v, f = self.local.get(keys[start:start + rows], fallback_value)
-                values[start:start + rows] = v
-                found[start:start + rows] = f
+            if rows:      # the kernel writes straight into the segment's rows of the result buffers
+                self.local.get(keys[start:start + rows], fallback_value, values=values[start:start + rows],
+                               is_found=found[start:start + rows])
         return values, found
 
     def local_set(self, keys, values, segments, assume_unique):
@@ -115,7 +123,7 @@ class CudaShardOps:
                 self.local.set(keys[start:start + rows], values[start:start + rows], assume_unique=assume_unique)
 
     def local_remove(self, keys, segments):
-        flags = torch.zeros(keys.shape[0], device=self.device, dtype=torch.bool)
+        flags = torch.empty(keys.shape[0], device=self.device, dtype=torch.bool)
         for start, rows in segments:
             if rows:
                 flags[start:start + rows] = self.local.remove_rows(keys[start:start + rows])
@@ -123,6 +131,21 @@ class CudaShardOps:
 
     def local_n_elements(self):
         return self.local._n_elements
+
+    def to_host(self, words):
+        """Small int64 device tensor -> list of ints on the host, through a kernel store into pinned memory (a copy
+        would wait behind bulk device-to-host transfers that other streams have in flight)."""
+        n = words.numel()
+        if self._pinned is None or self._pinned.numel() < n:
+            self._pinned = torch.empty(max(n, 4 * L.MAX_SHARDS), dtype=torch.long, pin_memory=True)
+        flat = words.contiguous().reshape(-1)
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_words_to_pinned(L.ptr(flat), ctypes.c_void_p(self._pinned.data_ptr()), n,
+                                                L.stream_ptr(self.device)), "dok_words_to_pinned")
+            done = torch.cuda.Event()
+            done.record()
+        done.synchronize()
+        return self._pinned[:n].tolist()
 
     def ready(self):
         return self.local._keys is not None
@@ -140,7 +163,7 @@ class ShardedClosedHashmap:
     """
 
     def __init__(self, n_buckets_per_shard, prime1, prime2, alpha1, alpha2, beta1, beta2, group=None, device=None,
-                 rehash_factor=2.0, rehash_threshold=0.75, ops=None):
+                 rehash_factor=2.0, rehash_threshold=0.75, ops=None, pipeline_chunks=2):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -152,6 +175,7 @@ class ShardedClosedHashmap:
                 device = torch.device("cuda", torch.cuda.current_device())
             ops = CudaShardOps(device, n_buckets_per_shard, params, rehash_factor, rehash_threshold)
         self.ops = ops
+        self.pipeline_chunks = max(1, int(pipeline_chunks))     # must be the same on every rank
         self._value_shape = None
         self._value_dtype = None
 
@@ -162,74 +186,137 @@ class ShardedClosedHashmap:
         send = counts.t().contiguous()                       # [world, 2]: what goes to each owner
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=self.group)
-        both = torch.stack([send, recv]).cpu().tolist()
-        return [int(c[1]) for c in both[0]], [int(c[0]) for c in both[1]], [int(c[1]) for c in both[1]]
+        flat = self.ops.to_host(torch.stack([send, recv]))          # [2, world, 2] flattened
+        w = self.world
+        send_h = [flat[2 * i:2 * i + 2] for i in range(w)]
+        recv_h = [flat[2 * w + 2 * i:2 * w + 2 * i + 2] for i in range(w)]
+        return [int(c[1]) for c in send_h], [int(c[0]) for c in recv_h], [int(c[1]) for c in recv_h]
 
-    def _all_to_all_rows(self, rows, send, recv):
-        """rows grouped by destination -> rows grouped by source."""
+    def _all_to_all_rows(self, rows, send, recv, async_op=False):
+        """rows grouped by destination -> rows grouped by source.  With async_op the exchange is only enqueued:
+        returns (out, work) and the caller waits on `work` before touching `out`."""
         if self.world == 1:
-            return rows
+            return (rows, None) if async_op else rows
         out = self.ops.empty((sum(recv),) + tuple(rows.shape[1:]), rows.dtype)
-        dist.all_to_all_single(out, rows, output_split_sizes=recv, input_split_sizes=send, group=self.group)
-        return out
+        work = dist.all_to_all_single(out, rows, output_split_sizes=recv, input_split_sizes=send, group=self.group,
+                                      async_op=async_op)
+        return (out, work) if async_op else out
 
-    def _route(self, keys, values=None):
-        """-> (owned_keys, owned_values, segments, dest, send, recv); segments = [(start, rows)] per source rank."""
+    def _route(self, keys, values=None, want_dest=True, async_op=False):
+        """-> (owned_keys, owned_values, segments, dest, send, recv[, works]); segments = [(start, rows)] per source
+        rank.  With async_op the key / value exchanges are in flight on return and `works` must be waited for."""
         if self.world == 1:        # one shard owns everything: no partition, no exchange, no permutation
-            return keys, values, [(0, keys.shape[0])], None, None, None
-        grouped_keys, grouped_values, dest, counts = self.ops.partition(keys, values, self.world)
+            out = (keys, values, [(0, keys.shape[0])], None, None, None)
+            return out + ([],) if async_op else out
+        grouped_keys, grouped_values, dest, counts = self.ops.partition(keys, values, self.world, want_dest=want_dest)
         send, recv_rows, recv = self._exchange_counts(counts)
         assert keys.shape[0] <= sum(send) <= grouped_keys.shape[0], "partition lost rows"
-        owned_keys = self._all_to_all_rows(grouped_keys[:sum(send)], send, recv)
-        owned_values = None if values is None else self._all_to_all_rows(grouped_values[:sum(send)], send, recv)
+        works = []
+        owned_keys, w = self._all_to_all_rows(grouped_keys[:sum(send)], send, recv, async_op=True)
+        works.append(w)
+        owned_values = None
+        if values is not None:
+            owned_values, w = self._all_to_all_rows(grouped_values[:sum(send)], send, recv, async_op=True)
+            works.append(w)
         starts = [sum(recv[:i]) for i in range(self.world)]
-        return owned_keys, owned_values, list(zip(starts, recv_rows)), dest, send, recv
+        out = (owned_keys, owned_values, list(zip(starts, recv_rows)), dest, send, recv)
+        if async_op:
+            return out + (works,)
+        for w in works:
+            w.wait()
+        return out
+
+    def _chunk_bounds(self, n, pipelined):
+        """The same number of chunks on every rank (the calls are collective), whatever each rank's batch size."""
+        c = self.pipeline_chunks if (pipelined and self.world > 1) else 1
+        return [(n * i // c, n * (i + 1) // c) for i in range(c)]
 
     # ------------------------------------------------------------------ operations
     def set(self, keys, values, assume_unique=False):
         """Collective insert-or-assign.  `assume_unique` promises pairwise different keys across ALL ranks' batches."""
         if self._value_shape is None:
             self._value_shape, self._value_dtype = tuple(values.shape[1:]), values.dtype
-        owned_keys, owned_values, segments, _, _, _ = self._route(keys, values)
+        owned_keys, owned_values, segments, _, _, _ = self._route(keys, values, want_dest=False)
         self.ops.local_set(owned_keys, owned_values, segments, assume_unique)
+
+    def _lookup(self, keys, local_op, with_values, fallback_value=None):
+        """Shared body of get and remove.  For get the batch is cut into `pipeline_chunks` pieces that move through
+        partition -> key exchange -> local op -> result exchange -> inverse permutation as a software pipeline: the
+        exchanges are enqueued asynchronously, so the key exchange of piece i + 1 and the result exchange of piece
+        i - 1 run while the table is probed for piece i.  remove goes through in one piece: cutting it would let a
+        later rank's first piece overtake an earlier rank's second, and which of two equal keys reports the removal
+        is defined by rank order."""
+        n = keys.shape[0]
+        out_values = self.ops.empty((n,) + self._value_shape, self._value_dtype) if with_values else None
+        out_flags = self.ops.empty((n,), torch.bool)
+        bounds = self._chunk_bounds(n, pipelined=with_values)
+        routed, returned = [], []
+
+        def probe(i):
+            owned_keys, _, segments, dest, send, recv, works = routed[i]
+            for w in works:
+                if w is not None:
+                    w.wait()
+            if self.ops.ready() and owned_keys.shape[0]:
+                res = local_op(owned_keys, segments)
+                owned_values, owned_flags = res if with_values else (None, res)
+            else:
+                # this shard holds nothing yet (or received nothing): every row it was asked about is a miss
+                owned_values = None
+                if with_values:
+                    owned_values = self.ops.empty((owned_keys.shape[0],) + self._value_shape, self._value_dtype)
+                    fill = 0 if fallback_value is None else fallback_value
+                    if owned_values.numel():
+                        owned_values[:] = torch.as_tensor(fill, dtype=self._value_dtype)
+                owned_flags = self.ops.empty((owned_keys.shape[0],), torch.bool)
+                owned_flags[:] = False
+            if dest is None:
+                returned.append((owned_values, owned_flags, None, []))
+                return
+            works = []
+            back_values = None
+            if with_values:
+                back_values, w = self._all_to_all_rows(owned_values, recv, send, async_op=True)
+                works.append(w)
+            back_flags, w = self._all_to_all_rows(owned_flags.view(torch.uint8), recv, send, async_op=True)
+            works.append(w)
+            returned.append((back_values, back_flags, dest, works))
+
+        for i, (lo, hi) in enumerate(bounds):
+            routed.append(self._route(keys[lo:hi], async_op=True))
+            if i >= 1:
+                probe(i - 1)
+        probe(len(bounds) - 1)
+        for (lo, hi), (values, flags, dest, works) in zip(bounds, returned):
+            for w in works:
+                if w is not None:
+                    w.wait()
+            if dest is None:
+                if with_values:
+                    out_values[lo:hi] = values
+                out_flags[lo:hi] = flags
+            else:
+                self.ops.unpermute(values, flags, dest, out_values[lo:hi] if with_values else None,
+                                   out_flags[lo:hi].view(torch.uint8))
+        return out_values, out_flags
 
     def get(self, keys, fallback_value=None):
         """Collective lookup -> (values[n, *value_shape], is_found[n]) in the caller's row order."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
-        owned_keys, _, segments, dest, send, recv = self._route(keys)
-        if self.ops.ready() and owned_keys.shape[0]:
-            owned_values, owned_found = self.ops.local_get(owned_keys, segments, fallback_value)
-        else:
-            # this shard holds nothing yet (or received nothing): every row it was asked about is a miss
-            owned_values = self.ops.empty((owned_keys.shape[0],) + self._value_shape, self._value_dtype)
-            fill = 0 if fallback_value is None else fallback_value
-            if owned_values.numel():
-                owned_values[:] = torch.as_tensor(fill, dtype=self._value_dtype)
-            owned_found = self.ops.empty((owned_keys.shape[0],), torch.bool)
-            owned_found[:] = False
-        if dest is None:
-            return owned_values, owned_found
-        back_values = self._all_to_all_rows(owned_values, recv, send)
-        back_found = self._all_to_all_rows(owned_found.view(torch.uint8), recv, send)
-        out_values, out_found = self.ops.unpermute(back_values, back_found, dest)
-        return out_values, out_found.view(torch.bool)
+        if self.world == 1:
+            if not self.ops.ready():
+                return self._lookup(keys, None, True, fallback_value)
+            return self.ops.local_get(keys, [(0, keys.shape[0])], fallback_value)
+        return self._lookup(keys, lambda k, seg: self.ops.local_get(k, seg, fallback_value), True, fallback_value)
 
     def remove(self, keys):
         """Collective removal -> is_removed[n] aligned to the caller's rows (equal keys report once)."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
-        owned_keys, _, segments, dest, send, recv = self._route(keys)
-        if self.ops.ready() and owned_keys.shape[0]:
-            owned_flags = self.ops.local_remove(owned_keys, segments)
-        else:
-            owned_flags = self.ops.empty((owned_keys.shape[0],), torch.bool)
-            owned_flags[:] = False
-        if dest is None:
-            return owned_flags
-        back = self._all_to_all_rows(owned_flags.view(torch.uint8), recv, send)
-        _, out = self.ops.unpermute(None, back, dest)
-        return out.view(torch.bool)
+        if self.world == 1 and self.ops.ready():
+            return self.ops.local_remove(keys, [(0, keys.shape[0])])
+        return self._lookup(keys, lambda k, seg: self.ops.local_remove(k, seg), False)[1]
 
     @property
     def n_elements(self):

@@ -244,20 +244,27 @@ int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, cons
 /* ---- hash-sharded table: batch routing (no counterpart in the reference, which is single-GPU) ------- */
 
 /* Owner shard of each row: mulhi64(mix(uuid ^ salt), n_shards).  Stable partition of a batch by owner:
- * step 1 per-tile histogram + scan -> tile_offsets int64[n_shards * dok_partition_tiles(n) + 1] and
- * shard_counts int64[2 * n_shards]: rows per owner, then the same rounded up to multiples of 16 rows;
- * step 2 scatters key rows (and value rows, if values != NULL) into keys_out/values_out grouped by owner, order
- * within an owner preserved.  Each owner's segment starts at the sum of the ROUNDED counts before it (so every
- * segment is 16-byte aligned for the exchange); the rows of the gap behind a segment are left unwritten and must
- * be ignored by the receiver.  keys_out/values_out need dok_partition_capacity(n, n_shards) rows.  dest_index[n] receives each row's position in that grouped order (used by dok_shard_unpermute). */
+ * step 1 computes every row's owner (owners[n], one byte per row), a per-tile histogram and its scan ->
+ * tile_offsets int64[n_shards * dok_partition_tiles(n) + 1] and shard_counts int64[2 * n_shards]: rows per
+ * owner, then the same rounded up to multiples of 16 rows;
+ * step 2 scatters key rows of key_bytes (and value rows, if values != NULL) into keys_out/values_out grouped by
+ * owner, order within an owner preserved.  Each owner's segment starts at the sum of the ROUNDED counts before it
+ * (so every segment is 16-byte aligned for the exchange); the rows of the gap behind a segment are left unwritten
+ * and must be ignored by the receiver.  keys_out/values_out need dok_partition_capacity(n, n_shards) rows.
+ * dest_index[n] (may be NULL) receives each row's position in that grouped order (for dok_shard_unpermute). */
 int64_t dok_partition_tiles(int64_t n);
 int64_t dok_partition_capacity(int64_t n, int n_shards);
-int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards,
+int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, uint8_t *owners,
                               int64_t *tile_offsets, int64_t *shard_counts, void *stream);
-int dok_shard_partition_scatter(const dok_hash_params *hp, const void *keys, const void *values,
-                                int value_bytes, int64_t n, int n_shards, const int64_t *tile_offsets,
+int dok_shard_partition_scatter(const void *keys, int key_bytes, const void *values, int value_bytes, int64_t n,
+                                int n_shards, const uint8_t *owners, const int64_t *tile_offsets,
                                 const int64_t *shard_counts, void *keys_out, void *values_out, int64_t *dest_index,
                                 void *stream);
+
+/* n_words (<= 1024) int64 words from device memory to PINNED host memory (cudaHostAlloc / torch pin_memory), written
+ * by a kernel through the mapped address instead of a copy-engine transfer, so that the read-back of the row counts
+ * does not queue behind bulk device-to-host copies of other streams.  Complete when the stream reaches this point. */
+int dok_words_to_pinned(const int64_t *src, int64_t *pinned_dst, int n_words, void *stream);
 
 /* out_values[i] = grouped_values[dest_index[i]], out_found[i] = grouped_found[dest_index[i]] */
 int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found, const int64_t *dest_index,

@@ -59,7 +59,7 @@ class OracleShardOps:
             self._router = r
         return self._router.hash_uuid(np.ascontiguousarray(k))[1]
 
-    def partition(self, keys, values, world):
+    def partition(self, keys, values, world, want_dest=True):
         owner = owners(self._uuids(keys), world)
         order, dest, counts = stable_partition(owner, world)
         order_t = torch.from_numpy(order)
@@ -68,9 +68,16 @@ class OracleShardOps:
         return (keys[order_t], None if values is None else values[order_t], torch.from_numpy(dest),
                 torch.stack([counts_t, counts_t]))
 
-    def unpermute(self, grouped_values, grouped_flags, dest):
-        return (None if grouped_values is None else grouped_values[dest],
-                None if grouped_flags is None else grouped_flags[dest])
+    def unpermute(self, grouped_values, grouped_flags, dest, out_values=None, out_flags=None):
+        v = None if grouped_values is None else grouped_values[dest]
+        f = None if grouped_flags is None else grouped_flags[dest]
+        if v is not None and out_values is not None:
+            out_values[:] = v
+            v = out_values
+        if f is not None and out_flags is not None:
+            out_flags[:] = f
+            f = out_flags
+        return v, f
 
     def local_get(self, keys, segments, fallback_value):
         assert sum(rows for _, rows in segments) == keys.shape[0]
@@ -87,6 +94,9 @@ class OracleShardOps:
 
     def local_n_elements(self):
         return torch.tensor(self.local.n_elements)
+
+    def to_host(self, words):
+        return words.reshape(-1).tolist()
 
     def ready(self):
         return self.local._keys is not None
