@@ -569,14 +569,41 @@ __device__ __forceinline__ void dok_store_fallback(const DevTable &t, const Fall
   }
 }
 
-// Number of threads of the block with `pred` set, added to a device counter by ONE atomic per block: the counters
-// of a launch are a handful of addresses, and atomics on one address are served one after the other, so their
-// number per launch matters (a million per-warp atomics on one word cost about as much as the probing itself).
-// Every thread of the block must call it, with the same `counter`.
-__device__ __forceinline__ void dok_block_add(ll_t *counter, int pred) {
-  if (counter == nullptr) return;
-  const int c = __syncthreads_count(pred);
-  if (threadIdx.x == 0 && c) atomicAdd((ull_t *)counter, (ull_t)c);
+// Per-launch counters.  The counters of a launch are a handful of global addresses, and atomics on one address are
+// served one after the other, so a million per-warp atomics on one word cost about as much as the probing itself.
+// A block therefore tallies in shared memory (one vote and one shared atomic per warp and counter) and the LAST warp
+// of the block to finish adds the block's totals to global memory: one global atomic per block and counter, and no
+// barrier at the end of the kernel, where warps finish at very different times.
+// Slots 0 .. 7 go to counters[slot] (the dok_counter indices), slot 8 to `extra`.  Every thread of the block must
+// call begin and flush, and every lane of a warp must call add together.
+#define DOK_TALLY_SLOTS 9
+#define DOK_TALLY_EXTRA 8
+struct BlockTally { int v[DOK_TALLY_SLOTS]; int done; };
+
+__device__ __forceinline__ void dok_tally_begin(BlockTally &b) {
+  if (threadIdx.x < DOK_TALLY_SLOTS) b.v[threadIdx.x] = 0;
+  if (threadIdx.x == DOK_TALLY_SLOTS) b.done = 0;
+  __syncthreads();
+}
+__device__ __forceinline__ void dok_tally_add(BlockTally &b, int slot, int pred) {
+  const unsigned m = __ballot_sync(0xffffffffu, pred);
+  if ((threadIdx.x & 31) == 0 && m) atomicAdd(&b.v[slot], __popc(m));
+}
+__device__ __forceinline__ void dok_tally_flush(BlockTally &b, ll_t *counters, ll_t *extra) {
+  __syncwarp();
+  int last = 0;
+  if ((threadIdx.x & 31) == 0) {
+    __threadfence_block();
+    last = atomicAdd(&b.done, 1) == (int)(blockDim.x >> 5) - 1;
+  }
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (!last) return;
+  const int k = threadIdx.x & 31;
+  if (k < DOK_TALLY_SLOTS) {
+    const int c = ((volatile int *)b.v)[k];
+    ll_t *dst = k < DOK_TALLY_EXTRA ? (counters ? counters + k : nullptr) : extra;
+    if (c && dst) atomicAdd((ull_t *)dst, (ull_t)c);
+  }
 }
 
 // warp sum + one atomicAdd per warp (replaces warp_sum + atomicAdd of sparse_dok_tensor_impl.cu:52-55).

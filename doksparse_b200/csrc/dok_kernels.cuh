@@ -17,6 +17,8 @@ template <int SB, int LW, class Keys>
 __global__ void __launch_bounds__(DOK_TPB, (LW == 2 ? 8 : 1)) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
                                                     uint8_t *__restrict__ out_found, Fallback fb, ll_t *counters,
                                                     int count_probes) {
+  __shared__ BlockTally tally;
+  if (counters) dok_tally_begin(tally);
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   const bool active = e < keys.count();
   KeyHash kh{0, 0};
@@ -32,7 +34,8 @@ __global__ void __launch_bounds__(DOK_TPB, (LW == 2 ? 8 : 1)) k_get(DevTable t, 
   }
   if (active && out_found) out_found[e] = (uint8_t)hit;
   if (counters) {
-    dok_block_add(counters + DOK_CNT_HITS, hit);
+    dok_tally_add(tally, DOK_CNT_HITS, hit);
+    dok_tally_flush(tally, counters, nullptr);
     if (count_probes) dok_warp_add(counters + DOK_CNT_PROBES, probes);
   }
 }
@@ -82,6 +85,8 @@ __device__ __forceinline__ void dok_write_row(const DevTable &t, const DevHash &
 template <int SB, class Keys, class Values>
 __global__ void __launch_bounds__(DOK_TPB, 4) k_set_unique(DevTable t, DevHash hp, Keys keys, Values values,
                                                         uint8_t *__restrict__ out_stored, ll_t *counters) {
+  __shared__ BlockTally tally;
+  if (counters) dok_tally_begin(tally);
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   const bool active = e < keys.count();
   KeyHash kh{0, 0};
@@ -93,10 +98,11 @@ __global__ void __launch_bounds__(DOK_TPB, 4) k_set_unique(DevTable t, DevHash h
     if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
   }
   if (counters) {
-    dok_block_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
-    dok_block_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
-    dok_block_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
-    dok_block_add(counters + DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
+    dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
+    dok_tally_add(tally, DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
+    dok_tally_add(tally, DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
+    dok_tally_add(tally, DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
+    dok_tally_flush(tally, counters, nullptr);
   }
 }
 
@@ -113,6 +119,8 @@ template <int SB, class Keys, class Values>
 __global__ void __launch_bounds__(DOK_TPB, 4) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
                                                        ll_t *__restrict__ slot_out, ll_t epoch,
                                                        uint8_t *__restrict__ out_stored, ll_t *counters) {
+  __shared__ BlockTally tally;
+  dok_tally_begin(tally);
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   const bool active = e < keys.count();
   KeyHash kh{0, 0};
@@ -134,14 +142,15 @@ __global__ void __launch_bounds__(DOK_TPB, 4) k_set_claim(DevTable t, DevHash hp
     }
     if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
   }
-  dok_block_add(slot_out + keys.count(), dup);
+  dok_tally_add(tally, DOK_TALLY_EXTRA, dup);
   if (counters) {
-    dok_block_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
-    dok_block_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
-    dok_block_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
-    dok_block_add(counters + DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
-    dok_block_add(counters + DOK_CNT_DUPLICATES, dup);
+    dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
+    dok_tally_add(tally, DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
+    dok_tally_add(tally, DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
+    dok_tally_add(tally, DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
+    dok_tally_add(tally, DOK_CNT_DUPLICATES, dup);
   }
+  dok_tally_flush(tally, counters, slot_out + keys.count());
 }
 
 // Second kernel: does nothing unless the first one counted duplicates.  Then the row that owns a conflicted
@@ -168,6 +177,8 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_resolve(DevTable t, DevHash hp,
 template <int SB, int REMOVE, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys keys, uint8_t *__restrict__ out_flags,
                                                   ll_t *counters) {
+  __shared__ BlockTally tally;
+  if (counters) dok_tally_begin(tally);
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   const bool active = e < keys.count();
   KeyHash kh{0, 0};
@@ -176,7 +187,10 @@ __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys k
   int hit = active && loc.found >= 0;
   if (REMOVE && hit) hit = dok_cas_tag(t, loc.found, kh.uuid, DOK_REMOVED) == kh.uuid;
   if (active && out_flags) out_flags[e] = (uint8_t)hit;
-  dok_block_add(counters ? counters + DOK_CNT_HITS : nullptr, hit);
+  if (counters) {
+    dok_tally_add(tally, DOK_CNT_HITS, hit);
+    dok_tally_flush(tally, counters, nullptr);
+  }
 }
 
 static __global__ void k_fill_i64(ll_t *p, ll_t n, ll_t v) {
@@ -188,6 +202,8 @@ static __global__ void k_fill_i64(ll_t *p, ll_t n, ll_t v) {
 template <int SB, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, Keys keys, ll_t *__restrict__ scratch,
                                                        ll_t scratch_slots, ll_t *counters) {
+  __shared__ BlockTally tally;
+  dok_tally_begin(tally);
   const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   const bool active = e < keys.count();
   KeyHash kh{0, 0};
@@ -207,7 +223,8 @@ __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, K
       if (++slot == scratch_slots) slot = 0;
     }
   }
-  dok_block_add(counters + DOK_CNT_CLAIMED_EMPTY, claimed);
+  dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, claimed);
+  dok_tally_flush(tally, counters, nullptr);
 }
 
 // ---------------------------------------------------------------------------------------------------------
