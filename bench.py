@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--batch-log2", type=int, default=25, help="queries per GPU and step (default 2^25 = 32 Mi)")
     ap.add_argument("--no-ref-gpu", action="store_true",
                     help="reference arm: skip the extra leg that runs the reference's kernels on the GPU")
+    ap.add_argument("--no-peer", action="store_true",
+                    help="multi-GPU: exchange rows with NCCL all-to-all instead of stores into the peers' memory")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -348,7 +350,9 @@ def workload_config(args, world):
         "batch_per_gpu": 1 << args.batch_log2, "shards": world,
         "l2_policy": f"inputs larger than L2: {N_BATCHES} rotating batches of {(1 << args.batch_log2) * 8 >> 20} MiB keys, "
                      f"table {(int((1 << args.keys_log2) / LOAD_FACTOR) * 16) >> 20} MiB per GPU",
-        "parallelism": f"hash-sharded x{world}, NCCL all-to-all" if world > 1 else "single GPU",
+        "parallelism": ("single GPU" if world == 1 else
+                        f"hash-sharded x{world}, " + ("NCCL all-to-all" if getattr(args, "no_peer", False) else
+                                                      "rows stored into the owners' memory over NVLink (peer exchange)")),
     }
 
 
@@ -376,7 +380,10 @@ def run_candidate(args):
     n_keys, q = 1 << args.keys_log2, 1 << args.batch_log2
     total_keys = n_keys * world
     nb = int(n_keys / LOAD_FACTOR)
-    table = ShardedClosedHashmap(nb, device=device, rehash_threshold=0.95, **fixed_parameters())
+    # rows of a batch go straight into the owners' memory over NVLink (sized for a batch plus skew and padding);
+    # --no-peer keeps the NCCL all-to-all exchange
+    peer_rows = 0 if (world == 1 or args.no_peer) else int(q * 1.25) + 16 * world
+    table = ShardedClosedHashmap(nb, device=device, rehash_threshold=0.95, peer_capacity_rows=peer_rows, **fixed_parameters())
 
     # ---- build (untimed): rank r inserts key indices [r * n_keys, (r + 1) * n_keys), routed to their owners
     chunk = min(n_keys, 1 << 25)

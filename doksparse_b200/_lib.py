@@ -103,6 +103,12 @@ def _declare(lib):
         "dok_shard_partition_scatter": ([P, I, P, I, I64, I, P, P, P, P, P, P, P], I),
         "dok_shard_unpermute": ([P, P, P, I, I64, P, P, P], I),
         "dok_words_to_pinned": ([P, P, I, P], I),
+        "dok_shard_partition_scatter_peer": ([P, I, P, I, I64, I, P, P, P, P, P, P, P, P], I),
+        "dok_peer_alloc": ([I64, P], I),
+        "dok_peer_free": ([P], I),
+        "dok_peer_export": ([P, P], I),
+        "dok_peer_open": ([P, P], I),
+        "dok_peer_close": ([P], I),
         "dok_shard_owner": ([HP, P, I64, I, P, P], I),
         "dok_diag_random_reads": ([P, I64, I64, ctypes.c_uint64, P, P], I),
     }

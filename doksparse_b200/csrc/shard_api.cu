@@ -76,25 +76,40 @@ static __global__ void k_part_shard_counts(const ll_t *tile_offsets, int n_shard
   }
 }
 
+// Where the rows of each owner go.  Local exchange buffer: every owner the same base, row0 < 0 = "at the start of
+// the owner's segment in this rank's grouped order".  Peer exchange: base = the owner GPU's receive buffer (mapped into this process), row0 = where THIS rank's segment
+// starts inside it; the rows then cross NVLink as plain stores while the tile is being partitioned, and no separate
+// exchange pass follows.
+struct PartDest {
+  char *keys[DOK_MAX_SHARDS];
+  char *values[DOK_MAX_SHARDS];
+  ll_t row0[DOK_MAX_SHARDS];
+};
+
 // Pass 2: every row to its place.  Rows of one owner keep their batch order: inside a tile the place of a row is
 // the number of same-owner rows before it in (round, warp, lane) order -- per-(round, warp) counts from warp
 // matches, one exclusive scan per owner over the ROUNDS * warps counts, and the row's rank among its warp's
 // same-owner lanes -- behind the tile's offset from pass 1.  Three block barriers per tile.
+// dest_index[e] is always the row's position in THIS rank's grouped order (segments at the padded local offsets),
+// which is where the owner's answer for the row will be found.
 static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, int kb, const char *__restrict__ values,
                                                                  int vb, const uint8_t *__restrict__ owners,
                                                                  int n_shards, ll_t tiles,
                                                                  const ll_t *__restrict__ tile_offsets,
-                                                                 const ll_t *__restrict__ shard_counts, char *keys_out,
-                                                                 char *values_out, ll_t *__restrict__ dest_index) {
+                                                                 const ll_t *__restrict__ shard_counts,
+                                                                 const __grid_constant__ PartDest dst,
+                                                                 ll_t *__restrict__ dest_index) {
   constexpr int WARPS = DOK_TPB / 32, CELLS = DOK_PART_ROUNDS * WARPS;        // cells of one owner, in row order
   __shared__ int before[DOK_MAX_SHARDS][CELLS];   // same-owner rows of the tile before cell (round, warp)
-  __shared__ ll_t tile_start[DOK_MAX_SHARDS];     // first output row of this tile's rows for each owner
+  __shared__ ll_t tile_first[DOK_MAX_SHARDS];     // rows of this owner in earlier tiles
+  __shared__ ll_t local_start[DOK_MAX_SHARDS];    // start of the owner's segment in this rank's grouped order
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < n_shards * CELLS; i += DOK_TPB) (&before[0][0])[i] = 0;
   if (threadIdx.x == 0) {
     ll_t padded = 0;                              // owner o's segment starts at the sum of the padded counts before it
     for (int o = 0; o < n_shards; o++) {
-      tile_start[o] = padded + tile_offsets[(ll_t)o * tiles + blockIdx.x] - tile_offsets[(ll_t)o * tiles];
+      tile_first[o] = tile_offsets[(ll_t)o * tiles + blockIdx.x] - tile_offsets[(ll_t)o * tiles];
+      local_start[o] = padded;
       padded += shard_counts[n_shards + o];
     }
   }
@@ -130,11 +145,13 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
 #pragma unroll
   for (int r = 0; r < DOK_PART_ROUNDS; r++) {
     if (owner[r] < 0) continue;
+    const int o = owner[r];
     const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    const ll_t dest = tile_start[owner[r]] + before[owner[r]][r * WARPS + warp] + rank[r];
-    if (dest_index) dest_index[e] = dest;
-    dok_copy_row(keys_out + dest * kb, (const char *)keys.keys + e * kb, kb);
-    if (values) dok_copy_row(values_out + dest * vb, values + e * vb, vb);
+    const ll_t in_segment = tile_first[o] + before[o][r * WARPS + warp] + rank[r];
+    if (dest_index) dest_index[e] = local_start[o] + in_segment;
+    const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + in_segment;
+    dok_copy_row(dst.keys[o] + row * kb, (const char *)keys.keys + e * kb, kb);
+    if (values) dok_copy_row(dst.values[o] + row * vb, values + e * vb, vb);
   }
 }
 
@@ -184,10 +201,85 @@ int dok_shard_partition_scatter(const void *keys, int key_bytes, const void *val
   if (values && (!values_out || value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES)) return DOK_BAD_ARG;
   const ll_t tiles = dok_partition_tiles(n);
   RowKeys rk{keys, n};
+  // every owner's segment lies in the same local buffer, at the prefix sum of the padded counts, which the kernel
+  // derives from shard_counts on the device (row0 < 0 asks for that): the host never needs the counts here
+  PartDest dst;
+  memset(&dst, 0, sizeof(dst));
+  for (int o = 0; o < n_shards; o++) { dst.keys[o] = (char *)keys_out; dst.values[o] = (char *)values_out; dst.row0[o] = -1; }
   k_part_scatter<<<(unsigned)tiles, DOK_TPB, 0, (cudaStream_t)stream>>>(
       rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, tiles, (const ll_t *)tile_offsets,
-      (const ll_t *)shard_counts, (char *)keys_out, (char *)values_out, (ll_t *)dest_index);
+      (const ll_t *)shard_counts, dst, (ll_t *)dest_index);
   return dok_check_launch();
+}
+
+int dok_shard_partition_scatter_peer(const void *keys, int key_bytes, const void *values, int value_bytes, int64_t n,
+                                     int n_shards, const uint8_t *owners, const int64_t *tile_offsets,
+                                     const int64_t *shard_counts, void *const *peer_keys, void *const *peer_values,
+                                     const int64_t *peer_row0, int64_t *dest_index, void *stream) {
+  if (n < 0 || n > DOK_MAX_BATCH || n_shards < 1 || n_shards > DOK_MAX_SHARDS) return DOK_BAD_ARG;
+  if (n == 0) return DOK_OK;
+  if (!keys || key_bytes < 1 || !owners || !tile_offsets || !shard_counts || !peer_keys || !peer_row0) return DOK_BAD_ARG;
+  if (values && (!peer_values || value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES)) return DOK_BAD_ARG;
+  PartDest dst;
+  memset(&dst, 0, sizeof(dst));
+  for (int o = 0; o < n_shards; o++) {
+    if (!peer_keys[o] || peer_row0[o] < 0 || (values && !peer_values[o])) return DOK_BAD_ARG;
+    dst.keys[o] = (char *)peer_keys[o];
+    dst.values[o] = values ? (char *)peer_values[o] : nullptr;
+    dst.row0[o] = peer_row0[o];
+  }
+  const ll_t tiles = dok_partition_tiles(n);
+  RowKeys rk{keys, n};
+  k_part_scatter<<<(unsigned)tiles, DOK_TPB, 0, (cudaStream_t)stream>>>(
+      rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, tiles, (const ll_t *)tile_offsets,
+      (const ll_t *)shard_counts, dst, (ll_t *)dest_index);
+  return dok_check_launch();
+}
+
+/* ---- exchange arena: device memory that the other ranks of the node map into their address space ------------ */
+
+int dok_peer_alloc(int64_t bytes, void **ptr_out) {
+  if (bytes < 1 || !ptr_out) return DOK_BAD_ARG;
+  void *p = nullptr;
+  const cudaError_t err = cudaMalloc(&p, (size_t)bytes);
+  if (err != cudaSuccess) { dok_last_error_slot() = (int)err; cudaGetLastError(); return DOK_CUDA_ERROR; }
+  *ptr_out = p;
+  return DOK_OK;
+}
+
+int dok_peer_free(void *ptr) {
+  if (!ptr) return DOK_OK;
+  const cudaError_t err = cudaFree(ptr);
+  if (err != cudaSuccess) { dok_last_error_slot() = (int)err; cudaGetLastError(); return DOK_CUDA_ERROR; }
+  return DOK_OK;
+}
+
+int dok_peer_export(void *ptr, uint8_t *handle_out /* DOK_PEER_HANDLE_BYTES */) {
+  if (!ptr || !handle_out) return DOK_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  const cudaError_t err = cudaIpcGetMemHandle(&h, ptr);
+  if (err != cudaSuccess) { dok_last_error_slot() = (int)err; cudaGetLastError(); return DOK_CUDA_ERROR; }
+  static_assert(sizeof(h) == DOK_PEER_HANDLE_BYTES, "handle size");
+  memcpy(handle_out, &h, sizeof(h));
+  return DOK_OK;
+}
+
+int dok_peer_open(const uint8_t *handle, void **ptr_out) {
+  if (!handle || !ptr_out) return DOK_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void *p = nullptr;
+  const cudaError_t err = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (err != cudaSuccess) { dok_last_error_slot() = (int)err; cudaGetLastError(); return DOK_CUDA_ERROR; }
+  *ptr_out = p;
+  return DOK_OK;
+}
+
+int dok_peer_close(void *ptr) {
+  if (!ptr) return DOK_OK;
+  const cudaError_t err = cudaIpcCloseMemHandle(ptr);
+  if (err != cudaSuccess) { dok_last_error_slot() = (int)err; cudaGetLastError(); return DOK_CUDA_ERROR; }
+  return DOK_OK;
 }
 
 int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found, const int64_t *dest_index,

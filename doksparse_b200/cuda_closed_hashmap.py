@@ -585,7 +585,7 @@ class CudaClosedHashmap:
         if values is None:
             values = torch.empty(n, *self.value_shape, device=self.device, dtype=self._value_dtype)
         else:
-            assert values.dtype == self._value_dtype and values.device == self.device and values.is_contiguous()
+            assert values.dtype == self._value_dtype and values.is_cuda and values.is_contiguous()
             assert values.shape == (n, *self.value_shape)
         if is_found is None:
             is_found = torch.empty(n, device=self.device, dtype=torch.bool)
@@ -609,11 +609,15 @@ class CudaClosedHashmap:
         return cnt[L.CNT_PROBES].item() / max(n, 1), cnt[L.CNT_HITS].item() / max(n, 1)
 
     # ------------------------------------------------------------------ remove
-    def remove_rows(self, keys):
-        """Kernel only: flags aligned to the rows given (no dedup, no sort).  Equal rows report once."""
+    def remove_rows(self, keys, is_removed=None):
+        """Kernel only: flags aligned to the rows given (no dedup, no sort).  Equal rows report once.
+        `is_removed`: optional preallocated bool[n] output."""
         keys = keys.contiguous()
         n = keys.shape[0]
-        is_removed = torch.empty(n, device=self.device, dtype=torch.bool)
+        if is_removed is None:
+            is_removed = torch.empty(n, device=self.device, dtype=torch.bool)
+        else:
+            assert is_removed.dtype == torch.bool and is_removed.shape == (n,) and is_removed.is_contiguous()
         cnt = self._counters()
         with torch.cuda.device(self.device):
             L.check(L.lib().dok_map_remove(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(is_removed), L.ptr(cnt),

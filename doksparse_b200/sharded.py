@@ -38,6 +38,9 @@ class CudaShardOps:
         self._routing = {k: torch.as_tensor(v).cpu().tolist() for k, v in params.items()}
         self._hp = None
         self._pinned = None
+        self._peer = None
+        self._copy_stream = None
+        self._in_flight = []
 
     def _routing_hash(self, keys):
         if self._hp is None:
@@ -53,6 +56,128 @@ class CudaShardOps:
                 hp.key_perm[i] = i
             self._hp = hp
         return ctypes.byref(self._hp)
+
+    # ------------------------------------------------------------------ peer exchange (NVLink, no exchange pass)
+    supports_peer = True
+
+    class _RawDeviceBytes:
+        """Lets torch wrap device memory it did not allocate (the exchange arena, a peer's mapping of its arena)."""
+
+        def __init__(self, ptr, nbytes):
+            self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
+
+    def peer_setup(self, group, world, rank, capacity_rows, key_row, value_row):
+        """Collective.  Allocates this rank's exchange arena, maps every peer's, and returns True when all ranks
+        succeeded (otherwise the arena is dropped everywhere and the NCCL exchange stays in use).
+        key_row / value_row = (row shape, dtype).  Arena = two generations (alternating per batch) of
+        {inbox keys | inbox values | result values | result flags}, each for capacity_rows rows."""
+        lib = L.lib()
+        self._peer = None
+        (kshape, kdtype), (vshape, vdtype) = key_row, value_row
+        kb = int(np.prod(kshape)) * torch.empty((), dtype=kdtype).element_size()
+        vb = int(np.prod(vshape)) * torch.empty((), dtype=vdtype).element_size()
+        cap = int(capacity_rows)
+        up = lambda x: (x + 255) // 256 * 256
+        sizes = [up(cap * kb), up(cap * vb), up(cap * vb), up(cap)]
+        gen_bytes = sum(sizes)
+        offs = [sum(sizes[:i]) for i in range(4)]
+        ok, base, handle = 1, ctypes.c_void_p(), (ctypes.c_uint8 * 64)()
+        with torch.cuda.device(self.device):
+            if lib.dok_peer_alloc(2 * gen_bytes, ctypes.byref(base)) != 0 or lib.dok_peer_export(base, handle) != 0:
+                ok = 0
+        handles = [None] * world
+        dist.all_gather_object(handles, (ok, bytes(handle)), group=group)
+        ok = min(h[0] for h in handles)
+        bases = [None] * world
+        if ok:
+            with torch.cuda.device(self.device):
+                for r in range(world):
+                    if r == rank:
+                        bases[r] = base.value
+                        continue
+                    p = ctypes.c_void_p()
+                    buf = (ctypes.c_uint8 * 64).from_buffer_copy(handles[r][1])
+                    if lib.dok_peer_open(buf, ctypes.byref(p)) != 0:
+                        ok = 0
+                        break
+                    bases[r] = p.value
+        flag = torch.tensor([ok], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) == 0:
+            with torch.cuda.device(self.device):
+                for r in range(world):
+                    if bases[r] is not None and r != rank:
+                        lib.dok_peer_close(ctypes.c_void_p(bases[r]))
+                if base.value:
+                    lib.dok_peer_free(base)
+            return False
+        views = [torch.as_tensor(self._RawDeviceBytes(bases[r], 2 * gen_bytes), device=self.device) for r in range(world)]
+        self._peer = dict(world=world, rank=rank, cap=cap, kb=kb, vb=vb, kshape=tuple(kshape), kdtype=kdtype,
+                          vshape=tuple(vshape), vdtype=vdtype, gen_bytes=gen_bytes, offs=offs, bases=bases, views=views,
+                          own_base=base, token=torch.zeros(1, device=self.device), group=group)
+        return True
+
+    def peer_close(self):
+        """Collective in effect: call it on every rank, after all of them have finished using the exchange."""
+        p, self._peer = getattr(self, "_peer", None), None
+        if not p:
+            return
+        lib = L.lib()
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            for r in range(p["world"]):
+                if r != p["rank"]:
+                    lib.dok_peer_close(ctypes.c_void_p(p["bases"][r]))
+            lib.dok_peer_free(p["own_base"])
+
+    def _peer_region(self, rank, generation, which, rows=None, row0=0):
+        """Typed view of region `which` (0 inbox keys, 1 inbox values, 2 result values, 3 result flags) of `rank`'s
+        arena, generation 0 / 1, rows [row0, row0 + rows)."""
+        p = self._peer
+        rows = p["cap"] - row0 if rows is None else rows
+        width, shape, dtype = [(p["kb"], p["kshape"], p["kdtype"]), (p["vb"], p["vshape"], p["vdtype"]),
+                               (p["vb"], p["vshape"], p["vdtype"]), (1, (), torch.bool)][which]
+        lo = generation * p["gen_bytes"] + p["offs"][which] + row0 * width
+        flat = p["views"][rank][lo:lo + rows * width]
+        return flat.view(dtype).view((rows,) + tuple(shape))
+
+    def peer_fence(self):
+        """Every rank's earlier work on its stream (stores into peers' arenas included) is complete before any rank's
+        later work starts: a one-element all-reduce, ordered on the stream, not blocking the host."""
+        dist.all_reduce(self._peer["token"], group=self._peer["group"])
+
+    def partition_count(self, keys, world):
+        """First pass of the partition -> (owners, tile offsets, counts[2 * world] on the device)."""
+        lib = L.lib()
+        n = keys.shape[0]
+        with torch.cuda.device(self.device):
+            tiles = lib.dok_partition_tiles(n)
+            offsets = torch.empty(world * tiles + 1, device=self.device, dtype=torch.long)
+            counts = torch.empty(2 * world, device=self.device, dtype=torch.long)
+            owners = torch.empty(n, device=self.device, dtype=torch.uint8)
+            L.check(lib.dok_shard_partition_count(self._routing_hash(keys), L.ptr(keys), n, world, L.ptr(owners),
+                                                  L.ptr(offsets), L.ptr(counts), L.stream_ptr(self.device)),
+                    "dok_shard_partition_count")
+        return owners, offsets, counts
+
+    def scatter_to_peers(self, keys, values, world, owners, offsets, counts, generation, row0, want_dest):
+        """Second pass with the owners' inboxes as destinations; row0[o] = first row of this rank's segment there."""
+        lib = L.lib()
+        p = self._peer
+        n = keys.shape[0]
+        gen = generation * p["gen_bytes"]
+        arr_p = ctypes.c_void_p * world
+        peer_keys = arr_p(*[p["bases"][o] + gen + p["offs"][0] for o in range(world)])
+        peer_values = arr_p(*[p["bases"][o] + gen + p["offs"][1] for o in range(world)])
+        rows = (ctypes.c_int64 * world)(*[int(r) for r in row0])
+        dest = torch.empty(n, device=self.device, dtype=torch.long) if want_dest else None
+        vb = 0 if values is None else p["vb"]
+        with torch.cuda.device(self.device):
+            L.check(lib.dok_shard_partition_scatter_peer(L.ptr(keys), p["kb"], L.ptr(values), vb, n, world, L.ptr(owners),
+                                                         L.ptr(offsets), L.ptr(counts), peer_keys,
+                                                         peer_values if values is not None else None, rows, L.ptr(dest),
+                                                         L.stream_ptr(self.device)), "dok_shard_partition_scatter_peer")
+        return dest
 
     def partition(self, keys, values, world, want_dest=True):
         """-> (grouped_keys, grouped_values or None, dest_index, counts[2, world] on the device): rows per owner, and
@@ -129,6 +254,46 @@ class CudaShardOps:
                 flags[start:start + rows] = self.local.remove_rows(keys[start:start + rows])
         return flags
 
+    def local_answer(self, keys, values, flags, fallback_value, remote):
+        """get (values given) or remove (values None) of one source's rows, answers delivered into `values` /
+        `flags`.  For another rank's rows (`remote`) those are views of the asker's memory: the kernel then answers
+        into local buffers and a bulk copy on a side stream carries them over NVLink while the next source's rows are
+        being probed -- row-sized stores from the probing kernel itself use the link far worse."""
+        if not remote:
+            self._answer(keys, values, flags, fallback_value)
+            return
+        local_values = None if values is None else torch.empty_like(values)
+        local_flags = torch.empty_like(flags)
+        self._answer(keys, local_values, local_flags, fallback_value)
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+        answered = torch.cuda.Event()
+        answered.record()
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(answered)
+            if values is not None:
+                values.copy_(local_values, non_blocking=True)
+            flags.copy_(local_flags, non_blocking=True)
+        self._in_flight.append((local_values, local_flags))
+
+    def answers_delivered(self):
+        """The current stream waits for the bulk copies of local_answer; their source buffers may then be reused."""
+        if self._in_flight:
+            done = torch.cuda.Event()
+            done.record(self._copy_stream)
+            torch.cuda.current_stream(self.device).wait_event(done)
+            self._in_flight = []
+
+    def _answer(self, keys, values, flags, fallback_value):
+        if self.local._slots is None:              # this shard holds nothing yet: every row is a miss
+            if values is not None:
+                values[:] = torch.as_tensor(0 if fallback_value is None else fallback_value, dtype=values.dtype)
+            flags[:] = False
+        elif values is not None:
+            self.local.get(keys, fallback_value, values=values, is_found=flags)
+        else:
+            self.local.remove_rows(keys, is_removed=flags)
+
     def local_n_elements(self):
         return self.local._n_elements
 
@@ -163,7 +328,7 @@ class ShardedClosedHashmap:
     """
 
     def __init__(self, n_buckets_per_shard, prime1, prime2, alpha1, alpha2, beta1, beta2, group=None, device=None,
-                 rehash_factor=2.0, rehash_threshold=0.75, ops=None, pipeline_chunks=2):
+                 rehash_factor=2.0, rehash_threshold=0.75, ops=None, pipeline_chunks=2, peer_capacity_rows=0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -176,6 +341,13 @@ class ShardedClosedHashmap:
             ops = CudaShardOps(device, n_buckets_per_shard, params, rehash_factor, rehash_threshold)
         self.ops = ops
         self.pipeline_chunks = max(1, int(pipeline_chunks))     # must be the same on every rank
+        # Peer exchange (ranks of ONE node, NVLink): with peer_capacity_rows > 0 (the same on every rank) the rows of
+        # a batch are stored straight into the owners' memory by the partition kernel, and answers straight into the
+        # askers', instead of travelling through all-to-all passes.  A batch that does not fit the capacity (rows
+        # received by any owner, or rows of any rank's own batch, padding included) takes the all-to-all path.
+        self._peer_capacity = int(peer_capacity_rows) if (self.world > 1 and self.world <= 16) else 0
+        self._peer_on = False
+        self._peer_seq = 0
         self._value_shape = None
         self._value_dtype = None
 
@@ -231,13 +403,85 @@ class ShardedClosedHashmap:
         c = self.pipeline_chunks if (pipelined and self.world > 1) else 1
         return [(n * i // c, n * (i + 1) // c) for i in range(c)]
 
+    # ------------------------------------------------------------------ peer exchange
+    def _peer_plan(self, keys):
+        """First partition pass and the gathered count matrix -> plan, or None when this batch must take the
+        all-to-all path (the decision is made from the same matrix on every rank, so all ranks agree)."""
+        w, r = self.world, self.rank
+        keys = keys.contiguous()
+        owners, offsets, counts = self.ops.partition_count(keys, w)
+        matrix = self.ops.empty((w, 2 * w), torch.long)
+        dist.all_gather_into_tensor(matrix, counts, group=self.group)
+        flat = self.ops.to_host(matrix)
+        exact = [[int(flat[s * 2 * w + o]) for o in range(w)] for s in range(w)]        # [source][owner]
+        padded = [[int(flat[s * 2 * w + w + o]) for o in range(w)] for s in range(w)]
+        cap = self._peer_capacity
+        if max(sum(padded[s][o] for s in range(w)) for o in range(w)) > cap or max(sum(row) for row in padded) > cap:
+            return None
+        gen = self._peer_seq & 1
+        self._peer_seq += 1
+        starts, run = [], 0
+        for s in range(w):                                  # my inbox: sources in rank order, at padded offsets
+            starts.append(run)
+            run += padded[s][r]
+        return dict(keys=keys, owners=owners, offsets=offsets, counts=counts, exact=exact, padded=padded, gen=gen,
+                    row0=[sum(padded[s][o] for s in range(r)) for o in range(w)],
+                    segments=[(starts[s], exact[s][r]) for s in range(w)], inbox_rows=run)
+
+    def _peer_lookup(self, plan, with_values, fallback_value):
+        """get / remove over the peer exchange: keys into the owners' inboxes, answers straight into the askers'
+        result regions, two stream-ordered fences, inverse permutation."""
+        w, r, ops = self.world, self.rank, self.ops
+        gen, exact, padded = plan["gen"], plan["exact"], plan["padded"]
+        dest = ops.scatter_to_peers(plan["keys"], None, w, plan["owners"], plan["offsets"], plan["counts"], gen,
+                                    plan["row0"], want_dest=True)
+        ops.peer_fence()
+        owned_keys = ops._peer_region(r, gen, 0, rows=plan["inbox_rows"])
+        order = list(range(w))
+        if with_values:       # lookups commute: other ranks' rows first, so that the copy of their answers over NVLink
+            order = [s for s in order if s != r] + [r]      # runs while this rank's own rows are probed
+        for s in order:       # removals are applied in rank order: which of two equal keys reports is defined by it
+            start, rows = plan["segments"][s]
+            if not rows:
+                continue
+            at = sum(padded[s][o] for o in range(r))        # my segment in source s's grouped order
+            flags = ops._peer_region(s, gen, 3, rows=rows, row0=at)
+            values = ops._peer_region(s, gen, 2, rows=rows, row0=at) if with_values else None
+            ops.local_answer(owned_keys[start:start + rows], values, flags, fallback_value, remote=(s != r))
+        ops.answers_delivered()
+        ops.peer_fence()
+        n_mine = sum(padded[r])
+        res_flags = ops._peer_region(r, gen, 3, rows=n_mine).view(torch.uint8)
+        res_values = ops._peer_region(r, gen, 2, rows=n_mine) if with_values else None
+        out_values, out_flags = ops.unpermute(res_values, res_flags, dest)
+        return out_values, out_flags.view(torch.bool)
+
     # ------------------------------------------------------------------ operations
     def set(self, keys, values, assume_unique=False):
         """Collective insert-or-assign.  `assume_unique` promises pairwise different keys across ALL ranks' batches."""
         if self._value_shape is None:
             self._value_shape, self._value_dtype = tuple(values.shape[1:]), values.dtype
+            if self._peer_capacity and getattr(self.ops, "supports_peer", False):
+                self._peer_on = self.ops.peer_setup(self.group, self.world, self.rank, self._peer_capacity,
+                                                    (tuple(keys.shape[1:]), keys.dtype), (self._value_shape, self._value_dtype))
+        if self._peer_on:
+            plan = self._peer_plan(keys)
+            if plan is not None:
+                self.ops.scatter_to_peers(plan["keys"], values.contiguous(), self.world, plan["owners"], plan["offsets"],
+                                          plan["counts"], plan["gen"], plan["row0"], want_dest=False)
+                self.ops.peer_fence()
+                owned_keys = self.ops._peer_region(self.rank, plan["gen"], 0, rows=plan["inbox_rows"])
+                owned_values = self.ops._peer_region(self.rank, plan["gen"], 1, rows=plan["inbox_rows"])
+                self.ops.local_set(owned_keys, owned_values, plan["segments"], assume_unique)
+                return
         owned_keys, owned_values, segments, _, _, _ = self._route(keys, values, want_dest=False)
         self.ops.local_set(owned_keys, owned_values, segments, assume_unique)
+
+    def close(self):
+        """Releases the peer exchange arena (every rank, after the last operation)."""
+        if self._peer_on:
+            self._peer_on = False
+            self.ops.peer_close()
 
     def _lookup(self, keys, local_op, with_values, fallback_value=None):
         """Shared body of get and remove.  For get the batch is cut into `pipeline_chunks` pieces that move through
@@ -308,6 +552,10 @@ class ShardedClosedHashmap:
             if not self.ops.ready():
                 return self._lookup(keys, None, True, fallback_value)
             return self.ops.local_get(keys, [(0, keys.shape[0])], fallback_value)
+        if self._peer_on:
+            plan = self._peer_plan(keys)
+            if plan is not None:
+                return self._peer_lookup(plan, True, fallback_value)
         return self._lookup(keys, lambda k, seg: self.ops.local_get(k, seg, fallback_value), True, fallback_value)
 
     def remove(self, keys):
@@ -316,6 +564,10 @@ class ShardedClosedHashmap:
             raise RuntimeError("store something first")
         if self.world == 1 and self.ops.ready():
             return self.ops.local_remove(keys, [(0, keys.shape[0])])
+        if self._peer_on:
+            plan = self._peer_plan(keys)
+            if plan is not None:
+                return self._peer_lookup(plan, False, None)[1]
         return self._lookup(keys, lambda k, seg: self.ops.local_remove(k, seg), False)[1]
 
     @property

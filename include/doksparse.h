@@ -261,6 +261,27 @@ int dok_shard_partition_scatter(const void *keys, int key_bytes, const void *val
                                 const int64_t *shard_counts, void *keys_out, void *values_out, int64_t *dest_index,
                                 void *stream);
 
+/* The same scatter with one destination per owner: peer_keys[o] / peer_values[o] are the owner GPU's receive
+ * buffers mapped into this process (dok_peer_open; this rank's own buffer for o == rank) and peer_row0[o] >= 0 the
+ * row at which THIS rank's segment starts inside them.  The rows cross NVLink as plain stores while the batch is
+ * being partitioned; no exchange pass follows.  dest_index is as above (positions in this rank's own grouped order,
+ * where the owner's answers will be placed).  The caller orders the launch against the owners' reads (a collective
+ * on the stream before the owners touch the rows, double buffering against the next batch). */
+int dok_shard_partition_scatter_peer(const void *keys, int key_bytes, const void *values, int value_bytes, int64_t n,
+                                     int n_shards, const uint8_t *owners, const int64_t *tile_offsets,
+                                     const int64_t *shard_counts, void *const *peer_keys, void *const *peer_values,
+                                     const int64_t *peer_row0, int64_t *dest_index, void *stream);
+
+/* Exchange arena: device memory of this process that other processes of the node map (CUDA IPC, peer access over
+ * NVLink).  dok_peer_alloc allocates outside any caching allocator (an IPC handle names a whole allocation);
+ * dok_peer_export fills a DOK_PEER_HANDLE_BYTES handle to send to the peers; dok_peer_open maps a peer's handle. */
+#define DOK_PEER_HANDLE_BYTES 64
+int dok_peer_alloc(int64_t bytes, void **ptr_out);
+int dok_peer_free(void *ptr);
+int dok_peer_export(void *ptr, uint8_t *handle_out);
+int dok_peer_open(const uint8_t *handle, void **ptr_out);
+int dok_peer_close(void *ptr);
+
 /* n_words (<= 1024) int64 words from device memory to PINNED host memory (cudaHostAlloc / torch pin_memory), written
  * by a kernel through the mapped address instead of a copy-engine transfer, so that the read-back of the row counts
  * does not queue behind bulk device-to-host copies of other streams.  Complete when the stream reaches this point. */

@@ -1,0 +1,76 @@
+"""Worker of tests/test_sharded_multi_gpu.py (one process per GPU, launched by torch.distributed.run).
+
+The same operation stream goes through two sharded maps, one exchanging rows with NCCL all-to-all and one storing
+them straight into the peers' memory, and -- gathered on rank 0 -- through ONE serial CPU oracle table that receives
+the ranks' batches in rank order.  Everything a caller can observe must agree bit for bit."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from doksparse_b200.sharded import ShardedClosedHashmap  # noqa: E402
+from oracle import port  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    np.random.seed(7)
+    params = port.draw_hash_parameters(1 << 17, 1)
+    nb = 1 << 17
+    cap = 30000
+    via_nccl = ShardedClosedHashmap(nb, device=device, **params)
+    via_peer = ShardedClosedHashmap(nb, device=device, peer_capacity_rows=cap, **params)
+    single = port.OracleHashmap(n_buckets=nb * world, **params) if rank == 0 else None
+    rng = np.random.default_rng(100 + rank)
+
+    def gather(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    for step in range(7):
+        n = [9000, 0, 12000, 5, 40000, 7000, 15000][(step + rank) % 7]     # 40000 rows exceed the capacity: all-to-all
+        keys = rng.integers(0, 50000, size=(n, 1), dtype=np.int64)          # duplicates within and across ranks
+        values = rng.standard_normal((n, 2)).astype(np.float32)
+        queries = rng.integers(0, 60000, size=(n // 2 + 3, 1), dtype=np.int64)
+        doomed = np.unique(rng.integers(0, 60000, size=(n // 5 + 1, 1), dtype=np.int64), axis=0)
+        tk, tv = torch.from_numpy(keys).to(device), torch.from_numpy(values).to(device)
+        tq, td = torch.from_numpy(queries).to(device), torch.from_numpy(doomed).to(device)
+        results = []
+        for table in (via_nccl, via_peer):
+            table.set(tk, tv)
+            gv, gf = table.get(tq, fallback_value=-3.0)
+            rm = table.remove(td)
+            results.append((gv.cpu().numpy(), gf.cpu().numpy(), rm.cpu().numpy(), table.n_elements))
+        a, b = results
+        assert np.array_equal(a[1], b[1]) and np.array_equal(a[0].view(np.uint8), b[0].view(np.uint8)), f"get differs, step {step}"
+        assert np.array_equal(a[2], b[2]), f"remove flags differ, step {step}"
+        assert a[3] == b[3], f"n_elements differ, step {step}"
+        everything = gather((keys, values, queries, doomed, b[0], b[1], b[2]))
+        if rank == 0:
+            for k, v, _, _, _, _, _ in everything:
+                if len(k):
+                    single.set(k, v)
+            wanted = [single.get(q, fallback_value=-3.0) for _, _, q, _, _, _, _ in everything]
+            for (_, _, _, _, got_v, got_f, _), (want_v, want_f) in zip(everything, wanted):
+                assert np.array_equal(got_f, want_f), f"found flags differ from the single table, step {step}"
+                assert np.array_equal(got_v.view(np.uint8), want_v.view(np.uint8)), f"values differ from the single table, step {step}"
+            for _, _, _, d, _, _, got_r in everything:
+                assert np.array_equal(got_r, single.remove_rows(d)), f"remove flags differ from the single table, step {step}"
+            assert single.n_elements == b[3]
+    assert via_peer._peer_on, "the peer exchange was not in use"
+    via_peer.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("multi-gpu parity ok")
+
+
+if __name__ == "__main__":
+    main()
