@@ -486,6 +486,21 @@ def run_candidate(args):
         h2d = sum(host[0][k].numel() * host[0][k].element_size() for k in ("get_keys", "set_keys", "set_values", "fresh_keys"))
         d2h = out_values.numel() * 4 + out_found.numel()
 
+        # what the host link gives when every rank copies at once and nothing else runs: the bound of the e2e leg
+        probe_src, probe_dst = host[0]["get_keys"], torch.empty_like(batches[0]["get_keys"])
+        probe_dst.copy_(probe_src, non_blocking=True)
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        for _ in range(4):
+            probe_dst.copy_(probe_src, non_blocking=True)
+        p1.record()
+        torch.cuda.synchronize()
+        probe_gbs = torch.tensor([4 * probe_src.numel() * 8 / (p0.elapsed_time(p1) * 1e-3) / 1e9], device=device)
+        if world > 1:
+            dist.all_reduce(probe_gbs, op=dist.ReduceOp.MIN)
+        del probe_dst
+
         from doksparse_b200.host_batch import HostBatch
         # chunks of 4 Mi rows on three streams (copy in | kernels | copy out); routed batches use larger chunks
         pipe = HostBatch(table, device, chunk_rows=(1 << 22) if world == 1 else (1 << 23))
@@ -516,6 +531,7 @@ def run_candidate(args):
                "how": "HostBatch: pinned host buffers in and out, chunked over copy-in / kernel / copy-out streams",
                "ms_per_step": float(e_ms.item()) / e2e_steps,
                "h2d_gbs_per_gpu": h2d / (float(e_ms.item()) / e2e_steps * 1e-3) / 1e9,
+               "h2d_copy_only_gbs_per_gpu": float(probe_gbs.item()),   # all ranks copying at once, slowest rank
                **e2e_checks}
 
     # ---- what the hardware gives a probing kernel: independent random 16-byte reads over this GPU's slot array

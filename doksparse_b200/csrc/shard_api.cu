@@ -89,9 +89,14 @@ struct PartDest {
 // Pass 2: every row to its place.  Rows of one owner keep their batch order: inside a tile the place of a row is
 // the number of same-owner rows before it in (round, warp, lane) order -- per-(round, warp) counts from warp
 // matches, one exclusive scan per owner over the ROUNDS * warps counts, and the row's rank among its warp's
-// same-owner lanes -- behind the tile's offset from pass 1.  Three block barriers per tile.
+// same-owner lanes -- behind the tile's offset from pass 1.
+// STAGED: the tile's rows are first sorted by owner in shared memory and then written out run by run, so that
+// consecutive threads store consecutive rows of one owner: with 8 owners a warp's 32 rows would otherwise leave as
+// 8 pieces of ~32 bytes each, which wastes most of an NVLink packet (and of a memory transaction).  Needs
+// DOK_PART_TILE * (kb + vb) bytes of dynamic shared memory; wide rows take the direct path.
 // dest_index[e] is always the row's position in THIS rank's grouped order (segments at the padded local offsets),
 // which is where the owner's answer for the row will be found.
+template <bool STAGED>
 static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, int kb, const char *__restrict__ values,
                                                                  int vb, const uint8_t *__restrict__ owners,
                                                                  int n_shards, ll_t tiles,
@@ -100,7 +105,10 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
                                                                  const __grid_constant__ PartDest dst,
                                                                  ll_t *__restrict__ dest_index) {
   constexpr int WARPS = DOK_TPB / 32, CELLS = DOK_PART_ROUNDS * WARPS;        // cells of one owner, in row order
+  extern __shared__ __align__(16) char stage[];   // STAGED: key rows of the tile sorted by owner, then value rows
   __shared__ int before[DOK_MAX_SHARDS][CELLS];   // same-owner rows of the tile before cell (round, warp)
+  __shared__ int tile_total[DOK_MAX_SHARDS];      // rows of the owner in this tile
+  __shared__ int sorted_start[DOK_MAX_SHARDS + 1];// STAGED: first sorted position of the owner's run in the tile
   __shared__ ll_t tile_first[DOK_MAX_SHARDS];     // rows of this owner in earlier tiles
   __shared__ ll_t local_start[DOK_MAX_SHARDS];    // start of the owner's segment in this rank's grouped order
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -140,19 +148,69 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
       before[o][c0 + lane] = run + inc - v;
       run += __shfl_sync(0xffffffffu, inc, 31);
     }
+    if (lane == 0) tile_total[o] = run;
   }
   __syncthreads();
+  if (!STAGED) {
+#pragma unroll
+    for (int r = 0; r < DOK_PART_ROUNDS; r++) {
+      if (owner[r] < 0) continue;
+      const int o = owner[r];
+      const ll_t e = base + r * DOK_TPB + threadIdx.x;
+      const ll_t in_segment = tile_first[o] + before[o][r * WARPS + warp] + rank[r];
+      if (dest_index) dest_index[e] = local_start[o] + in_segment;
+      const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + in_segment;
+      dok_copy_row(dst.keys[o] + row * kb, (const char *)keys.keys + e * kb, kb);
+      if (values) dok_copy_row(dst.values[o] + row * vb, values + e * vb, vb);
+    }
+    return;
+  }
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int o = 0; o < n_shards; o++) { sorted_start[o] = run; run += tile_total[o]; }
+    sorted_start[n_shards] = run;
+  }
+  __syncthreads();
+  char *stage_values = stage + (size_t)DOK_PART_TILE * kb;
 #pragma unroll
   for (int r = 0; r < DOK_PART_ROUNDS; r++) {
     if (owner[r] < 0) continue;
     const int o = owner[r];
     const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    const ll_t in_segment = tile_first[o] + before[o][r * WARPS + warp] + rank[r];
-    if (dest_index) dest_index[e] = local_start[o] + in_segment;
-    const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + in_segment;
-    dok_copy_row(dst.keys[o] + row * kb, (const char *)keys.keys + e * kb, kb);
-    if (values) dok_copy_row(dst.values[o] + row * vb, values + e * vb, vb);
+    const int in_tile = before[o][r * WARPS + warp] + rank[r];
+    if (dest_index) dest_index[e] = local_start[o] + tile_first[o] + in_tile;
+    const int pos = sorted_start[o] + in_tile;
+    dok_copy_row(stage + (size_t)pos * kb, (const char *)keys.keys + e * kb, kb);
+    if (values) dok_copy_row(stage_values + (size_t)pos * vb, values + e * vb, vb);
   }
+  __syncthreads();
+  const int tile_rows = sorted_start[n_shards];
+  for (int i = threadIdx.x; i < tile_rows; i += DOK_TPB) {
+    int o = 0;                                    // the run that sorted position i belongs to
+    while (sorted_start[o + 1] <= i) o++;
+    const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + tile_first[o] + (i - sorted_start[o]);
+    dok_copy_row(dst.keys[o] + row * kb, stage + (size_t)i * kb, kb);
+    if (values) dok_copy_row(dst.values[o] + row * vb, stage_values + (size_t)i * vb, vb);
+  }
+}
+
+// staged when the tile's rows fit the shared memory a block may ask for without crowding out its neighbours
+#define DOK_PART_STAGE_LIMIT (64 * 1024)
+static int dok_launch_scatter(const RowKeys &rk, int kb, const char *values, int vb, const uint8_t *owners, int n_shards,
+                              const ll_t *tile_offsets, const ll_t *shard_counts, const PartDest &dst, ll_t *dest_index,
+                              cudaStream_t st) {
+  const ll_t tiles = dok_partition_tiles(rk.n);
+  const size_t stage_bytes = (size_t)DOK_PART_TILE * (size_t)(kb + (values ? vb : 0));
+  if (n_shards > 2 && stage_bytes <= DOK_PART_STAGE_LIMIT) {
+    // more than the 48 KiB a kernel gets by default: the attribute is per device, and setting it again is cheap
+    cudaFuncSetAttribute(k_part_scatter<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DOK_PART_STAGE_LIMIT);
+    k_part_scatter<true><<<(unsigned)tiles, DOK_TPB, stage_bytes, st>>>(rk, kb, values, vb, owners, n_shards, tiles,
+                                                                        tile_offsets, shard_counts, dst, dest_index);
+  } else {
+    k_part_scatter<false><<<(unsigned)tiles, DOK_TPB, 0, st>>>(rk, kb, values, vb, owners, n_shards, tiles, tile_offsets,
+                                                               shard_counts, dst, dest_index);
+  }
+  return dok_check_launch();
 }
 
 static __global__ void __launch_bounds__(DOK_TPB) k_unpermute(const char *__restrict__ grouped_values,
@@ -199,17 +257,14 @@ int dok_shard_partition_scatter(const void *keys, int key_bytes, const void *val
   if (n == 0) return DOK_OK;
   if (!keys || key_bytes < 1 || !owners || !tile_offsets || !shard_counts || !keys_out) return DOK_BAD_ARG;
   if (values && (!values_out || value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES)) return DOK_BAD_ARG;
-  const ll_t tiles = dok_partition_tiles(n);
   RowKeys rk{keys, n};
   // every owner's segment lies in the same local buffer, at the prefix sum of the padded counts, which the kernel
   // derives from shard_counts on the device (row0 < 0 asks for that): the host never needs the counts here
   PartDest dst;
   memset(&dst, 0, sizeof(dst));
   for (int o = 0; o < n_shards; o++) { dst.keys[o] = (char *)keys_out; dst.values[o] = (char *)values_out; dst.row0[o] = -1; }
-  k_part_scatter<<<(unsigned)tiles, DOK_TPB, 0, (cudaStream_t)stream>>>(
-      rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, tiles, (const ll_t *)tile_offsets,
-      (const ll_t *)shard_counts, dst, (ll_t *)dest_index);
-  return dok_check_launch();
+  return dok_launch_scatter(rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, (const ll_t *)tile_offsets,
+                            (const ll_t *)shard_counts, dst, (ll_t *)dest_index, (cudaStream_t)stream);
 }
 
 int dok_shard_partition_scatter_peer(const void *keys, int key_bytes, const void *values, int value_bytes, int64_t n,
@@ -228,12 +283,9 @@ int dok_shard_partition_scatter_peer(const void *keys, int key_bytes, const void
     dst.values[o] = values ? (char *)peer_values[o] : nullptr;
     dst.row0[o] = peer_row0[o];
   }
-  const ll_t tiles = dok_partition_tiles(n);
   RowKeys rk{keys, n};
-  k_part_scatter<<<(unsigned)tiles, DOK_TPB, 0, (cudaStream_t)stream>>>(
-      rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, tiles, (const ll_t *)tile_offsets,
-      (const ll_t *)shard_counts, dst, (ll_t *)dest_index);
-  return dok_check_launch();
+  return dok_launch_scatter(rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, (const ll_t *)tile_offsets,
+                            (const ll_t *)shard_counts, dst, (ll_t *)dest_index, (cudaStream_t)stream);
 }
 
 /* ---- exchange arena: device memory that the other ranks of the node map into their address space ------------ */

@@ -12,16 +12,17 @@ from tests.helpers import dev, host
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("value_columns", [3, 12])      # 12 float32 columns: rows too wide for the staged scatter
 @pytest.mark.parametrize("world", [2, 8, 64])
 @pytest.mark.parametrize("n", [1, 2047, 2048, 2049, 100_003])
-def test_partition_matches_host_restatement(world, n):
+def test_partition_matches_host_restatement(world, n, value_columns):
     from doksparse_b200.sharded import CudaShardOps
     np.random.seed(world)
     params = port.draw_hash_parameters(1 << 20, 2)
     ops = CudaShardOps("cuda:0", 1024, params, 2.0, 0.75)
     rng = np.random.default_rng(n)
     keys = rng.integers(0, 2 ** 40, size=(n, 2)).astype(np.int64)
-    vals = rng.standard_normal((n, 3)).astype(np.float32)
+    vals = rng.standard_normal((n, value_columns)).astype(np.float32)
     gk, gv, dest, counts = ops.partition(dev(keys), dev(vals), world)
 
     o = port.OracleHashmap(n_buckets=8, **params)
