@@ -129,7 +129,7 @@ class ClockSampler:
         self.rows, self.proc, self.thread = [], None, None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "25"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -349,7 +349,7 @@ def workload_config(args, world):
         "keys_per_gpu": 1 << args.keys_log2, "buckets_per_gpu": int((1 << args.keys_log2) / LOAD_FACTOR),
         "batch_per_gpu": 1 << args.batch_log2, "shards": world,
         "l2_policy": f"inputs larger than L2: {N_BATCHES} rotating batches of {(1 << args.batch_log2) * 8 >> 20} MiB keys, "
-                     f"table {(int((1 << args.keys_log2) / LOAD_FACTOR) * 16) >> 20} MiB per GPU",
+                     f"table {(int((1 << args.keys_log2) / LOAD_FACTOR) * 32) >> 20} MiB per GPU",
         "parallelism": ("single GPU" if world == 1 else
                         f"hash-sharded x{world}, " + ("NCCL all-to-all" if getattr(args, "no_peer", False) else
                                                       "rows stored into the owners' memory over NVLink (peer exchange)")),
@@ -558,6 +558,10 @@ def run_candidate(args):
         per_kernel[op] = {"ms": kernel_ms[op], "mops_per_gpu": gops * 1e3, "bytes_per_op": algorithmic_bytes(op),
                           "achieved_gbs": achieved, "frac": achieved / peak,
                           "frac_of_random_request_ceiling": gops / request_ceiling}
+        if TRAFFIC_BYTES_PER_OP.get(op) and world == 1:
+            # what DRAM really moves (ncu: whole 128-byte lines per probed group), as a rate and against the peak
+            dram = TRAFFIC_BYTES_PER_OP[op] * local_rows[op] / (kernel_ms[op] * 1e-3) / 1e9
+            per_kernel[op].update({"dram_traffic_gbs": dram, "dram_traffic_frac": dram / peak})
     top = max(kernel_ms, key=kernel_ms.get)
     roofline = {"bound": "hbm", "kernel": {"get": "k_get", "set": "k_set_claim (+ k_set_resolve, idle without duplicates)",
                                            "remove": "k_find<remove>"}[top],
@@ -566,8 +570,9 @@ def run_candidate(args):
                 "peak_source": peak_source,
                 "random_request_ceiling_greq_s": request_ceiling,
                 "note": ("phase time includes routing and exchange when shards > 1; " if world > 1 else "") +
-                        "a table much larger than L2 serves ~48 G random requests/s whatever their size, so one "
-                        "request per operation caps a probing kernel well below the byte roofline"}
+                        "DRAM serves a random access with a whole 128-byte line (~48 G lines/s = the HBM bandwidth), "
+                        "so a probing kernel is bound by lines touched per operation, not by the bytes it needs: "
+                        "see kernels.*.dram_traffic_frac for the share of the HBM peak each kernel really moves"}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
