@@ -245,13 +245,87 @@ class SparseDOKTensor(object):
                 values = values.squeeze(i)
         return values
 
+    def __spgetitem__(self, selectors):
+        """Sparse gather (sparse_dok_tensor.py:342-350 -> get_items, sparse_dok_tensor_impl.py:148-232; kernels
+        sparse_dok_tensor_impl.cu:110-268): a SparseDOKTensor of the selection's broadcast shape that holds the selected
+        positions which are stored, keyed by their position in the selection.  One fused lookup over the selectors,
+        a compaction of the hits, and one insert of pairwise different keys into a map of int(2 * hits) buckets (the
+        reference's size).  A selection without a hit gives an empty tensor (the reference builds a 0-bucket map)."""
+        selectors, _ = self._handle_selectors(selectors)
+        shape = tuple(selectors[0].shape)
+        hashmap = self._hashmap
+        n_sel = int(selectors[0].numel())
+        if hashmap._values is None or n_sel == 0:
+            return SparseDOKTensor(size=shape, device=self.device, dtype=self.dtype)
+        values = torch.empty(n_sel, device=self.device, dtype=self.dtype)
+        found = torch.empty(n_sel, device=self.device, dtype=torch.bool)
+        sel = _selectors_struct(selectors)
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_dok_get(hashmap._c_table(), hashmap._c_hash(), ctypes.byref(sel), L.ptr(values),
+                                        L.ptr(found), None, None, L.stream_ptr(self.device)), "dok_dok_get")
+        hits = found.nonzero().flatten()                       # row-major positions in the selection
+        n = int(hits.numel())
+        if not shape:
+            shape = (1,)                                       # all selectors scalar: a one-element selection
+        if n == 0:
+            return SparseDOKTensor(size=shape, device=self.device, dtype=self.dtype)
+        keys = torch.stack(torch.unravel_index(hits, shape), dim=1)
+        out = CudaClosedHashmap(n_buckets=int(n * 2.0), device=self.device)
+        out.set(keys.contiguous(), values[hits][:, None].contiguous(), assume_unique=True)
+        return SparseDOKTensor.from_storage(out, size=shape)
+
+    def _set_items_sparse(self, src, selectors):
+        """Assignment of a sparse source of the selection's shape (set_items_sparse, sparse_dok_tensor_impl.py:234-340):
+        every selected position that is stored is removed, the table is rebuilt with
+        ceil((n_elements + nnz(src)) * rehash_factor * 2) buckets -- unconditionally, as in the reference -- and the
+        stored elements of the source are inserted at the positions the selectors map them to; n_elements grows by
+        nnz(src).  Equal destination positions: the last source element wins (the reference's kernel races)."""
+        hashmap = self._hashmap
+        if isinstance(src, SparseDOKTensor):
+            if src._hashmap._values is None:
+                src_indices = torch.zeros(len(src.shape), 0, device=self.device, dtype=torch.long)
+                src_values = torch.zeros(0, device=self.device, dtype=self.dtype)
+            else:
+                src_indices, src_values = src.indices(), src.values()
+        else:
+            src = src if src.layout == torch.sparse_coo else src.to_sparse_coo()
+            src_indices, src_values = src._indices(), src._values()
+        assert selectors[0].ndim == src_indices.shape[0]
+        src_indices = src_indices.to(self.device)
+        src_values = src_values.to(device=self.device, dtype=self.dtype)
+        first = (0,) * selectors[0].ndim
+        if hashmap._keys is None:            # the reference seeds an empty map with a zero at the first position (:236-239)
+            first_key = torch.stack([s[first] for s in selectors], dim=0)[None]
+            hashmap.set(first_key, torch.zeros(1, 1, device=self.device, dtype=self.dtype))
+        if selectors[0].numel():
+            cnt = hashmap._counters()
+            sel = _selectors_struct(selectors)
+            with torch.cuda.device(self.device):
+                L.check(L.lib().dok_dok_zero_items(hashmap._c_table(), hashmap._c_hash(), ctypes.byref(sel), L.ptr(cnt),
+                                                   L.stream_ptr(self.device)), "dok_dok_zero_items")
+            hashmap._n_elements -= cnt[L.CNT_HITS]
+            hashmap._after_mutation(0)
+        n_src = int(src_values.shape[0])
+        hashmap.rehash(math.ceil((hashmap.n_elements + n_src) * hashmap._rehash_factor * 2))
+        if n_src:
+            where = tuple(src_indices[d] for d in range(src_indices.shape[0]))
+            dest_keys = torch.stack([s[where] for s in selectors], dim=1).contiguous()
+            hashmap = self._hashmap
+            before = hashmap.n_elements
+            hashmap.set(dest_keys, src_values[:, None].contiguous())
+            # the reference adds nnz(src) whatever was new (:340)
+            hashmap._n_elements += n_src - (hashmap.n_elements - before)
+            hashmap._after_mutation(n_src)
+
     def __setitem__(self, selectors, values):
         """Dense assignment (sparse_dok_tensor.py:317-327 -> sparse_dok_tensor_impl.py:412-474).  A Python scalar is
         treated like a 0-dim tensor, as the reference's README documents."""
         selectors, _ = self._handle_selectors(selectors)
         shape = selectors[0].shape
         if isinstance(values, SparseDOKTensor) or (isinstance(values, Tensor) and values.is_sparse):
-            raise NotImplementedError("assignment of sparse values is not implemented yet")
+            assert tuple(values.shape) == tuple(shape), f"expecting the value shape to be {tuple(shape)}, got {tuple(values.shape)} instead"
+            self._set_items_sparse(values, selectors)
+            return
         if not isinstance(values, Tensor):
             values = torch.tensor(values, device=self.device, dtype=self.dtype)
         values = torch.broadcast_to(values.to(device=self.device, dtype=self.dtype), shape)

@@ -240,3 +240,40 @@ def test_views_clone_and_unary():
     assert torch.equal(t3.flatten().to_dense(), t3.to_dense().flatten())
     assert torch.equal(t3.reshape(10, 12).to_dense(), t3.to_dense().reshape(10, 12))
     assert torch.equal(torch.add(t3, t3).to_dense(), 2 * t3.to_dense())      # __torch_function__ COO fallback
+
+
+def test_sparse_gather_and_sparse_assignment():
+    """__spgetitem__ and assignment of sparse values (the reference's get_items / set_items_sparse), against the dense
+    semantics they stand for: the gather holds exactly the stored selected positions; the assignment replaces the
+    selection by the source (absent source positions become absent)."""
+    from doksparse_b200 import SparseDOKTensor
+    rng = np.random.default_rng(11)
+    shape = (200, 300)
+    idx, vals = random_coo(rng, shape, 9000)
+    np.random.seed(11)
+    t = SparseDOKTensor(shape, torch.from_numpy(idx).cuda(), torch.from_numpy(vals).cuda())
+    rows = torch.from_numpy(rng.permutation(200)[:40]).cuda()
+    cols = torch.from_numpy(rng.permutation(300)[:70]).cuda()
+    sel = (rows[:, None], cols[None, :])
+
+    gathered = t.__spgetitem__(sel)
+    assert tuple(gathered.shape) == (40, 70)
+    dense_selection = t[sel]
+    assert torch.equal(gathered.to_dense(), dense_selection)
+    n_hits = t.count_items(sel)
+    assert gathered._nnz() == n_hits == int((dense_selection != 0).sum())
+    assert gathered.storage().n_buckets == int(n_hits * 2.0)
+    miss = t.__spgetitem__((torch.tensor([0, 1]).cuda(), torch.tensor([0, 0]).cuda()))
+    assert tuple(miss.shape) == (2,) and torch.equal(miss.to_dense(), t[torch.tensor([0, 1]).cuda(), torch.tensor([0, 0]).cuda()])
+
+    for as_torch_coo in (False, True):
+        src_idx, src_vals = random_coo(rng, (40, 70), 500)
+        src = SparseDOKTensor((40, 70), torch.from_numpy(src_idx).cuda(), torch.from_numpy(src_vals).cuda())
+        want = t.to_dense()
+        want[rows[:, None], cols[None, :]] = src.to_dense()
+        live_outside = int((want != 0).sum()) - 500
+        t[sel] = src.to_sparse_coo() if as_torch_coo else src
+        assert torch.equal(t.to_dense(), want)
+        assert torch.equal(t[sel], src.to_dense())
+        assert t._nnz() == live_outside + 500                          # n_elements: what stayed plus nnz(src)
+        assert t.storage().n_buckets == int(np.ceil((live_outside + 500) * 2.0 * 2))
