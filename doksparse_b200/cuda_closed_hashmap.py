@@ -41,6 +41,7 @@ class CudaClosedHashmap:
         key_perm=None,
         rehash_factor=2.0,
         rehash_threshold=0.75,
+        tombstone_threshold=None,
     ):
         self._empty_marker = -1
         self._removed_marker = -3
@@ -68,6 +69,14 @@ class CudaClosedHashmap:
         self._n_elements = torch.zeros(size=(), device=self.device, dtype=torch.long)
         self._rehash_factor = rehash_factor
         self._rehash_threshold = rehash_threshold
+        # Tombstone-aware maintenance (no counterpart in the reference, whose rehash looks at live items only,
+        # cuda_closed_hashmap.py:365, so that chains only ever grow under churn): with a threshold t, a removal that
+        # leaves live + tombstone slots above t * n_buckets rebuilds the table at its size, which drops the tombstones.
+        # Off by default: a rebuild draws new hash parameters, which a bit-for-bit comparison with the reference
+        # would see.
+        self._tombstone_threshold = tombstone_threshold
+        self._n_tombstones = torch.zeros(size=(), device=self.device, dtype=torch.long)   # upper bound, on the device
+        self._tombstone_host_bound = 0                                                  # looser bound, on the host
 
         self._key_perm = None
         if key_perm is not None:
@@ -375,7 +384,10 @@ class CudaClosedHashmap:
             prime1=cp(self.prime1), prime2=cp(self.prime2), alpha1=cp(self.alpha1), alpha2=cp(self.alpha2),
             beta1=cp(self.beta1), beta2=cp(self.beta2), key_perm=cp(self._key_perm),
             rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
+            tombstone_threshold=self._tombstone_threshold,
         )
+        new._n_tombstones = cp(self._n_tombstones)
+        new._tombstone_host_bound = self._tombstone_host_bound
         if self._slots is not None:
             new._slots = cp(self._slots)
             new._uuid_only = None
@@ -551,13 +563,15 @@ class CudaClosedHashmap:
             # whatever the number of new keys is, the reference would not rehash: insert and count on the device
             cnt = self._launch_set(new_keys, new_values, assume_unique)
             self._n_elements += cnt[L.CNT_CLAIMED_EMPTY] + cnt[L.CNT_REUSED_REMOVED]
+            self._n_tombstones -= cnt[L.CNT_REUSED_REMOVED]
             self._after_mutation(n)
             return
         n_new = self._count_new(new_keys)
         n_elements = self.n_elements
         if n_elements + n_new > limit:
             self.rehash(int((n_elements + n_new) * self._rehash_factor))
-        self._launch_set(new_keys, new_values, assume_unique)
+        cnt = self._launch_set(new_keys, new_values, assume_unique)
+        self._n_tombstones -= cnt[L.CNT_REUSED_REMOVED]
         self._n_elements += n_new
         self._shared["snapshots"].clear()
         self._shared["bound"] = n_elements + n_new
@@ -623,8 +637,29 @@ class CudaClosedHashmap:
             L.check(L.lib().dok_map_remove(self._c_table(), self._c_hash(), L.ptr(keys), n, L.ptr(is_removed), L.ptr(cnt),
                                            L.stream_ptr(self.device)), "dok_map_remove")
         self._n_elements -= cnt[L.CNT_HITS]
+        self._n_tombstones += cnt[L.CNT_HITS]
+        self._tombstone_host_bound += n
         self._after_mutation(0)
+        self._maintain()
         return is_removed
+
+    def _maintain(self):
+        """Rebuild at the same size when live + tombstone slots exceed tombstone_threshold * n_buckets.  The host
+        first looks at its own upper bounds (no synchronisation) and reads the device counts only when they cross."""
+        if self._tombstone_threshold is None or self._slots is None:
+            return
+        limit = self._tombstone_threshold * self.n_buckets
+        if self._element_bound() + self._tombstone_host_bound <= limit:
+            return
+        tombstones = int(self._n_tombstones.item())
+        self._tombstone_host_bound = tombstones
+        if self.n_elements + tombstones > limit and tombstones > 0:
+            self.rehash(self.n_buckets)
+
+    @property
+    def tombstone_bound(self):
+        """Upper bound of the tombstone slots, from the device counters (exact unless DOK assignments reused some)."""
+        return int(self._n_tombstones.item())
 
     def remove(self, keys):
         if self._slots is None:
@@ -644,6 +679,7 @@ class CudaClosedHashmap:
         self.__init__(
             n_buckets=n_buckets, device=self.device, key_perm=self._key_perm,
             rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
+            tombstone_threshold=self._tombstone_threshold,
         )
         # live rows have pairwise different keys: one kernel
         self.set(keys, values, assume_unique=True)

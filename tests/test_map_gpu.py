@@ -394,3 +394,40 @@ def test_large_roundtrip_properties():
     k2, v2, u2 = m.items()
     assert k2.shape[0] == m.n_elements
     assert torch.equal(torch.sort(k2[:, 0]).values, torch.sort(torch.cat([keys[: n // 4, 0], keys[n // 2:, 0]])).values)
+
+
+def test_tombstone_aware_maintenance():
+    """With tombstone_threshold the table is rebuilt at its size once live + tombstone slots exceed it: tombstones go,
+    contents stay.  Without it (the reference's behaviour) tombstones only accumulate."""
+    from doksparse_b200 import CudaClosedHashmap
+    rng = np.random.default_rng(3)
+    nb = 1 << 16
+    pool = rng.permutation(1 << 20)[:60000].astype(np.int64)[:, None]
+    values = rng.standard_normal((60000, 2)).astype(np.float32)
+    tables, first_prime = {}, {}
+    for name, threshold in (("plain", None), ("maintained", 0.6)):
+        np.random.seed(4)
+        table = CudaClosedHashmap(n_buckets=nb, device="cuda:0", rehash_threshold=0.9, tombstone_threshold=threshold)
+        live = {}
+        for lo in range(0, 60000, 10000):                     # a sliding window: insert 10 k, remove the 10 k before
+            k, v = pool[lo:lo + 10000], values[lo:lo + 10000]
+            table.set(dev(k), dev(v))
+            first_prime.setdefault(name, int(table.prime2[0]))
+            live.update({int(a): tuple(b) for a, b in zip(k[:, 0], v)})
+            if lo >= 10000:
+                old = pool[lo - 10000:lo]
+                flags = table.remove_rows(dev(old))
+                assert bool(flags.all())
+                for a in old[:, 0]:
+                    del live[int(a)]
+            assert table.n_buckets == nb and table.n_elements == len(live)
+            assert table.n_tombstones <= table.tombstone_bound
+        keys, vals, _ = table.items()
+        got = {int(a): tuple(b) for a, b in zip(host(keys)[:, 0], host(vals))}
+        assert got == live
+        tables[name] = table
+    # a rebuild draws new hash parameters: that is how it shows from outside
+    assert int(tables["plain"].prime2[0]) == first_prime["plain"]
+    assert int(tables["maintained"].prime2[0]) != first_prime["maintained"]
+    assert tables["maintained"].n_tombstones < tables["plain"].n_tombstones
+    assert tables["maintained"].n_elements + tables["maintained"].n_tombstones <= 0.6 * nb + 10000
