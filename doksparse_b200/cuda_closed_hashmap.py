@@ -684,6 +684,44 @@ class CudaClosedHashmap:
         # live rows have pairwise different keys: one kernel
         self.set(keys, values, assume_unique=True)
 
+    # ------------------------------------------------------------------ persistence
+    def state_dict(self):
+        """Everything needed to rebuild the map, independent of the slot layout: the live (key, value) rows from one
+        compaction pass, the hash parameters (so that uuids, and with them the owner shards of a sharded map, stay
+        the same) and the sizing options.  Tombstones are not kept.  The reference has no checkpoint format."""
+        if self._slots is not None:
+            self._materialise_parameters()
+        state = {"format": 1, "n_buckets": self.n_buckets, "rehash_factor": self._rehash_factor,
+                 "rehash_threshold": self._rehash_threshold, "tombstone_threshold": self._tombstone_threshold,
+                 "key_perm": None if self._key_perm is None else self._key_perm.cpu(), "keys": None, "values": None}
+        for name in ("prime1", "prime2", "alpha1", "alpha2", "beta1", "beta2"):
+            v = getattr(self, "_" + name)
+            state[name] = None if v is None else v.cpu()
+        if self._slots is not None:
+            keys, values, _ = self.items(uuid=False)
+            state["keys"] = keys.reshape((-1,) + tuple(self.key_shape)).cpu()
+            state["values"] = values.cpu()
+            state["n_elements"] = self.n_elements            # may over-count like the reference's DOK assignments do
+        return state
+
+    @classmethod
+    def from_state_dict(cls, state, device="cuda:0"):
+        assert state.get("format") == 1
+        table = cls(n_buckets=state["n_buckets"], device=device, rehash_factor=state["rehash_factor"],
+                    rehash_threshold=state["rehash_threshold"], tombstone_threshold=state.get("tombstone_threshold"),
+                    key_perm=state["key_perm"],
+                    **{name: state[name] for name in ("prime1", "prime2", "alpha1", "alpha2", "beta1", "beta2")})
+        if state["keys"] is not None:
+            keys, values = state["keys"].to(table.device), state["values"].to(table.device)
+            if keys.shape[0]:      # items() gives key columns in the caller's order, like rehash relies on
+                table.set(keys, values, assume_unique=True)
+            else:
+                table._allocate(keys.shape[1:], keys.dtype, values.shape[1:], values.dtype)
+            table._n_elements.fill_(int(state["n_elements"]))
+            table._shared["bound"] = int(state["n_elements"])
+            table._shared["snapshots"].clear()
+        return table
+
     def __getitem__(self, keys):
         return self.get(keys)
 

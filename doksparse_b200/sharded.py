@@ -477,6 +477,18 @@ class ShardedClosedHashmap:
         owned_keys, owned_values, segments, _, _, _ = self._route(keys, values, want_dest=False)
         self.ops.local_set(owned_keys, owned_values, segments, assume_unique)
 
+    def state_dict(self):
+        """This rank's shard (see CudaClosedHashmap.state_dict) plus the sharding it belongs to.  Every rank saves its
+        own; a map rebuilt with the same world size and parameters routes every key to the shard that holds it."""
+        return {"world": self.world, "rank": self.rank, "shard": self.ops.local.state_dict(),
+                "value_shape": self._value_shape, "value_dtype": self._value_dtype}
+
+    def load_state_dict(self, state):
+        """Replaces this rank's shard by a saved one (same world size and rank)."""
+        assert state["world"] == self.world and state["rank"] == self.rank, "a shard belongs to its rank"
+        self.ops.local = CudaClosedHashmap.from_state_dict(state["shard"], device=self.ops.device)
+        self._value_shape, self._value_dtype = state["value_shape"], state["value_dtype"]
+
     def close(self):
         """Releases the peer exchange arena (every rank, after the last operation)."""
         if self._peer_on:

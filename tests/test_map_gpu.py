@@ -431,3 +431,30 @@ def test_tombstone_aware_maintenance():
     assert int(tables["maintained"].prime2[0]) != first_prime["maintained"]
     assert tables["maintained"].n_tombstones < tables["plain"].n_tombstones
     assert tables["maintained"].n_elements + tables["maintained"].n_tombstones <= 0.6 * nb + 10000
+
+
+def test_state_dict_round_trip(tmp_path):
+    """A map rebuilt from its state_dict answers like the original (same uuids: same parameters), whatever the slot
+    layout did in between; tombstones are gone."""
+    from doksparse_b200 import CudaClosedHashmap
+    rng = np.random.default_rng(8)
+    np.random.seed(8)
+    table = CudaClosedHashmap(n_buckets=1 << 15, device="cuda:0")
+    keys = np.unique(rng.integers(0, 1 << 40, size=(12000, 2), dtype=np.int64), axis=0)
+    values = rng.standard_normal((len(keys), 3)).astype(np.float32)
+    table.set(dev(keys), dev(values))
+    table.remove_rows(dev(keys[:3000]))
+    path = tmp_path / "map.pt"
+    torch.save(table.state_dict(), path)
+    again = CudaClosedHashmap.from_state_dict(torch.load(path), device="cuda:0")
+    assert again.n_elements == table.n_elements == len(keys) - 3000 and again.n_buckets == table.n_buckets
+    assert again.n_tombstones == 0 < table.n_tombstones
+    queries = dev(np.concatenate([keys[::3], keys[:10] + 1]))
+    for a, b in zip(table.get(queries, -1.0), again.get(queries, -1.0)):
+        assert torch.equal(a, b)
+    ka, va, ua = (host(x) for x in table.items())
+    kb, vb, ub = (host(x) for x in again.items())
+    for x, y in zip(port.sort_items(ka, va, ua), port.sort_items(kb, vb, ub)):
+        np.testing.assert_array_equal(x, y)
+    empty = CudaClosedHashmap.from_state_dict(CudaClosedHashmap(n_buckets=64, device="cuda:0").state_dict())
+    assert empty.n_elements == 0 and empty.n_buckets == 64
