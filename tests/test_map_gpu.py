@@ -405,7 +405,7 @@ def test_tombstone_aware_maintenance():
     pool = rng.permutation(1 << 20)[:60000].astype(np.int64)[:, None]
     values = rng.standard_normal((60000, 2)).astype(np.float32)
     tables, first_prime = {}, {}
-    for name, threshold in (("plain", None), ("maintained", 0.6)):
+    for name, threshold in (("plain", None), ("maintained", 0.4)):
         np.random.seed(4)
         table = CudaClosedHashmap(n_buckets=nb, device="cuda:0", rehash_threshold=0.9, tombstone_threshold=threshold)
         live = {}
@@ -430,7 +430,7 @@ def test_tombstone_aware_maintenance():
     assert int(tables["plain"].prime2[0]) == first_prime["plain"]
     assert int(tables["maintained"].prime2[0]) != first_prime["maintained"]
     assert tables["maintained"].n_tombstones < tables["plain"].n_tombstones
-    assert tables["maintained"].n_elements + tables["maintained"].n_tombstones <= 0.6 * nb + 10000
+    assert tables["maintained"].n_elements + tables["maintained"].n_tombstones <= 0.4 * nb + 10000
 
 
 def test_state_dict_round_trip(tmp_path):
