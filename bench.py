@@ -52,6 +52,8 @@ def parse_args():
                     help="reference arm: skip the extra leg that runs the reference's kernels on the GPU")
     ap.add_argument("--no-peer", action="store_true",
                     help="multi-GPU: exchange rows with NCCL all-to-all instead of stores into the peers' memory")
+    ap.add_argument("--no-pipeline", action="store_true",
+                    help="multi-GPU: call get / set / remove one after the other instead of one pipelined submission")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -374,6 +376,8 @@ def run_candidate(args):
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"        # keep NCCL's banner off stdout: one JSON line only
+        # the small collectives of the exchange (count gather, fences) must not queue behind the big probing grids
+        os.environ.setdefault("TORCH_NCCL_HIGH_PRIORITY", "1")
         dist.init_process_group("nccl", device_id=device)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
 
@@ -418,8 +422,15 @@ def run_candidate(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    pipelined = world > 1 and not args.no_peer and not args.no_pipeline
+
     def step(b, events=None):
         d = batches[b % N_BATCHES]
+        if pipelined and events is None:
+            # one submission: the send stage of each operation overlaps the table work of the one before
+            (values, found), _, _ = table.run([("get", d["get_keys"]), ("set", d["set_keys"], d["set_values"]),
+                                               ("remove", d["fresh_keys"])])
+            return values, found
         if events is not None:
             events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
         values, found = table.get(d["get_keys"])
@@ -457,17 +468,27 @@ def run_candidate(args):
     t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
     for s in range(args.steps):
-        step(s + args.warmup, events)
+        step(s + args.warmup, None if pipelined else events)
     t_stop.record()
     barrier()
     launches = L.lib().dok_launch_count() - launches0
     clocks = sampler.stop() if sampler else None
     elapsed_ms = torch.tensor([t_start.elapsed_time(t_stop)], device=device)
+    phase_steps = args.steps
+    if pipelined:
+        # the timed steps were single pipelined submissions; the per-operation times come from a short separate
+        # pass that calls the operations one after the other (they add up to more than a pipelined step)
+        phase_steps = 3
+        step(0, [])                                   # warm the sequential path (allocator pools of the main stream)
+        barrier()
+        for s in range(phase_steps):
+            step(s + 1, events)
+        barrier()
     phase = torch.zeros(3, device=device)
-    for s in range(args.steps):
+    for s in range(phase_steps):
         e = events[4 * s: 4 * s + 4]
         phase += torch.tensor([e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), e[2].elapsed_time(e[3])], device=device)
-    phase /= args.steps
+    phase /= phase_steps
     if world > 1:
         dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
         dist.all_reduce(phase, op=dist.ReduceOp.MAX)
@@ -569,7 +590,9 @@ def run_candidate(args):
                 "traffic": TRAFFIC_BYTES_PER_OP.get(top, 0) * local_rows[top] if TRAFFIC_BYTES_PER_OP.get(top) else None,
                 "peak_source": peak_source,
                 "random_request_ceiling_greq_s": request_ceiling,
-                "note": ("phase time includes routing and exchange when shards > 1; " if world > 1 else "") +
+                "note": ("phase time includes routing and exchange when shards > 1" +
+                         (", measured with the operations called one after the other (the timed steps pipeline them); "
+                          if pipelined else "; ") if world > 1 else "") +
                         "DRAM serves a random access with a whole 128-byte line (~48 G lines/s = the HBM bandwidth), "
                         "so a probing kernel is bound by lines touched per operation, not by the bytes it needs: "
                         "see kernels.*.dram_traffic_frac for the share of the HBM peak each kernel really moves"}

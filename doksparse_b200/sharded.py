@@ -112,9 +112,15 @@ class CudaShardOps:
                     lib.dok_peer_free(base)
             return False
         views = [torch.as_tensor(self._RawDeviceBytes(bases[r], 2 * gen_bytes), device=self.device) for r in range(world)]
-        self._peer = dict(world=world, rank=rank, cap=cap, kb=kb, vb=vb, kshape=tuple(kshape), kdtype=kdtype,
+        # a second communicator for the fences of the apply stage: collectives of one communicator run in issue order,
+        # and a fence that waits for table work must not hold up the count gather of the next operation's send stage
+        group_apply = None
+        if group is None or group is dist.group.WORLD:
+            group_apply = dist.new_group(backend="nccl")
+        self._peer = dict(group_apply=group_apply, world=world, rank=rank, cap=cap, kb=kb, vb=vb, kshape=tuple(kshape), kdtype=kdtype,
                           vshape=tuple(vshape), vdtype=vdtype, gen_bytes=gen_bytes, offs=offs, bases=bases, views=views,
-                          own_base=base, token=torch.zeros(1, device=self.device), group=group)
+                          own_base=base, token=torch.zeros(1, device=self.device),
+                          token_apply=torch.zeros(1, device=self.device), group=group)
         return True
 
     def peer_close(self):
@@ -141,10 +147,17 @@ class CudaShardOps:
         flat = p["views"][rank][lo:lo + rows * width]
         return flat.view(dtype).view((rows,) + tuple(shape))
 
-    def peer_fence(self):
+    def peer_fence(self, apply_side=False):
         """Every rank's earlier work on its stream (stores into peers' arenas included) is complete before any rank's
-        later work starts: a one-element all-reduce, ordered on the stream, not blocking the host."""
-        dist.all_reduce(self._peer["token"], group=self._peer["group"])
+        later work starts: a one-element all-reduce, ordered on the stream, not blocking the host.  `apply_side`
+        fences travel on the second communicator when there is one."""
+        p = self._peer
+        group = p["group_apply"] if (apply_side and p["group_apply"] is not None) else p["group"]
+        token = p["token_apply"] if apply_side else p["token"]
+        dist.all_reduce(token, group=group)
+
+    def can_pipeline(self):
+        return self._peer is not None and self._peer["group_apply"] is not None
 
     def partition_count(self, keys, world):
         """First pass of the partition -> (owners, tile offsets, counts[2 * world] on the device)."""
@@ -348,6 +361,7 @@ class ShardedClosedHashmap:
         self._peer_capacity = int(peer_capacity_rows) if (self.world > 1 and self.world <= 16) else 0
         self._peer_on = False
         self._peer_seq = 0
+        self._streams = None
         self._value_shape = None
         self._value_dtype = None
 
@@ -428,14 +442,21 @@ class ShardedClosedHashmap:
                     row0=[sum(padded[s][o] for s in range(r)) for o in range(w)],
                     segments=[(starts[s], exact[s][r]) for s in range(w)], inbox_rows=run)
 
-    def _peer_lookup(self, plan, with_values, fallback_value):
-        """get / remove over the peer exchange: keys into the owners' inboxes, answers straight into the askers'
-        result regions, two stream-ordered fences, inverse permutation."""
+    # An operation over the peer exchange has two stages.  SEND: rows into the owners' inboxes (partition + stores
+    # over NVLink).  APPLY: the owner's table work on what it received, answers into the askers' result regions, the
+    # inverse permutation.  A fence (one-element all-reduce on the stream) separates them.
+    def _peer_send(self, plan, values, want_dest):
+        plan["dest"] = self.ops.scatter_to_peers(plan["keys"], values, self.world, plan["owners"], plan["offsets"],
+                                                 plan["counts"], plan["gen"], plan["row0"], want_dest=want_dest)
+
+    def _peer_apply_set(self, plan, assume_unique):
+        owned_keys = self.ops._peer_region(self.rank, plan["gen"], 0, rows=plan["inbox_rows"])
+        owned_values = self.ops._peer_region(self.rank, plan["gen"], 1, rows=plan["inbox_rows"])
+        self.ops.local_set(owned_keys, owned_values, plan["segments"], assume_unique)
+
+    def _peer_apply_lookup(self, plan, with_values, fallback_value):
         w, r, ops = self.world, self.rank, self.ops
-        gen, exact, padded = plan["gen"], plan["exact"], plan["padded"]
-        dest = ops.scatter_to_peers(plan["keys"], None, w, plan["owners"], plan["offsets"], plan["counts"], gen,
-                                    plan["row0"], want_dest=True)
-        ops.peer_fence()
+        gen, padded = plan["gen"], plan["padded"]
         owned_keys = ops._peer_region(r, gen, 0, rows=plan["inbox_rows"])
         order = list(range(w))
         if with_values:       # lookups commute: other ranks' rows first, so that the copy of their answers over NVLink
@@ -449,12 +470,125 @@ class ShardedClosedHashmap:
             values = ops._peer_region(s, gen, 2, rows=rows, row0=at) if with_values else None
             ops.local_answer(owned_keys[start:start + rows], values, flags, fallback_value, remote=(s != r))
         ops.answers_delivered()
-        ops.peer_fence()
+        ops.peer_fence(apply_side=True)
         n_mine = sum(padded[r])
         res_flags = ops._peer_region(r, gen, 3, rows=n_mine).view(torch.uint8)
         res_values = ops._peer_region(r, gen, 2, rows=n_mine) if with_values else None
-        out_values, out_flags = ops.unpermute(res_values, res_flags, dest)
+        out_values, out_flags = ops.unpermute(res_values, res_flags, plan["dest"])
         return out_values, out_flags.view(torch.bool)
+
+    def _peer_lookup(self, plan, with_values, fallback_value):
+        """get / remove over the peer exchange, one operation at a time."""
+        self._peer_send(plan, None, want_dest=True)
+        self.ops.peer_fence()
+        return self._peer_apply_lookup(plan, with_values, fallback_value)
+
+    def run(self, operations):
+        """Several operations as one software pipeline: [("get", keys[, fallback_value]), ("set", keys, values[,
+        assume_unique]), ("remove", keys)] -> list of results (get: (values, is_found); set: None; remove: flags).
+        Collective: every rank passes the same sequence of operation kinds.  The operations are applied in order, as if
+        called one after the other; what overlaps is the SEND stage of operation k + 1 (it only reads the caller's
+        batch: partition, count gather, stores into the owners' other inbox generation over NVLink) with the APPLY
+        stage of operation k (table work in HBM), on two streams.  Without the peer exchange the operations simply
+        run one after the other.  Results are ready for the caller's current stream when the call returns."""
+        if not operations:
+            return []
+        if not self._peer_on or not self.ops.can_pipeline():
+            return [self._run_one(op) for op in operations]
+        ops = self.ops
+        device = ops.device
+        if self._streams is None:
+            # the send stage runs at high priority: its kernels are short, and behind the big grids of the table work
+            # they would otherwise only start when those have handed out all their blocks
+            self._streams = (torch.cuda.Stream(device=device, priority=-1), torch.cuda.Stream(device=device))
+        s_send, s_apply = self._streams
+        main = torch.cuda.current_stream(device)
+        start = torch.cuda.Event()
+        start.record(main)
+        s_send.wait_event(start)
+        s_apply.wait_event(start)
+        results = [None] * len(operations)
+
+        def send(i):
+            """-> plan with the fence still to come, or None when the batch must take the all-to-all path"""
+            kind, keys = operations[i][0], operations[i][1]
+            with torch.cuda.stream(s_send):
+                plan = self._peer_plan(keys)
+                if plan is not None:
+                    values = operations[i][2].contiguous() if kind == "set" else None
+                    self._peer_send(plan, values, want_dest=(kind != "set"))
+                    if plan["dest"] is not None:
+                        plan["dest"].record_stream(s_apply)
+            return plan
+
+        def fence(plan, applied):
+            """all ranks' sends of this operation and applies of the previous one are complete past this point"""
+            with torch.cuda.stream(s_send):
+                if applied is not None:
+                    s_send.wait_event(applied)
+                ops.peer_fence()
+                sent = torch.cuda.Event()
+                sent.record(s_send)
+            return sent
+
+        def apply(i, plan, sent):
+            kind = operations[i][0]
+            with torch.cuda.stream(s_apply):
+                s_apply.wait_event(sent)
+                if kind == "set":
+                    self._peer_apply_set(plan, operations[i][3] if len(operations[i]) > 3 else False)
+                elif kind == "get":
+                    results[i] = self._peer_apply_lookup(plan, True, operations[i][2] if len(operations[i]) > 2 else None)
+                else:
+                    results[i] = self._peer_apply_lookup(plan, False, None)[1]
+                for t in (results[i] if isinstance(results[i], tuple) else (results[i],)):
+                    if t is not None:
+                        t.record_stream(main)
+                applied = torch.cuda.Event()
+                applied.record(s_apply)
+            return applied
+
+        def drain():
+            for s in (s_send, s_apply):
+                ev = torch.cuda.Event()
+                ev.record(s)
+                main.wait_event(ev)
+
+        assert all(op[0] in ("get", "set", "remove") for op in operations)
+        applied = None
+        plan = send(0)
+        sent = fence(plan, None) if plan is not None else None
+        for i in range(len(operations)):
+            if plan is None:
+                # this batch does not fit the arena: everything so far completes, then the all-to-all path
+                drain()
+                results[i] = self._run_one(operations[i], peer=False)
+                back = torch.cuda.Event()
+                back.record(main)
+                s_send.wait_event(back)
+                s_apply.wait_event(back)
+                applied = None
+                nxt = send(i + 1) if i + 1 < len(operations) else None
+            else:
+                applied = apply(i, plan, sent)                                # enqueued; the table work takes a while
+                nxt = send(i + 1) if i + 1 < len(operations) else None       # runs meanwhile (the host waits for counts)
+            if i + 1 < len(operations):
+                plan = nxt
+                sent = fence(plan, applied) if plan is not None else None
+        drain()
+        return results
+
+    def _run_one(self, op, peer=True):
+        kind = op[0]
+        saved, self._peer_on = self._peer_on, self._peer_on and peer
+        try:
+            if kind == "set":
+                return self.set(op[1], op[2], assume_unique=op[3] if len(op) > 3 else False)
+            if kind == "get":
+                return self.get(op[1], op[2] if len(op) > 2 else None)
+            return self.remove(op[1])
+        finally:
+            self._peer_on = saved
 
     # ------------------------------------------------------------------ operations
     def set(self, keys, values, assume_unique=False):
@@ -467,12 +601,9 @@ class ShardedClosedHashmap:
         if self._peer_on:
             plan = self._peer_plan(keys)
             if plan is not None:
-                self.ops.scatter_to_peers(plan["keys"], values.contiguous(), self.world, plan["owners"], plan["offsets"],
-                                          plan["counts"], plan["gen"], plan["row0"], want_dest=False)
+                self._peer_send(plan, values.contiguous(), want_dest=False)
                 self.ops.peer_fence()
-                owned_keys = self.ops._peer_region(self.rank, plan["gen"], 0, rows=plan["inbox_rows"])
-                owned_values = self.ops._peer_region(self.rank, plan["gen"], 1, rows=plan["inbox_rows"])
-                self.ops.local_set(owned_keys, owned_values, plan["segments"], assume_unique)
+                self._peer_apply_set(plan, assume_unique)
                 return
         owned_keys, owned_values, segments, _, _, _ = self._route(keys, values, want_dest=False)
         self.ops.local_set(owned_keys, owned_values, segments, assume_unique)

@@ -1,7 +1,7 @@
 """Worker of tests/test_sharded_multi_gpu.py (one process per GPU, launched by torch.distributed.run).
 
 The same operation stream goes through two sharded maps, one exchanging rows with NCCL all-to-all and one storing
-them straight into the peers' memory, and -- gathered on rank 0 -- through ONE serial CPU oracle table that receives
+them straight into the peers' memory (operation by operation and as pipelined submissions), and -- gathered on rank 0 -- through ONE serial CPU oracle table that receives
 the ranks' batches in rank order.  Everything a caller can observe must agree bit for bit."""
 import os
 import sys
@@ -44,9 +44,12 @@ def main():
         tq, td = torch.from_numpy(queries).to(device), torch.from_numpy(doomed).to(device)
         results = []
         for table in (via_nccl, via_peer):
-            table.set(tk, tv)
-            gv, gf = table.get(tq, fallback_value=-3.0)
-            rm = table.remove(td)
+            if table is via_peer and step % 2 == 1:      # every other step as one pipelined submission
+                _, (gv, gf), rm = table.run([("set", tk, tv), ("get", tq, -3.0), ("remove", td)])
+            else:
+                table.set(tk, tv)
+                gv, gf = table.get(tq, fallback_value=-3.0)
+                rm = table.remove(td)
             results.append((gv.cpu().numpy(), gf.cpu().numpy(), rm.cpu().numpy(), table.n_elements))
         a, b = results
         assert np.array_equal(a[1], b[1]) and np.array_equal(a[0].view(np.uint8), b[0].view(np.uint8)), f"get differs, step {step}"
