@@ -65,3 +65,67 @@ def test_world_size_one_equals_plain_map():
     assert torch.equal(sv, mv) and torch.equal(sf, mf)
     assert torch.equal(s.remove(q[::2]), m.remove_rows(q[::2]))
     assert s.n_elements == m.n_elements == len(s)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_peer_scatter_places_rows_in_each_owners_buffer(world):
+    """dok_shard_partition_scatter_peer on one GPU: every "owner" gets its own buffer inside an arena from
+    dok_peer_alloc and a different start row; rows must land there in batch order (the multi-GPU runs hand the same
+    entry point the peers' mapped arenas instead)."""
+    from doksparse_b200 import _lib as L
+    from doksparse_b200.sharded import CudaShardOps
+    lib = L.lib()
+    np.random.seed(world)
+    params = port.draw_hash_parameters(1 << 20, 1)
+    ops = CudaShardOps("cuda:0", 1024, params, 2.0, 0.75)
+    rng = np.random.default_rng(5)
+    n = 50_000
+    keys = rng.integers(0, 2 ** 50, size=(n, 1)).astype(np.int64)
+    vals = rng.standard_normal((n, 2)).astype(np.float32)
+    tk, tv = dev(keys), dev(vals)
+    owners, offsets, counts = ops.partition_count(tk, world)
+
+    o = port.OracleHashmap(n_buckets=8, **params)
+    o._keys, o._values = np.zeros((8, 1), np.int64), np.zeros((8, 1), np.float32)
+    own = routing.owners(o.hash_uuid(keys)[1], world)
+    np.testing.assert_array_equal(host(owners), own)
+    want_counts = np.bincount(own, minlength=world)
+    np.testing.assert_array_equal(host(counts[:world]), want_counts)
+
+    region_rows = n + 64
+    base = ctypes.c_void_p()
+    assert lib.dok_peer_alloc(world * region_rows * 16, ctypes.byref(base)) == 0
+    try:
+        handle = (ctypes.c_uint8 * 64)()
+        assert lib.dok_peer_export(base, handle) == 0              # the handle other processes would open
+        row0 = [17 * (i + 1) for i in range(world)]
+        arr = ctypes.c_void_p * world
+        peer_keys = arr(*[base.value + i * region_rows * 16 for i in range(world)])
+        peer_vals = arr(*[base.value + i * region_rows * 16 + region_rows * 8 for i in range(world)])
+        rows = (ctypes.c_int64 * world)(*row0)
+        dest = torch.empty(n, device="cuda:0", dtype=torch.long)
+        L.check(lib.dok_shard_partition_scatter_peer(L.ptr(tk), 8, L.ptr(tv), 8, n, world, L.ptr(owners), L.ptr(offsets),
+                                                     L.ptr(counts), peer_keys, peer_vals, rows, L.ptr(dest),
+                                                     L.stream_ptr(torch.device("cuda:0"))), "scatter_peer")
+        arena = torch.as_tensor(CudaShardOps._RawDeviceBytes(base.value, world * region_rows * 16), device="cuda:0")
+        torch.cuda.synchronize()
+        for i in range(world):
+            mine = own == i
+            c = int(mine.sum())
+            lo = i * region_rows * 16
+            got_k = arena[lo + row0[i] * 8: lo + (row0[i] + c) * 8].view(torch.int64)
+            got_v = arena[lo + region_rows * 8 + row0[i] * 8: lo + region_rows * 8 + (row0[i] + c) * 8].view(torch.float32).view(c, 2)
+            np.testing.assert_array_equal(host(got_k), keys[mine, 0])          # batch order inside the owner
+            np.testing.assert_array_equal(host(got_v), vals[mine])
+        # dest = position in this rank's own grouped order (padded segment starts), as for the local scatter
+        padded = (want_counts + 15) // 16 * 16
+        starts = np.concatenate([[0], np.cumsum(padded)[:-1]])
+        rank_in_owner = np.zeros(n, dtype=np.int64)
+        for i in range(world):
+            rank_in_owner[own == i] = np.arange(int((own == i).sum()))
+        np.testing.assert_array_equal(host(dest), starts[own] + rank_in_owner)
+        # the count words come back through pinned memory
+        assert ops.to_host(counts)[:world] == want_counts.tolist()
+    finally:
+        torch.cuda.synchronize()
+        assert lib.dok_peer_free(base) == 0
