@@ -116,6 +116,75 @@ __global__ void __launch_bounds__(DOK_TPB) k_dense_insert(DevTable t, DevHash hp
   }
 }
 
+// ---- flatten / reshape: re-key + re-insert in one pass ----------------------------------------------------
+
+struct Rekey {
+  int old_ndim, new_ndim;
+  int old_perm[DOK_MAX_KEY_SIZE];       // storage column of logical index d in the source table
+  ll_t old_strides[DOK_MAX_KEY_SIZE];   // row-major strides of the source shape (logical order)
+  ll_t new_sizes[DOK_MAX_KEY_SIZE];     // destination shape
+};
+
+// One thread per SOURCE slot: a live slot's index tuple is linearised in the old shape, unravelled in the new one
+// and inserted with its value into the destination table -- no compaction of the source, no intermediate tensors
+// (the reference goes through indices()/values() and, for reshape, through a whole intermediate flattened tensor:
+// sparse_dok_tensor.py:479-514).  Distinct positions stay distinct, so every insert claims a fresh slot.
+template <int SB>
+__global__ void __launch_bounds__(DOK_TPB) k_rekey_insert(DevTable src, DevTable dst, DevHash hp, Rekey rk, ll_t *counters) {
+  const ll_t stride = (ll_t)gridDim.x * DOK_TPB;
+  int claimed = 0, failed = 0;
+  for (ll_t base = (ll_t)blockIdx.x * DOK_TPB; base < src.nb; base += stride) {       // uniform over the block
+    const ll_t s = base + threadIdx.x;
+    bool active = false;
+    ll_t idx[DOK_MAX_KEY_SIZE];
+    KeyHash kh{0, 0};
+    if (s < src.nb) {
+      const ll_t tag = dok_load_tag(src, s);
+      active = tag >= 0;                                  // uuids are non-negative; empty, tombstone, padding are not
+    }
+    if (active) {
+      const ll_t *krow = (const ll_t *)dok_key_row(src, s);
+      ull_t linear = 0;
+#pragma unroll
+      for (int d = 0; d < DOK_MAX_KEY_SIZE; d++)
+        if (d < rk.old_ndim) linear += (ull_t)krow[rk.old_perm[d]] * (ull_t)rk.old_strides[d];
+#pragma unroll
+      for (int d = DOK_MAX_KEY_SIZE - 1; d >= 0; d--) {
+        idx[d] = 0;
+        if (d < rk.new_ndim) {
+          const ull_t size = (ull_t)rk.new_sizes[d];
+          const ull_t q = linear / size;
+          idx[d] = (ll_t)(linear - q * size);
+          linear = q;
+        }
+      }
+      ll_t u = dok_uuid_term(idx[0], hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+      ull_t h = (ull_t)idx[0] * (ull_t)hp.a1[0] + (ull_t)hp.b1[0];
+#pragma unroll
+      for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
+        if (d < rk.new_ndim) {
+          u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
+          h *= (ull_t)idx[d] * (ull_t)hp.a1[d] + (ull_t)hp.b1[d];
+        }
+      kh = KeyHash{dok_llabs(u), (ll_t)h};
+    }
+    int outcome = -1;
+    const ll_t slot = dok_find_or_claim<SB>(dst, kh, active, &outcome);
+    if (active && slot >= 0) {
+      ll_t *krow = (ll_t *)dok_key_row(dst, slot);
+#pragma unroll
+      for (int d = 0; d < DOK_MAX_KEY_SIZE; d++) if (d < rk.new_ndim) krow[hp.perm[d]] = idx[d];
+      dok_store_value(dst, slot, dok_value_ptr(src, s));
+    }
+    claimed += outcome == DOK_OUT_CLAIMED_EMPTY || outcome == DOK_OUT_REUSED;
+    failed += outcome == DOK_OUT_FAILED;
+  }
+  if (counters) {
+    dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, claimed);
+    dok_warp_add(counters + DOK_CNT_FAILED, failed);
+  }
+}
+
 static unsigned streaming_grid(ll_t numel) {
   const ll_t blocks = (numel + DOK_TPB - 1) / DOK_TPB;
   const ll_t cap = 148 * 8;   // 8 resident blocks of 256 threads per SM
@@ -179,6 +248,35 @@ int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_s
   int rc = dok_check_launch();
   if (rc != DOK_OK) return rc;
   k_set_resolve<<<grid_for(sk.n), DOK_TPB, 0, st>>>(dt, dh, sk, sv, (const ll_t *)slot_scratch, (ll_t)epoch);
+  return dok_check_launch();
+}
+
+int dok_dok_rekey_insert(const dok_table *src, const dok_hash_params *src_hp, const int64_t *src_sizes,
+                         const dok_table *dst, const dok_hash_params *dst_hp, const int64_t *dst_sizes,
+                         int64_t *counters, void *stream) {
+  DevHash sh, dh;
+  DevTable st_, dt;
+  if (!prepare(src, src_hp, &st_, &sh) || !prepare(dst, dst_hp, &dt, &dh)) return DOK_BAD_ARG;
+  if (sh.dtype != DOK_I64 || dh.dtype != DOK_I64 || !src_sizes || !dst_sizes || st_.vb != dt.vb) return DOK_BAD_ARG;
+  Rekey rk;
+  memset(&rk, 0, sizeof(rk));
+  rk.old_ndim = sh.ks;
+  rk.new_ndim = dh.ks;
+  ll_t old_total = 1, new_total = 1;
+  for (int d = sh.ks - 1; d >= 0; d--) {
+    if (src_sizes[d] < 1) return DOK_BAD_ARG;
+    rk.old_strides[d] = old_total;
+    rk.old_perm[d] = sh.perm[d];
+    old_total *= src_sizes[d];
+  }
+  for (int d = 0; d < dh.ks; d++) {
+    if (dst_sizes[d] < 1) return DOK_BAD_ARG;
+    rk.new_sizes[d] = dst_sizes[d];
+    new_total *= dst_sizes[d];
+  }
+  if (old_total != new_total) return DOK_BAD_ARG;
+  const unsigned grid = streaming_grid(st_.nb);
+  DOK_DISPATCH_SB(dt, (k_rekey_insert<SB><<<grid, DOK_TPB, 0, (cudaStream_t)stream>>>(st_, dt, dh, rk, (ll_t *)counters)));
   return dok_check_launch();
 }
 

@@ -422,24 +422,44 @@ class SparseDOKTensor(object):
     def T(self):
         return self.t()
 
+    def _rekeyed(self, new_shape):
+        """This tensor with its stored positions re-expressed in `new_shape` (same number of elements), built by ONE
+        kernel that walks the slots, re-keys and inserts (dok_dok_rekey_insert); the table gets
+        next_power_of_2(nnz) buckets like a tensor constructed from indices and values."""
+        new_shape = tuple(int(x) for x in new_shape)
+        hashmap = self._hashmap
+        if hashmap._values is None:
+            return SparseDOKTensor(size=new_shape, device=self.device, dtype=self.dtype)
+        live = int((hashmap._uuid >= 0).sum().item())
+        out = CudaClosedHashmap(n_buckets=next_power_of_2(live), device=self.device)
+        out._begin_bulk_insert((len(new_shape),), torch.long, (1,), self.dtype, live)
+        if live:
+            cnt = out._counters()
+            old_sizes = (ctypes.c_int64 * len(self.shape))(*[int(x) for x in self.shape])
+            new_sizes = (ctypes.c_int64 * len(new_shape))(*new_shape)
+            with torch.cuda.device(self.device):
+                L.check(L.lib().dok_dok_rekey_insert(hashmap._c_table(), hashmap._c_hash(), old_sizes, out._c_table(),
+                                                     out._c_hash(), new_sizes, L.ptr(cnt), L.stream_ptr(self.device)),
+                        "dok_dok_rekey_insert")
+        return SparseDOKTensor.from_storage(out, size=new_shape)
+
     def flatten(self):
-        indices = self.indices()
-        values = self.values()
-        stride = torch.tensor(self._stride(), device=self.device, dtype=torch.long)[:, None]
-        flat_indices = (indices * stride).sum(dim=0, keepdim=True)
-        return SparseDOKTensor(size=[int(np.prod(self.shape))], indices=flat_indices, values=values, device=self.device)
+        """(sparse_dok_tensor.py:479-489)"""
+        return self._rekeyed((int(np.prod(self.shape)),))
 
     def reshape(self, *new_shape):
+        """(sparse_dok_tensor.py:491-514).  The reference builds the flattened tensor first and the reshaped one from
+        it; here the slots are re-keyed straight into the new shape, and the random draws that the skipped
+        intermediate table would have consumed are consumed all the same."""
+        if len(new_shape) == 1 and isinstance(new_shape[0], (tuple, list, torch.Size)):
+            new_shape = tuple(new_shape[0])
         assert np.prod(new_shape) == np.prod(self.shape)
-        flattened = self.flatten()
         if len(new_shape) == 1:
-            return flattened
-        indices = flattened.indices()
-        values = flattened.values()
-        new_stride = torch.tensor(util.shape_to_stride(new_shape), device=self.device, dtype=torch.long)[:, None]
-        new_extent = torch.tensor(new_shape, device=self.device, dtype=torch.long)[:, None]
-        new_indices = torch.div(indices.expand(len(new_shape), -1), new_stride, rounding_mode="floor") % new_extent
-        return SparseDOKTensor(size=tuple(new_shape), indices=new_indices, values=values, device=self.device)
+            return self.flatten()
+        if self._hashmap._values is not None:
+            live = int((self._hashmap._uuid >= 0).sum().item())
+            util.consume_fresh_map_draws(next_power_of_2(live), 1, live)
+        return self._rekeyed(new_shape)
 
     # ------------------------------------------------------------------ elementwise on stored values
     def _unary(self, name, *args, **kwargs):

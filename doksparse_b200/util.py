@@ -54,3 +54,26 @@ def shape_to_stride(shape):
         out.append(acc)
         acc *= int(s)
     return tuple(reversed(out))
+
+
+def consume_fresh_map_draws(n_buckets, key_size, n_new, rehash_factor=2.0, rehash_threshold=0.75):
+    """Advances the global numpy random state by exactly what a never-used reference map of `n_buckets` consumes when
+    its first `set` stores `n_new` distinct keys of `key_size` elements (cuda_closed_hashmap.py:66-113, 350-366): one
+    draw per element for prime1, prime2, alpha1, alpha2, beta1, beta2, and the same again for the rebuilt table when
+    the batch crosses the rehash threshold.  Used where this library skips an intermediate tensor that the reference
+    builds, so that tensors created afterwards still get the parameters the reference would give them."""
+    import numpy as np
+
+    def draw(nb):
+        prime1 = [next_prime(np.random.randint(nb, nb * 2)) for _ in range(key_size)]
+        for _ in range(key_size):
+            np.random.randint(0, 2 ** 60, dtype="int64")
+        for _ in range(4):
+            for p in prime1:
+                np.random.randint(int(p))
+
+    if n_new == 0:
+        return
+    draw(int(n_buckets))
+    if n_new > int(rehash_threshold * n_buckets):
+        draw(int(n_new * rehash_factor))

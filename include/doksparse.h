@@ -237,6 +237,15 @@ int dok_dok_zero_items(const dok_table *t, const dok_hash_params *hp, const dok_
  * sizes[ndim] is the dense shape, ndim = hp->key_size, keys are int64. */
 int dok_dense_count_nonzero(const void *dense, int64_t numel, int elem_bytes, int is_float, int64_t *count_out,
                             void *stream);
+
+/* flatten / reshape in one pass (replaces the indices() / values() round trips of sparse_dok_tensor.py:479-514):
+ * every live slot of src (int64 index keys of shape src_sizes[src_hp->key_size], row-major) is re-keyed to the index
+ * tuple of the same linear position in dst_sizes[dst_hp->key_size] and inserted with its value into dst (an initialised
+ * table with the same value_bytes and enough room).  counters[DOK_CNT_CLAIMED_EMPTY] += rows inserted,
+ * counters[DOK_CNT_FAILED] += rows that found dst full. */
+int dok_dok_rekey_insert(const dok_table *src, const dok_hash_params *src_hp, const int64_t *src_sizes /* host */,
+                         const dok_table *dst, const dok_hash_params *dst_hp, const int64_t *dst_sizes /* host */,
+                         int64_t *counters, void *stream);
 int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, const void *dense,
                              const int64_t *sizes /* host */, int64_t numel, int is_float, int64_t *counters,
                              void *stream);

@@ -277,3 +277,38 @@ def test_sparse_gather_and_sparse_assignment():
         assert torch.equal(t[sel], src.to_dense())
         assert t._nnz() == live_outside + 500                          # n_elements: what stayed plus nnz(src)
         assert t.storage().n_buckets == int(np.ceil((live_outside + 500) * 2.0 * 2))
+
+
+def test_flatten_and_reshape_rekey_in_one_pass():
+    """flatten / reshape through the fused re-key kernel, against the dense semantics, for plain tensors, permuted
+    views and an empty tensor; the random draws stay in step with the reference's two-tensor route."""
+    from doksparse_b200 import SparseDOKTensor
+    from doksparse_b200.util import consume_fresh_map_draws
+    rng = np.random.default_rng(21)
+    shape = (12, 10, 16)
+    idx, vals = random_coo(rng, shape, 700)
+    np.random.seed(21)
+    t = SparseDOKTensor(shape, torch.from_numpy(idx).cuda(), torch.from_numpy(vals).cuda())
+    dense = t.to_dense()
+    flat = t.flatten()
+    assert tuple(flat.shape) == (1920,) and flat._nnz() == 700 and flat.storage().n_buckets == 1024
+    assert torch.equal(flat.to_dense(), dense.flatten())
+    for new_shape in ((40, 48), (2, 6, 10, 16), (1920, 1)):
+        r = t.reshape(*new_shape)
+        assert tuple(r.shape) == new_shape and r._nnz() == 700 and r.storage().n_buckets == 1024
+        assert torch.equal(r.to_dense(), dense.reshape(new_shape))
+    view = t.permute(2, 0, 1)
+    assert torch.equal(view.reshape(16, 120).to_dense(), dense.permute(2, 0, 1).reshape(16, 120))
+    assert torch.equal(view.flatten().to_dense(), dense.permute(2, 0, 1).flatten())
+    empty = SparseDOKTensor((4, 6), device="cuda:0")
+    assert empty.reshape(3, 8)._nnz() == 0 and tuple(empty.reshape(3, 8).shape) == (3, 8)
+
+    # draws: reshape to 2-D consumes what a flattened tensor plus the reshaped one would
+    np.random.seed(5)
+    a = t.reshape(40, 48)
+    after_reshape = np.random.get_state()[1][:8].copy(), np.random.get_state()[2]
+    np.random.seed(5)
+    consume_fresh_map_draws(1024, 1, 700)
+    consume_fresh_map_draws(1024, 2, 700)
+    expected = np.random.get_state()[1][:8].copy(), np.random.get_state()[2]
+    assert (after_reshape[0] == expected[0]).all() and after_reshape[1] == expected[1]
