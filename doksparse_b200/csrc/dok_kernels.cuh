@@ -228,6 +228,55 @@ __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, K
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// rehash: live slots of one table straight into another
+// ---------------------------------------------------------------------------------------------------------
+
+// One thread per SOURCE slot: the stored key row of a live slot is hashed with the destination's parameters and
+// inserted, key bytes and value copied as they are (both tables store key element i in column perm[i]).  Replaces
+// the reference's rehash = two boolean-mask gathers plus a full `set` with its pre-get and unique
+// (cuda_closed_hashmap.py:456-468) and this library's own compaction + insert.  Live keys are pairwise different,
+// so every row claims a fresh slot; tombstones stay behind.
+template <int SB>
+__global__ void __launch_bounds__(DOK_TPB) k_reinsert(DevTable src, DevTable dst, DevHash hp, ll_t *counters) {
+  const ll_t stride = (ll_t)gridDim.x * DOK_TPB;
+  int claimed = 0, failed = 0;
+  for (ll_t base = (ll_t)blockIdx.x * DOK_TPB; base < src.nb; base += stride) {       // uniform over the block
+    const ll_t s = base + threadIdx.x;
+    bool active = false;
+    if (s < src.nb) active = dok_load_tag(src, s) >= 0;   // uuids are non-negative; empty, tombstone, padding are not
+    KeyHash kh{0, 0};
+    const char *krow = dok_key_row(src, active ? s : 0);
+    if (active) {
+      ll_t k = dok_key_elem(krow, hp.dtype, hp.perm[0]);
+      ll_t u = dok_uuid_term(k, hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+      ull_t h = (ull_t)k * (ull_t)hp.a1[0] + (ull_t)hp.b1[0];
+      for (int i = 1; i < hp.ks; i++) {
+        k = dok_key_elem(krow, hp.dtype, hp.perm[i]);
+        u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(k, hp.a[i], hp.b[i], hp.p[i], hp.m[i]));
+        h *= (ull_t)k * (ull_t)hp.a1[i] + (ull_t)hp.b1[i];
+      }
+      kh = KeyHash{dok_llabs(u), (ll_t)h};
+    }
+    int outcome = -1;
+    const ll_t slot = dok_find_or_claim<SB>(dst, kh, active, &outcome);
+    if (active && slot >= 0) {
+      char *drow = dok_key_row(dst, slot);
+      if ((dst.kb & 7) == 0) for (int i = 0; i < (dst.kb >> 3); i++) ((ull_t *)drow)[i] = ((const ull_t *)krow)[i];
+      else if ((dst.kb & 3) == 0) for (int i = 0; i < (dst.kb >> 2); i++) ((unsigned *)drow)[i] = ((const unsigned *)krow)[i];
+      else if ((dst.kb & 1) == 0) for (int i = 0; i < (dst.kb >> 1); i++) ((unsigned short *)drow)[i] = ((const unsigned short *)krow)[i];
+      else for (int i = 0; i < dst.kb; i++) drow[i] = krow[i];
+      dok_store_value(dst, slot, dok_value_ptr(src, s));
+    }
+    claimed += outcome == DOK_OUT_CLAIMED_EMPTY || outcome == DOK_OUT_REUSED;
+    failed += outcome == DOK_OUT_FAILED;
+  }
+  if (counters) {
+    dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, claimed);
+    dok_warp_add(counters + DOK_CNT_FAILED, failed);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // init / uuid
 // ---------------------------------------------------------------------------------------------------------
 

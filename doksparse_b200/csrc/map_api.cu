@@ -169,4 +169,17 @@ int dok_map_compact_scatter(const dok_table *t, const dok_hash_params *hp, const
   return dok_check_launch();
 }
 
+int dok_map_reinsert(const dok_table *src, const dok_table *dst, const dok_hash_params *dst_hp, int64_t *counters,
+                     void *stream) {
+  DevHash dh;
+  DevTable st_, dt;
+  if (!prepare(dst, dst_hp, &dt, &dh) || !dok_make_table(src, &st_)) return DOK_BAD_ARG;
+  if (st_.kb != dt.kb || st_.vb != dt.vb) return DOK_BAD_ARG;
+  ll_t blocks = (st_.nb + DOK_TPB - 1) / DOK_TPB;
+  if (blocks > 148 * 8) blocks = 148 * 8;            // 8 resident blocks of 256 threads per SM, grid-stride over the slots
+  if (blocks < 1) blocks = 1;
+  DOK_DISPATCH_SB(dt, (k_reinsert<SB><<<(unsigned)blocks, DOK_TPB, 0, (cudaStream_t)stream>>>(st_, dt, dh, (ll_t *)counters)));
+  return dok_check_launch();
+}
+
 }  // extern "C"

@@ -194,7 +194,8 @@ class CudaClosedHashmap:
         self._materialise_parameters()
         if n_new > int(self._rehash_threshold * self.n_buckets):
             self.__init__(n_buckets=int(n_new * self._rehash_factor), device=self.device, key_perm=self._key_perm,
-                          rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold)
+                          rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
+                          tombstone_threshold=self._tombstone_threshold)
             self._allocate(key_shape, key_dtype, value_shape, value_dtype)
             self._materialise_parameters()
         self._n_elements += n_new
@@ -674,15 +675,36 @@ class CudaClosedHashmap:
 
     # ------------------------------------------------------------------ rehash
     def rehash(self, n_buckets):
-        keys, values, _ = self.items(uuid=False)
-        keys = keys.reshape((-1,) + tuple(self.key_shape))
+        """New table of `n_buckets` with new random parameters holding the live items (cuda_closed_hashmap.py:456-468).
+        One kernel walks the old slots and inserts every live one into the new table (dok_map_reinsert): no
+        compaction, no pre-get, no unique.  Like the reference's recursive `set`, a table that the live items fill
+        beyond the rehash threshold grows once more (and draws its parameters again)."""
+        if self._slots is None:
+            self.__init__(n_buckets=n_buckets, device=self.device, key_perm=self._key_perm,
+                          rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
+                          tombstone_threshold=self._tombstone_threshold)
+            return
+        live = int((self._uuid >= 0).sum().item())
+        old_slots, old_stamp = self._slots, self._shared["stamp"]          # kept alive until the kernel has run
+        source = L.Table()
+        source.slots = old_slots.data_ptr()
+        source.stamp = old_stamp.data_ptr() if old_stamp is not None else None
+        source.n_buckets = self._n_buckets
+        source.slot_bytes = self._layout.slot_bytes
+        source.value_bytes, source.key_bytes = self._value_bytes, self._key_bytes
+        geometry = (self._key_shape, self._key_dtype, self._value_shape, self._value_dtype)
         self.__init__(
             n_buckets=n_buckets, device=self.device, key_perm=self._key_perm,
             rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
             tombstone_threshold=self._tombstone_threshold,
         )
-        # live rows have pairwise different keys: one kernel
-        self.set(keys, values, assume_unique=True)
+        self._begin_bulk_insert(*geometry, live)
+        if live:
+            cnt = self._counters()
+            with torch.cuda.device(self.device):
+                L.check(L.lib().dok_map_reinsert(ctypes.byref(source), self._c_table(), self._c_hash(), L.ptr(cnt),
+                                                 L.stream_ptr(self.device)), "dok_map_reinsert")
+            old_slots.record_stream(torch.cuda.current_stream(self.device))
 
     # ------------------------------------------------------------------ persistence
     def state_dict(self):

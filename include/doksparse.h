@@ -238,6 +238,13 @@ int dok_dok_zero_items(const dok_table *t, const dok_hash_params *hp, const dok_
 int dok_dense_count_nonzero(const void *dense, int64_t numel, int elem_bytes, int is_float, int64_t *count_out,
                             void *stream);
 
+/* rehash in one pass (replaces cuda_closed_hashmap.py:456-468: two boolean-mask gathers and a full set): every live
+ * slot of src is hashed with dst's parameters and inserted into dst (initialised, same key and value widths, same
+ * key_perm); key bytes and values are copied as stored.  counters[DOK_CNT_CLAIMED_EMPTY] += rows inserted,
+ * counters[DOK_CNT_FAILED] += rows that found dst full. */
+int dok_map_reinsert(const dok_table *src, const dok_table *dst, const dok_hash_params *dst_hp, int64_t *counters,
+                     void *stream);
+
 /* flatten / reshape in one pass (replaces the indices() / values() round trips of sparse_dok_tensor.py:479-514):
  * every live slot of src (int64 index keys of shape src_sizes[src_hp->key_size], row-major) is re-keyed to the index
  * tuple of the same linear position in dst_sizes[dst_hp->key_size] and inserted with its value into dst (an initialised
