@@ -14,6 +14,13 @@ Per batch and rank:
 The uuid parameters used for routing are fixed at construction and identical on every rank; each shard is an
 ordinary CudaClosedHashmap and rehashes locally on its own load.
 
+With `peer_capacity_rows > 0` (ranks of one node) steps 2, 3 and 5 are replaced by the peer exchange: the counts of
+all ranks are gathered, the partition kernel stores each row straight into its owner's memory over NVLink (every rank
+maps the others' exchange arenas), a one-element all-reduce on the stream orders the stores before the owners' reads,
+and answers are delivered into the asker's memory the same way.  `run([...])` submits several operations at once and
+overlaps the sending of one with the table work of the one before.  Batches that do not fit the arena take the
+all-to-all path; `close()` releases the arena.
+
 The collective and bookkeeping logic talks to the device through a small `ops` object so that it can be
 exercised with CPU ranks (gloo) in the tests, where a test double stands in for the CUDA kernels.  The product
 default, `CudaShardOps`, has no CPU path.
