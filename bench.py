@@ -428,8 +428,10 @@ def run_candidate(args):
         d = batches[b % N_BATCHES]
         if pipelined and events is None:
             # one submission: the send stage of each operation overlaps the table work of the one before
+            # (wait=False: the first send of the next step may overlap this step's last table work; the timed loop
+            # and the check wait once, at their end)
             (values, found), _, _ = table.run([("get", d["get_keys"]), ("set", d["set_keys"], d["set_values"]),
-                                               ("remove", d["fresh_keys"])])
+                                               ("remove", d["fresh_keys"])], wait=False)
             return values, found
         if events is not None:
             events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
@@ -446,6 +448,8 @@ def run_candidate(args):
 
     # ---- correctness of what is being timed (first batch, before any timing)
     values, found = step(0)
+    if pipelined:
+        table.wait()
     d0 = batches[0]
     expect_found = d0["get_idx"] < (1 << 40)
     checks = {"found_flags_ok": bool(torch.equal(found, expect_found)),
@@ -457,6 +461,8 @@ def run_candidate(args):
     sampler = ClockSampler(local_rank) if rank == 0 else None      # started early: its start-up must not fall into the timed region
     for s in range(1, args.warmup):
         step(s)
+    if pipelined:
+        table.wait()
     if sampler:
         time.sleep(0.5)
         sampler.rows.clear()
@@ -469,6 +475,8 @@ def run_candidate(args):
     t_start.record()
     for s in range(args.steps):
         step(s + args.warmup, None if pipelined else events)
+    if pipelined:
+        table.wait()
     t_stop.record()
     barrier()
     launches = L.lib().dok_launch_count() - launches0

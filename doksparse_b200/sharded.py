@@ -369,6 +369,7 @@ class ShardedClosedHashmap:
         self._peer_on = False
         self._peer_seq = 0
         self._streams = None
+        self._last_applied = None
         self._value_shape = None
         self._value_dtype = None
 
@@ -490,14 +491,17 @@ class ShardedClosedHashmap:
         self.ops.peer_fence()
         return self._peer_apply_lookup(plan, with_values, fallback_value)
 
-    def run(self, operations):
+    def run(self, operations, wait=True):
         """Several operations as one software pipeline: [("get", keys[, fallback_value]), ("set", keys, values[,
         assume_unique]), ("remove", keys)] -> list of results (get: (values, is_found); set: None; remove: flags).
         Collective: every rank passes the same sequence of operation kinds.  The operations are applied in order, as if
         called one after the other; what overlaps is the SEND stage of operation k + 1 (it only reads the caller's
         batch: partition, count gather, stores into the owners' other inbox generation over NVLink) with the APPLY
         stage of operation k (table work in HBM), on two streams.  Without the peer exchange the operations simply
-        run one after the other.  Results are ready for the caller's current stream when the call returns."""
+        run one after the other.  Results are ready for the caller's current stream when the call returns -- unless
+        `wait=False`: then the call only enqueues, the next submission's first send may overlap this one's last table
+        work, and the caller calls `wait()` before it uses results or reuses / frees the input tensors (which must
+        already be complete on the current stream at the time of the call)."""
         if not operations:
             return []
         if not self._peer_on or not self.ops.can_pipeline():
@@ -562,13 +566,14 @@ class ShardedClosedHashmap:
                 main.wait_event(ev)
 
         assert all(op[0] in ("get", "set", "remove") for op in operations)
-        applied = None
+        applied = self._last_applied          # table work of an earlier submission that was not waited for
         plan = send(0)
-        sent = fence(plan, None) if plan is not None else None
+        sent = fence(plan, applied) if plan is not None else None
         for i in range(len(operations)):
             if plan is None:
                 # this batch does not fit the arena: everything so far completes, then the all-to-all path
                 drain()
+                self._last_applied = None
                 results[i] = self._run_one(operations[i], peer=False)
                 back = torch.cuda.Event()
                 back.record(main)
@@ -582,8 +587,27 @@ class ShardedClosedHashmap:
             if i + 1 < len(operations):
                 plan = nxt
                 sent = fence(plan, applied) if plan is not None else None
-        drain()
+        self._last_applied = applied
+        if wait:
+            drain()
+            self._last_applied = None
         return results
+
+    def _settle(self):
+        """Operations called one at a time run on the caller's stream: anything still in flight from a submission
+        that was not waited for must be ordered before them."""
+        if self._last_applied is not None:
+            self.wait()
+
+    def wait(self):
+        """The caller's current stream waits for everything submitted with run(..., wait=False)."""
+        if self._streams is not None:
+            main = torch.cuda.current_stream(self.ops.device)
+            for s in self._streams:
+                ev = torch.cuda.Event()
+                ev.record(s)
+                main.wait_event(ev)
+        self._last_applied = None
 
     def _run_one(self, op, peer=True):
         kind = op[0]
@@ -600,6 +624,7 @@ class ShardedClosedHashmap:
     # ------------------------------------------------------------------ operations
     def set(self, keys, values, assume_unique=False):
         """Collective insert-or-assign.  `assume_unique` promises pairwise different keys across ALL ranks' batches."""
+        self._settle()
         if self._value_shape is None:
             self._value_shape, self._value_dtype = tuple(values.shape[1:]), values.dtype
             if self._peer_capacity and getattr(self.ops, "supports_peer", False):
@@ -698,6 +723,7 @@ class ShardedClosedHashmap:
         """Collective lookup -> (values[n, *value_shape], is_found[n]) in the caller's row order."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
+        self._settle()
         if self.world == 1:
             if not self.ops.ready():
                 return self._lookup(keys, None, True, fallback_value)
@@ -712,6 +738,7 @@ class ShardedClosedHashmap:
         """Collective removal -> is_removed[n] aligned to the caller's rows (equal keys report once)."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
+        self._settle()
         if self.world == 1 and self.ops.ready():
             return self.ops.local_remove(keys, [(0, keys.shape[0])])
         if self._peer_on:
@@ -723,6 +750,7 @@ class ShardedClosedHashmap:
     @property
     def n_elements(self):
         """Live rows over all shards (collective)."""
+        self._settle()
         n = self.ops.local_n_elements().clone().reshape(1)
         if self.world > 1:
             dist.all_reduce(n, group=self.group)

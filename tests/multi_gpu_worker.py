@@ -44,8 +44,13 @@ def main():
         tq, td = torch.from_numpy(queries).to(device), torch.from_numpy(doomed).to(device)
         results = []
         for table in (via_nccl, via_peer):
-            if table is via_peer and step % 2 == 1:      # every other step as one pipelined submission
-                _, (gv, gf), rm = table.run([("set", tk, tv), ("get", tq, -3.0), ("remove", td)])
+            if table is via_peer and step % 2 == 1:      # every other step as pipelined submissions
+                if step % 4 == 1:
+                    _, (gv, gf), rm = table.run([("set", tk, tv), ("get", tq, -3.0), ("remove", td)])
+                else:                                    # two submissions that are not waited for in between
+                    _, (gv, gf) = table.run([("set", tk, tv), ("get", tq, -3.0)], wait=False)
+                    (rm,) = table.run([("remove", td)], wait=False)
+                    table.wait()
             else:
                 table.set(tk, tv)
                 gv, gf = table.get(tq, fallback_value=-3.0)
