@@ -116,7 +116,7 @@ __device__ __forceinline__ ll_t dok_stamp(ll_t epoch, ll_t row) { return (epoch 
 // this epoch sets the conflict bit and counts a duplicate (in slot_out[n], zeroed by the host before the
 // launch); the second kernel then lets the slot's last row rewrite it.
 template <int SB, class Keys, class Values>
-__global__ void __launch_bounds__(DOK_TPB, 4) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
+__global__ void __launch_bounds__(DOK_TPB, 6) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
                                                        ll_t *__restrict__ slot_out, ll_t epoch,
                                                        uint8_t *__restrict__ out_stored, ll_t *counters) {
   __shared__ BlockTally tally;
