@@ -438,16 +438,20 @@ class ShardedClosedHashmap:
         exact = [[int(flat[s * 2 * w + o]) for o in range(w)] for s in range(w)]        # [source][owner]
         padded = [[int(flat[s * 2 * w + w + o]) for o in range(w)] for s in range(w)]
         cap = self._peer_capacity
-        if max(sum(padded[s][o] for s in range(w)) for o in range(w)) > cap or max(sum(row) for row in padded) > cap:
+        if max(sum(exact[s][o] for s in range(w)) for o in range(w)) > cap or max(sum(row) for row in padded) > cap:
             return None
         gen = self._peer_seq & 1
         self._peer_seq += 1
+        # Inboxes are filled without gaps: the sources' segments follow each other in rank order at their exact row
+        # counts (stores need no alignment, unlike the all-to-all), so an owner can apply everything it received
+        # with one launch, in which row order is (source rank, row): the order that makes "last row wins" global.
+        # Result regions keep the padded starts of the asker's grouped order, which is what dest_index refers to.
         starts, run = [], 0
-        for s in range(w):                                  # my inbox: sources in rank order, at padded offsets
+        for s in range(w):
             starts.append(run)
-            run += padded[s][r]
+            run += exact[s][r]
         return dict(keys=keys, owners=owners, offsets=offsets, counts=counts, exact=exact, padded=padded, gen=gen,
-                    row0=[sum(padded[s][o] for s in range(r)) for o in range(w)],
+                    row0=[sum(exact[s][o] for s in range(r)) for o in range(w)],
                     segments=[(starts[s], exact[s][r]) for s in range(w)], inbox_rows=run)
 
     # An operation over the peer exchange has two stages.  SEND: rows into the owners' inboxes (partition + stores
@@ -460,7 +464,7 @@ class ShardedClosedHashmap:
     def _peer_apply_set(self, plan, assume_unique):
         owned_keys = self.ops._peer_region(self.rank, plan["gen"], 0, rows=plan["inbox_rows"])
         owned_values = self.ops._peer_region(self.rank, plan["gen"], 1, rows=plan["inbox_rows"])
-        self.ops.local_set(owned_keys, owned_values, plan["segments"], assume_unique)
+        self.ops.local_set(owned_keys, owned_values, [(0, plan["inbox_rows"])], assume_unique)     # one launch
 
     def _peer_apply_lookup(self, plan, with_values, fallback_value):
         w, r, ops = self.world, self.rank, self.ops
