@@ -470,17 +470,24 @@ class ShardedClosedHashmap:
         w, r, ops = self.world, self.rank, self.ops
         gen, padded = plan["gen"], plan["padded"]
         owned_keys = ops._peer_region(r, gen, 0, rows=plan["inbox_rows"])
-        order = list(range(w))
-        if with_values:       # lookups commute: other ranks' rows first, so that the copy of their answers over NVLink
-            order = [s for s in order if s != r] + [r]      # runs while this rank's own rows are probed
-        for s in order:       # removals are applied in rank order: which of two equal keys reports is defined by it
-            start, rows = plan["segments"][s]
-            if not rows:
-                continue
-            at = sum(padded[s][o] for o in range(r))        # my segment in source s's grouped order
-            flags = ops._peer_region(s, gen, 3, rows=rows, row0=at)
-            values = ops._peer_region(s, gen, 2, rows=rows, row0=at) if with_values else None
-            ops.local_answer(owned_keys[start:start + rows], values, flags, fallback_value, remote=(s != r))
+        if with_values:
+            # lookups commute: other ranks' rows first, source by source, so that the copy of their answers over NVLink
+            # runs while the next source's rows (and last this rank's own) are probed
+            for s in [s for s in range(w) if s != r] + [r]:
+                start, rows = plan["segments"][s]
+                if not rows:
+                    continue
+                at = sum(padded[s][o] for o in range(r))    # my segment in source s's grouped order
+                ops.local_answer(owned_keys[start:start + rows], ops._peer_region(s, gen, 2, rows=rows, row0=at),
+                                 ops._peer_region(s, gen, 3, rows=rows, row0=at), fallback_value, remote=(s != r))
+        else:
+            # removals source by source in rank order, one launch each: among equal keys of different ranks the
+            # earlier rank reports the removal, and one launch over everything would leave that to the race
+            for s, (start, rows) in enumerate(plan["segments"]):
+                if rows:
+                    at = sum(padded[s][o] for o in range(r))
+                    ops.local_answer(owned_keys[start:start + rows], None, ops._peer_region(s, gen, 3, rows=rows, row0=at),
+                                     None, remote=(s != r))
         ops.answers_delivered()
         ops.peer_fence(apply_side=True)
         n_mine = sum(padded[r])
