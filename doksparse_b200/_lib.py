@@ -88,6 +88,11 @@ def _declare(lib):
         "dok_map_count_new": ([TP, HP, P, I64, P, I64, P, P], I),
         "dok_static_scratch_max_rows": ([], I64),
         "dok_map_count_new_static": ([TP, HP, P, I64, P, P], I),
+        "dok_map_get_sliced": ([TP, HP, P, I64, I64, P, P, P, P, P, P, P], I),
+        "dok_map_set_sliced": ([TP, HP, P, P, I64, I64, P, P, P, I64, I, P, P], I),
+        "dok_map_remove_sliced": ([TP, HP, P, I64, I64, P, P, P, P, P], I),
+        "dok_set_window_bytes": ([I64, I64], I),
+        "dok_table_passes": ([TP], I),
         "dok_compact_tiles": ([I64], I64),
         "dok_map_compact_count": ([TP, P, P], I),
         "dok_map_compact_scatter": ([TP, HP, P, P, I, P, P, P], I),
@@ -106,6 +111,11 @@ def _declare(lib):
         "dok_dok_rekey_insert": ([TP, HP, P, TP, HP, P, P, P], I),
         "dok_map_reinsert": ([TP, TP, HP, P, P], I),
         "dok_shard_partition_scatter_peer": ([P, I, P, I, I64, I, P, P, P, P, P, P, P, P], I),
+        "dok_shard_partition_check_slices": ([P, I, I64, I, P, P], I),
+        "dok_shard_partition_scatter_sliced": ([P, I, P, I, I64, I, P, P, P, P, P, P, I64, P, P, P], I),
+        "dok_copy_counted": ([P, P, I, P, P, I, I64, P, P, P], I),
+        "dok_shard_token_prepare": ([P, I64, P, P], I),
+        "dok_shard_token_finish": ([P, P, P], I),
         "dok_peer_alloc": ([I64, P], I),
         "dok_peer_free": ([P], I),
         "dok_peer_export": ([P, P], I),

@@ -28,7 +28,6 @@ static bool prepare(const dok_table *t, const dok_hash_params *hp, DevTable *dt,
   return dt->kb == dh->ks * dh->elem_bytes;
 }
 
-static unsigned grid_for(ll_t n) { return (unsigned)((n + DOK_TPB - 1) / DOK_TPB); }
 
 static bool make_sel(const dok_selectors *sel, const DevHash &dh, SelKeys *out) {
   if (!sel || sel->ndim != dh.ks || dh.dtype != DOK_I64) return false;
@@ -100,6 +99,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_dense_insert(DevTable t, DevHash hp
         }
       kh = KeyHash{dok_llabs(u), (ll_t)h};
     }
+    active = dok_in_window(t, kh, active);
     const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
     if (active && slot >= 0) {
       ll_t *krow = (ll_t *)dok_key_row(t, slot);
@@ -168,6 +168,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_rekey_insert(DevTable src, DevTable
         }
       kh = KeyHash{dok_llabs(u), (ll_t)h};
     }
+    active = dok_in_window(dst, kh, active);
     int outcome = -1;
     const ll_t slot = dok_find_or_claim<SB>(dst, kh, active, &outcome);
     if (active && slot >= 0) {
@@ -210,8 +211,7 @@ int dok_dok_count_exists(const dok_table *t, const dok_hash_params *hp, const do
   SelKeys sk;
   if (!prepare(t, hp, &dt, &dh) || !make_sel(sel, dh, &sk) || !counters) return DOK_BAD_ARG;
   if (sk.n == 0) return DOK_OK;
-  DOK_DISPATCH_SB(dt, (k_find<SB, 0><<<grid_for(sk.n), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, nullptr, (ll_t *)counters)));
-  return dok_check_launch();
+  return launch_find<0>(dt, dh, sk, nullptr, counters, (cudaStream_t)stream);
 }
 
 int dok_dok_zero_items(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel, int64_t *counters,
@@ -221,8 +221,7 @@ int dok_dok_zero_items(const dok_table *t, const dok_hash_params *hp, const dok_
   SelKeys sk;
   if (!prepare(t, hp, &dt, &dh) || !make_sel(sel, dh, &sk) || !counters) return DOK_BAD_ARG;
   if (sk.n == 0) return DOK_OK;
-  DOK_DISPATCH_SB(dt, (k_find<SB, 1><<<grid_for(sk.n), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, sk, nullptr, (ll_t *)counters)));
-  return dok_check_launch();
+  return launch_find<1>(dt, dh, sk, nullptr, counters, (cudaStream_t)stream);
 }
 
 int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel, const void *src,
@@ -241,14 +240,7 @@ int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_s
     sv.sizes[j] = j < sel->selector_ndim ? sel->sizes[j] : 1;
     sv.strides[j] = j < sel->selector_ndim ? src_strides[j] : 0;
   }
-  cudaStream_t st = (cudaStream_t)stream;
-  if (cudaMemsetAsync(slot_scratch + sk.n, 0, sizeof(int64_t), st) != cudaSuccess) return dok_check_launch();
-  DOK_DISPATCH_SB(dt, (k_set_claim<SB><<<grid_for(sk.n), DOK_TPB, 0, st>>>(dt, dh, sk, sv, (ll_t *)slot_scratch, (ll_t)epoch,
-                                                                           nullptr, (ll_t *)counters)));
-  int rc = dok_check_launch();
-  if (rc != DOK_OK) return rc;
-  k_set_resolve<<<grid_for(sk.n), DOK_TPB, 0, st>>>(dt, dh, sk, sv, (const ll_t *)slot_scratch, (ll_t)epoch);
-  return dok_check_launch();
+  return launch_set_general(dt, dh, sk, sv, slot_scratch, epoch, nullptr, counters, (cudaStream_t)stream);
 }
 
 int dok_dok_rekey_insert(const dok_table *src, const dok_hash_params *src_hp, const int64_t *src_sizes,
@@ -276,8 +268,9 @@ int dok_dok_rekey_insert(const dok_table *src, const dok_hash_params *src_hp, co
   }
   if (old_total != new_total) return DOK_BAD_ARG;
   const unsigned grid = streaming_grid(st_.nb);
-  DOK_DISPATCH_SB(dt, (k_rekey_insert<SB><<<grid, DOK_TPB, 0, (cudaStream_t)stream>>>(st_, dt, dh, rk, (ll_t *)counters)));
-  return dok_check_launch();
+  int rc = DOK_OK;
+  DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_rekey_insert<SB><<<grid, DOK_TPB, 0, (cudaStream_t)stream>>>(st_, wt, dh, rk, (ll_t *)counters))));
+  return rc;
 }
 
 int dok_dense_count_nonzero(const void *dense, int64_t numel, int elem_bytes, int is_float, int64_t *count_out,
@@ -314,14 +307,15 @@ int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, cons
   if (prod != numel) return DOK_BAD_ARG;
   const unsigned grid = streaming_grid(numel);
   cudaStream_t st = (cudaStream_t)stream;
+  int rc = DOK_OK;
   switch (dt.vb) {
-    case 1: DOK_DISPATCH_SB(dt, (k_dense_insert<SB, unsigned char><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned char *)dense, numel, is_float, shape, (ll_t *)counters))); break;
-    case 2: DOK_DISPATCH_SB(dt, (k_dense_insert<SB, unsigned short><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned short *)dense, numel, is_float, shape, (ll_t *)counters))); break;
-    case 4: DOK_DISPATCH_SB(dt, (k_dense_insert<SB, unsigned><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const unsigned *)dense, numel, is_float, shape, (ll_t *)counters))); break;
-    case 8: DOK_DISPATCH_SB(dt, (k_dense_insert<SB, ull_t><<<grid, DOK_TPB, 0, st>>>(dt, dh, (const ull_t *)dense, numel, is_float, shape, (ll_t *)counters))); break;
+    case 1: DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_dense_insert<SB, unsigned char><<<grid, DOK_TPB, 0, st>>>(wt, dh, (const unsigned char *)dense, numel, is_float, shape, (ll_t *)counters)))); break;
+    case 2: DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_dense_insert<SB, unsigned short><<<grid, DOK_TPB, 0, st>>>(wt, dh, (const unsigned short *)dense, numel, is_float, shape, (ll_t *)counters)))); break;
+    case 4: DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_dense_insert<SB, unsigned><<<grid, DOK_TPB, 0, st>>>(wt, dh, (const unsigned *)dense, numel, is_float, shape, (ll_t *)counters)))); break;
+    case 8: DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_dense_insert<SB, ull_t><<<grid, DOK_TPB, 0, st>>>(wt, dh, (const ull_t *)dense, numel, is_float, shape, (ll_t *)counters)))); break;
     default: return DOK_BAD_ARG;
   }
-  return dok_check_launch();
+  return rc;
 }
 
 }  // extern "C"

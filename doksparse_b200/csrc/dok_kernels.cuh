@@ -18,11 +18,13 @@ __global__ void __launch_bounds__(DOK_TPB, (LW == 2 ? 8 : 1)) k_get(DevTable t, 
                                                     uint8_t *__restrict__ out_found, Fallback fb, ll_t *counters,
                                                     int count_probes) {
   __shared__ BlockTally tally;
+  if (keys.idle()) return;
   if (counters) dok_tally_begin(tally);
-  const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
-  const bool active = e < keys.count();
+  ll_t e;
+  bool active = keys.row(e);
   KeyHash kh{0, 0};
   if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
   int probes = 0;
   // on a hit the quad writes the value from the registers that hold the line
   const Located loc = dok_locate<SB, LW, false>(t, kh, e, active, &probes, EmitValue<(SB == 0 ? 32 : SB), LW>{t, out_values});
@@ -48,6 +50,13 @@ __global__ void __launch_bounds__(DOK_TPB, (LW == 2 ? 8 : 1)) k_get(DevTable t, 
     default: { constexpr int SB = 0; CALL; break; }     \
   }
 
+// launch grid of a batch: one thread per row; sliced batches put the slice in gridDim.y
+inline dim3 dok_grid(const RowKeys &k) {
+  if (k.slice_rows == 0) return dim3((unsigned)((k.n + DOK_TPB - 1) / DOK_TPB));
+  return dim3((unsigned)((k.slice_rows + DOK_TPB - 1) / DOK_TPB), (unsigned)(k.n / k.slice_rows));
+}
+inline dim3 dok_grid(const SelKeys &k) { return dim3((unsigned)((k.n + DOK_TPB - 1) / DOK_TPB)); }
+
 template <class Keys>
 inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, void *out_values, uint8_t *out_found,
                       const void *fallback, int64_t *counters, int count_probes, cudaStream_t st) {
@@ -56,13 +65,15 @@ inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, vo
   Fallback fb;
   memset(&fb, 0, sizeof(fb));
   if (fallback) memcpy(&fb, fallback, (size_t)t.vb);
-  const unsigned grid = (unsigned)((n + DOK_TPB - 1) / DOK_TPB);
+  const dim3 grid = dok_grid(keys);
+  int rc = DOK_OK;
   if (t.sb == 32 && t.vb <= 8)      // tag and value fit the first 16 bytes of the slot: half the load width
-    k_get<32, 2, Keys><<<grid, DOK_TPB, 0, st>>>(t, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes);
+    DOK_FOR_WINDOWS(t, rc, (k_get<32, 2, Keys><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, (char *)out_values, out_found, fb,
+                                                                         (ll_t *)counters, count_probes)));
   else
-    DOK_DISPATCH_SB(t, (k_get<SB, 4, Keys><<<grid, DOK_TPB, 0, st>>>(t, hp, keys, (char *)out_values, out_found, fb,
-                                                                    (ll_t *)counters, count_probes)));
-  return dok_check_launch();
+    DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_get<SB, 4, Keys><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, (char *)out_values, out_found,
+                                                                                           fb, (ll_t *)counters, count_probes))));
+  return rc;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -86,11 +97,13 @@ template <int SB, class Keys, class Values>
 __global__ void __launch_bounds__(DOK_TPB, 4) k_set_unique(DevTable t, DevHash hp, Keys keys, Values values,
                                                         uint8_t *__restrict__ out_stored, ll_t *counters) {
   __shared__ BlockTally tally;
+  if (keys.idle()) return;
   if (counters) dok_tally_begin(tally);
-  const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
-  const bool active = e < keys.count();
+  ll_t e;
+  bool active = keys.row(e);
   KeyHash kh{0, 0};
   if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
   int outcome = -1;
   const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
   if (active) {
@@ -120,11 +133,13 @@ __global__ void __launch_bounds__(DOK_TPB, 6) k_set_claim(DevTable t, DevHash hp
                                                        ll_t *__restrict__ slot_out, ll_t epoch,
                                                        uint8_t *__restrict__ out_stored, ll_t *counters) {
   __shared__ BlockTally tally;
+  if (keys.idle()) return;
   dok_tally_begin(tally);
-  const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
-  const bool active = e < keys.count();
+  ll_t e;
+  bool active = keys.row(e);
   KeyHash kh{0, 0};
   if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
   int outcome = -1, dup = 0;
   const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
   if (active) {
@@ -160,12 +175,46 @@ template <class Keys, class Values>
 __global__ void __launch_bounds__(DOK_TPB) k_set_resolve(DevTable t, DevHash hp, Keys keys, Values values,
                                                          const ll_t *__restrict__ slot_in, ll_t epoch) {
   if (slot_in[keys.count()] == 0) return;        // the first kernel met no duplicate: every row is already in place
-  const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
-  if (e >= keys.count()) return;
+  if (keys.idle()) return;
+  ll_t e;
+  if (!keys.row(e)) return;
   const ll_t slot = slot_in[e];
   if (slot < 0) return;
+  if (t.win_hi != 0) {                           // windowed passes: by the slot's own group (each slot has one pass)
+    const ll_t g = slot / t.spg;
+    if (g < t.win_lo || g >= t.win_hi) return;
+  }
   if (__ldcg(dok_stamp_ptr(t, slot)) != (dok_stamp(epoch, e) | 1)) return;
   dok_write_row(t, hp, keys, values, e, slot, true);
+}
+
+// contiguous value rows [n, value_bytes]
+template <class Keys, class Values>
+inline int launch_set_general(const DevTable &t, const DevHash &hp, const Keys &keys, const Values &values,
+                              int64_t *slot_scratch, int64_t epoch, uint8_t *out_stored, int64_t *counters, cudaStream_t st) {
+  if (cudaMemsetAsync(slot_scratch + keys.n, 0, sizeof(int64_t), st) != cudaSuccess) return dok_check_launch();
+  const dim3 grid = dok_grid(keys);
+  int rc = DOK_OK;
+  DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_set_claim<SB><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, values, (ll_t *)slot_scratch,
+                                                                                       (ll_t)epoch, out_stored, (ll_t *)counters))));
+  if (rc != DOK_OK) return rc;
+  DOK_FOR_WINDOWS(t, rc, (k_set_resolve<<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, values, (const ll_t *)slot_scratch, (ll_t)epoch)));
+  return rc;
+}
+
+inline int launch_set(const DevTable &t, const DevHash &hp, const RowKeys &keys, const char *values, int64_t *slot_scratch,
+                      int64_t epoch, uint8_t *out_stored, int64_t *counters, cudaStream_t st) {
+  RowValues rv{values};
+  return launch_set_general(t, hp, keys, rv, slot_scratch, epoch, out_stored, counters, st);
+}
+
+inline int launch_set_unique(const DevTable &t, const DevHash &hp, const RowKeys &keys, const char *values,
+                             uint8_t *out_stored, int64_t *counters, cudaStream_t st) {
+  RowValues rv{values};
+  const dim3 grid = dok_grid(keys);
+  int rc = DOK_OK;
+  DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_set_unique<SB><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, rv, out_stored, (ll_t *)counters))));
+  return rc;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -178,11 +227,13 @@ template <int SB, int REMOVE, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys keys, uint8_t *__restrict__ out_flags,
                                                   ll_t *counters) {
   __shared__ BlockTally tally;
+  if (keys.idle()) return;
   if (counters) dok_tally_begin(tally);
-  const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
-  const bool active = e < keys.count();
+  ll_t e;
+  bool active = keys.row(e);
   KeyHash kh{0, 0};
   if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
   const Located loc = dok_locate<SB, 1, false>(t, kh, e, active, nullptr, NoEmit());
   int hit = active && loc.found >= 0;
   if (REMOVE && hit) hit = dok_cas_tag(t, loc.found, kh.uuid, DOK_REMOVED) == kh.uuid;
@@ -191,6 +242,15 @@ __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys k
     dok_tally_add(tally, DOK_CNT_HITS, hit);
     dok_tally_flush(tally, counters, nullptr);
   }
+}
+
+template <int REMOVE, class Keys>
+inline int launch_find(const DevTable &t, const DevHash &hp, const Keys &keys, uint8_t *out_flags, int64_t *counters,
+                       cudaStream_t st) {
+  const dim3 grid = dok_grid(keys);
+  int rc = DOK_OK;
+  DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_find<SB, REMOVE><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, out_flags, (ll_t *)counters))));
+  return rc;
 }
 
 static __global__ void k_fill_i64(ll_t *p, ll_t n, ll_t v) {
@@ -203,11 +263,13 @@ template <int SB, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, Keys keys, ll_t *__restrict__ scratch,
                                                        ll_t scratch_slots, ll_t *counters) {
   __shared__ BlockTally tally;
+  if (keys.idle()) return;
   dok_tally_begin(tally);
-  const ll_t e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
-  const bool active = e < keys.count();
+  ll_t e;
+  bool active = keys.row(e);
   KeyHash kh{0, 0};
   if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
   const Located loc = dok_locate<SB, 1, false>(t, kh, e, active, nullptr, NoEmit());
   int claimed = 0;
   if (active && loc.found < 0) {
@@ -257,6 +319,7 @@ __global__ void __launch_bounds__(DOK_TPB) k_reinsert(DevTable src, DevTable dst
       }
       kh = KeyHash{dok_llabs(u), (ll_t)h};
     }
+    active = dok_in_window(dst, kh, active);
     int outcome = -1;
     const ll_t slot = dok_find_or_claim<SB>(dst, kh, active, &outcome);
     if (active && slot >= 0) {

@@ -78,10 +78,7 @@ int dok_map_set_unique(const dok_table *t, const dok_hash_params *hp, const void
   if (n == 0) return DOK_OK;
   if (!keys || !values) return DOK_BAD_ARG;
   RowKeys rk{keys, n};
-  RowValues rv{(const char *)values};
-  DOK_DISPATCH_SB(dt, (k_set_unique<SB><<<grid_for(n), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, rk, rv, out_stored,
-                                                                                           (ll_t *)counters)));
-  return dok_check_launch();
+  return launch_set_unique(dt, dh, rk, (const char *)values, out_stored, counters, (cudaStream_t)stream);
 }
 
 int dok_map_set(const dok_table *t, const dok_hash_params *hp, const void *keys, const void *values, int64_t n,
@@ -92,15 +89,7 @@ int dok_map_set(const dok_table *t, const dok_hash_params *hp, const void *keys,
   if (n == 0) return DOK_OK;
   if (!keys || !values || !slot_scratch || !dok_has_stamps(dt) || epoch < 1 || epoch > DOK_MAX_EPOCH) return DOK_BAD_ARG;
   RowKeys rk{keys, n};
-  RowValues rv{(const char *)values};
-  cudaStream_t st = (cudaStream_t)stream;
-  if (cudaMemsetAsync(slot_scratch + n, 0, sizeof(int64_t), st) != cudaSuccess) return dok_check_launch();
-  DOK_DISPATCH_SB(dt, (k_set_claim<SB><<<grid_for(n), DOK_TPB, 0, st>>>(dt, dh, rk, rv, (ll_t *)slot_scratch, (ll_t)epoch,
-                                                                        out_stored, (ll_t *)counters)));
-  int rc = dok_check_launch();
-  if (rc != DOK_OK) return rc;
-  k_set_resolve<<<grid_for(n), DOK_TPB, 0, st>>>(dt, dh, rk, rv, (const ll_t *)slot_scratch, (ll_t)epoch);
-  return dok_check_launch();
+  return launch_set(dt, dh, rk, (const char *)values, slot_scratch, epoch, out_stored, counters, (cudaStream_t)stream);
 }
 
 int dok_map_remove(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n, uint8_t *out_removed,
@@ -111,8 +100,7 @@ int dok_map_remove(const dok_table *t, const dok_hash_params *hp, const void *ke
   if (n == 0) return DOK_OK;
   if (!keys) return DOK_BAD_ARG;
   RowKeys rk{keys, n};
-  DOK_DISPATCH_SB(dt, (k_find<SB, 1><<<grid_for(n), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, rk, out_removed, (ll_t *)counters)));
-  return dok_check_launch();
+  return launch_find<1>(dt, dh, rk, out_removed, counters, (cudaStream_t)stream);
 }
 
 int dok_map_count_exists(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
@@ -123,8 +111,7 @@ int dok_map_count_exists(const dok_table *t, const dok_hash_params *hp, const vo
   if (n == 0) return DOK_OK;
   if (!keys) return DOK_BAD_ARG;
   RowKeys rk{keys, n};
-  DOK_DISPATCH_SB(dt, (k_find<SB, 0><<<grid_for(n), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, rk, out_flags, (ll_t *)counters)));
-  return dok_check_launch();
+  return launch_find<0>(dt, dh, rk, out_flags, counters, (cudaStream_t)stream);
 }
 
 int dok_map_count_new(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
@@ -140,9 +127,73 @@ int dok_map_count_new(const dok_table *t, const dok_hash_params *hp, const void 
   int rc = dok_check_launch();
   if (rc != DOK_OK) return rc;
   RowKeys rk{keys, n};
-  DOK_DISPATCH_SB(dt, (k_count_new<SB><<<grid_for(n), DOK_TPB, 0, (cudaStream_t)stream>>>(dt, dh, rk, (ll_t *)scratch_tags,
-                                                                                          scratch_slots, (ll_t *)counters)));
-  return dok_check_launch();
+  rc = DOK_OK;
+  DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_count_new<SB><<<grid_for(n), DOK_TPB, 0, (cudaStream_t)stream>>>(
+                                                  wt, dh, rk, (ll_t *)scratch_tags, scratch_slots, (ll_t *)counters))));
+  return rc;
+}
+
+/* ---- sliced batches: rows whose count only the device knows (the inbox of a sharded table) ---------------------- */
+
+static bool sliced_keys(const void *keys, int64_t n_slices, int64_t slice_rows, const int64_t *slice_counts,
+                        const int64_t *abort_flag, RowKeys *out) {
+  if (!keys || !slice_counts || n_slices < 1 || n_slices > 65535 || slice_rows < 1) return false;
+  if (slice_rows > DOK_MAX_BATCH / n_slices) return false;
+  out->keys = keys;
+  out->n = n_slices * slice_rows;
+  out->slice_rows = slice_rows;
+  out->slice_counts = (const ll_t *)slice_counts;
+  out->abort = (const ll_t *)abort_flag;
+  return true;
+}
+
+int dok_map_get_sliced(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n_slices,
+                       int64_t slice_rows, const int64_t *slice_counts, const int64_t *abort_flag, void *out_values,
+                       uint8_t *out_found, const void *fallback, int64_t *counters, void *stream) {
+  DevHash dh;
+  DevTable dt;
+  RowKeys rk;
+  if (!prepare(t, hp, &dt, &dh) || !sliced_keys(keys, n_slices, slice_rows, slice_counts, abort_flag, &rk) || !out_values)
+    return DOK_BAD_ARG;
+  return launch_get(dt, dh, rk, out_values, out_found, fallback, counters, 0, (cudaStream_t)stream);
+}
+
+int dok_map_set_sliced(const dok_table *t, const dok_hash_params *hp, const void *keys, const void *values,
+                       int64_t n_slices, int64_t slice_rows, const int64_t *slice_counts, const int64_t *abort_flag,
+                       int64_t *slot_scratch, int64_t epoch, int assume_unique, int64_t *counters, void *stream) {
+  DevHash dh;
+  DevTable dt;
+  RowKeys rk;
+  if (!prepare(t, hp, &dt, &dh) || !sliced_keys(keys, n_slices, slice_rows, slice_counts, abort_flag, &rk) || !values)
+    return DOK_BAD_ARG;
+  if (assume_unique) return launch_set_unique(dt, dh, rk, (const char *)values, nullptr, counters, (cudaStream_t)stream);
+  if (!slot_scratch || !dok_has_stamps(dt) || epoch < 1 || epoch > DOK_MAX_EPOCH) return DOK_BAD_ARG;
+  return launch_set(dt, dh, rk, (const char *)values, slot_scratch, epoch, nullptr, counters, (cudaStream_t)stream);
+}
+
+int dok_map_remove_sliced(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n_slices,
+                          int64_t slice_rows, const int64_t *slice_counts, const int64_t *abort_flag,
+                          uint8_t *out_removed, int64_t *counters, void *stream) {
+  DevHash dh;
+  DevTable dt;
+  RowKeys rk;
+  if (!prepare(t, hp, &dt, &dh) || !sliced_keys(keys, n_slices, slice_rows, slice_counts, abort_flag, &rk)) return DOK_BAD_ARG;
+  return launch_find<1>(dt, dh, rk, out_removed, counters, (cudaStream_t)stream);
+}
+
+/* ---- passes over tables beyond the TLB's reach ----------------------------------------------------------------- */
+
+int dok_set_window_bytes(int64_t single_pass_limit, int64_t window_bytes) {
+  if (single_pass_limit < 0 || window_bytes < 128) return DOK_BAD_ARG;
+  dok_window_cfg().single_pass_limit = single_pass_limit;
+  dok_window_cfg().window_bytes = window_bytes;
+  return DOK_OK;
+}
+
+int dok_table_passes(const dok_table *t) {
+  DevTable dt;
+  if (!dok_make_table(t, &dt)) return -1;
+  return dok_window_passes(dt);
 }
 
 int64_t dok_compact_tiles(int64_t n_buckets) { return (n_buckets + DOK_COMPACT_TILE - 1) / DOK_COMPACT_TILE; }
@@ -178,8 +229,10 @@ int dok_map_reinsert(const dok_table *src, const dok_table *dst, const dok_hash_
   ll_t blocks = (st_.nb + DOK_TPB - 1) / DOK_TPB;
   if (blocks > 148 * 8) blocks = 148 * 8;            // 8 resident blocks of 256 threads per SM, grid-stride over the slots
   if (blocks < 1) blocks = 1;
-  DOK_DISPATCH_SB(dt, (k_reinsert<SB><<<(unsigned)blocks, DOK_TPB, 0, (cudaStream_t)stream>>>(st_, dt, dh, (ll_t *)counters)));
-  return dok_check_launch();
+  int rc = DOK_OK;
+  DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_reinsert<SB><<<(unsigned)blocks, DOK_TPB, 0, (cudaStream_t)stream>>>(
+                                                  st_, wt, dh, (ll_t *)counters))));
+  return rc;
 }
 
 }  // extern "C"

@@ -32,8 +32,10 @@ static long long *g_scratch_ptr[DOK_MAX_DEVICES];     // device address of dok_s
 // Device address of the static scratch on the CURRENT device, looked up once per device.
 static int static_scratch_address(long long **out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= DOK_MAX_DEVICES) {
-    dok_last_error_slot() = (int)cudaGetLastError();
+  const cudaError_t dev_err = cudaGetDevice(&dev);
+  if (dev_err != cudaSuccess || dev < 0 || dev >= DOK_MAX_DEVICES) {
+    dok_last_error_slot() = (int)(dev_err != cudaSuccess ? dev_err : cudaErrorInvalidDevice);
+    cudaGetLastError();
     return DOK_CUDA_ERROR;
   }
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
@@ -74,8 +76,9 @@ int dok_map_count_new_static(const dok_table *t, const dok_hash_params *hp, cons
   if (rc != DOK_OK) return rc;
   RowKeys rk{keys, n};
   const unsigned grid = (unsigned)((n + DOK_TPB - 1) / DOK_TPB);
-  DOK_DISPATCH_SB(dt, (k_count_new<SB><<<grid, DOK_TPB, 0, st>>>(dt, dh, rk, scratch, slots, (ll_t *)counters)));
-  return dok_check_launch();
+  rc = DOK_OK;
+  DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_count_new<SB><<<grid, DOK_TPB, 0, st>>>(wt, dh, rk, scratch, slots, (ll_t *)counters))));
+  return rc;
 }
 
 }  // extern "C"

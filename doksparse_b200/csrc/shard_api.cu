@@ -84,6 +84,12 @@ struct PartDest {
   char *keys[DOK_MAX_SHARDS];
   char *values[DOK_MAX_SHARDS];
   ll_t row0[DOK_MAX_SHARDS];
+  // Sliced exchange (slice_rows > 0): every (source, owner) pair has a slice of slice_rows rows at a FIXED place in
+  // the owner's inbox, so a source needs nobody's counts to know where its rows go; dest_index is the row's place in
+  // the asker's result region, owner * slice_rows + position.  *status != 0 (a slice overflowed somewhere, now or
+  // earlier) makes the launch a no-op: the host repeats the operation over the exact exchange.
+  ll_t slice_rows;
+  const ll_t *status;
 };
 
 // Pass 2: every row to its place.  Rows of one owner keep their batch order: inside a tile the place of a row is
@@ -112,6 +118,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
   __shared__ ll_t tile_first[DOK_MAX_SHARDS];     // rows of this owner in earlier tiles
   __shared__ ll_t local_start[DOK_MAX_SHARDS];    // start of the owner's segment in this rank's grouped order
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (dst.status != nullptr && *dst.status != 0) return;       // uniform over the grid
   for (int i = threadIdx.x; i < n_shards * CELLS; i += DOK_TPB) (&before[0][0])[i] = 0;
   if (threadIdx.x == 0) {
     ll_t padded = 0;                              // owner o's segment starts at the sum of the padded counts before it
@@ -158,7 +165,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
       const int o = owner[r];
       const ll_t e = base + r * DOK_TPB + threadIdx.x;
       const ll_t in_segment = tile_first[o] + before[o][r * WARPS + warp] + rank[r];
-      if (dest_index) dest_index[e] = local_start[o] + in_segment;
+      if (dest_index) dest_index[e] = (dst.slice_rows > 0 ? (ll_t)o * dst.slice_rows : local_start[o]) + in_segment;
       const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + in_segment;
       dok_copy_row(dst.keys[o] + row * kb, (const char *)keys.keys + e * kb, kb);
       if (values) dok_copy_row(dst.values[o] + row * vb, values + e * vb, vb);
@@ -178,7 +185,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
     const int o = owner[r];
     const ll_t e = base + r * DOK_TPB + threadIdx.x;
     const int in_tile = before[o][r * WARPS + warp] + rank[r];
-    if (dest_index) dest_index[e] = local_start[o] + tile_first[o] + in_tile;
+    if (dest_index) dest_index[e] = (dst.slice_rows > 0 ? (ll_t)o * dst.slice_rows : local_start[o]) + tile_first[o] + in_tile;
     const int pos = sorted_start[o] + in_tile;
     dok_copy_row(stage + (size_t)pos * kb, (const char *)keys.keys + e * kb, kb);
     if (values) dok_copy_row(stage_values + (size_t)pos * vb, values + e * vb, vb);
@@ -211,6 +218,61 @@ static int dok_launch_scatter(const RowKeys &rk, int kb, const char *values, int
                                                                shard_counts, dst, dest_index);
   }
   return dok_check_launch();
+}
+
+// Sliced exchange: rows per owner as above, and the sticky status word is raised when an owner's rows do not fit
+// its slice (or the caller already knows that the batch cannot go this way: force != 0).
+static __global__ void k_part_check_slices(const ll_t *shard_counts, int n_shards, ll_t slice_rows, int force, ll_t *status) {
+  const int o = threadIdx.x;
+  if ((o < n_shards && shard_counts[o] > slice_rows) || (o == 0 && force)) *status = 1;
+}
+
+// The source tells every owner how many rows it put into its slice of that owner's inbox (a store into the owner's
+// memory, like the rows themselves).  Always launched, also for an empty batch: the owner must not see the count of
+// an earlier use of the slice.
+struct CountDest { ll_t *at[DOK_MAX_SHARDS]; };
+static __global__ void k_part_publish_counts(const ll_t *shard_counts, int n_shards, const __grid_constant__ CountDest dst,
+                                             const ll_t *status) {
+  const int o = threadIdx.x;
+  if (o < n_shards && dst.at[o] != nullptr) *dst.at[o] = (status != nullptr && *status != 0) ? 0 : shard_counts[o];
+}
+
+// The token of one operation, before and after its all-reduce(MAX) over the ranks: {sticky status, signature,
+// -signature} goes in; what comes out tells every rank, on the device, whether any rank overflowed (now or earlier)
+// and whether all ranks submitted the same operation (max(signature) == -max(-signature)).  Either makes token[0]
+// non-zero, which the apply kernels read as "do nothing", and raises this rank's sticky status.
+static __global__ void k_token_prepare(const ll_t *status, ll_t signature, ll_t *token) {
+  token[0] = *status;
+  token[1] = signature;
+  token[2] = -signature;
+}
+static __global__ void k_token_finish(ll_t *token, ll_t *status) {
+  if (token[1] + token[2] != 0 && token[0] == 0) token[0] = 1;
+  if (token[0] > *status) *status = token[0];
+}
+
+// min(*count, max_rows) rows of two row arrays (the answers of a lookup: values and flags) to another place, usually
+// the asker's memory on another GPU: consecutive threads move consecutive 16-byte pieces, so the stores cross NVLink as
+// full packets.  The row count is read on the device; both sources and destinations are 16-byte aligned.
+static __global__ void __launch_bounds__(256) k_copy_counted(char *__restrict__ dst_a, const char *__restrict__ src_a, int rb_a,
+                                                             char *__restrict__ dst_b, const char *__restrict__ src_b, int rb_b,
+                                                             ll_t max_rows, const ll_t *count, const ll_t *abort) {
+  if (abort != nullptr && *abort != 0) return;
+  ll_t rows = *count;
+  if (rows > max_rows) rows = max_rows;
+  const ll_t stride = (ll_t)gridDim.x * blockDim.x;
+  const ll_t first = (ll_t)blockIdx.x * blockDim.x + threadIdx.x;
+#pragma unroll
+  for (int which = 0; which < 2; which++) {
+    char *dst = which ? dst_b : dst_a;
+    const char *src = which ? src_b : src_a;
+    const ll_t bytes = rows * (which ? rb_b : rb_a);
+    if (dst == nullptr || bytes == 0) continue;
+    const ll_t whole = bytes >> 4;
+    for (ll_t i = first; i < whole; i += stride) ((uint4 *)dst)[i] = ((const uint4 *)src)[i];
+    const ll_t tail = whole << 4;
+    if (first < bytes - tail) dst[tail + first] = src[tail + first];
+  }
 }
 
 static __global__ void __launch_bounds__(DOK_TPB) k_unpermute(const char *__restrict__ grouped_values,
@@ -286,6 +348,71 @@ int dok_shard_partition_scatter_peer(const void *keys, int key_bytes, const void
   RowKeys rk{keys, n};
   return dok_launch_scatter(rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, (const ll_t *)tile_offsets,
                             (const ll_t *)shard_counts, dst, (ll_t *)dest_index, (cudaStream_t)stream);
+}
+
+int dok_shard_partition_check_slices(const int64_t *shard_counts, int n_shards, int64_t slice_rows, int force,
+                                     int64_t *status, void *stream) {
+  if (!shard_counts || !status || n_shards < 1 || n_shards > DOK_MAX_SHARDS || slice_rows < 1) return DOK_BAD_ARG;
+  k_part_check_slices<<<1, DOK_MAX_SHARDS, 0, (cudaStream_t)stream>>>((const ll_t *)shard_counts, n_shards, slice_rows, force,
+                                                                      (ll_t *)status);
+  return dok_check_launch();
+}
+
+int dok_shard_partition_scatter_sliced(const void *keys, int key_bytes, const void *values, int value_bytes, int64_t n,
+                                       int n_shards, const uint8_t *owners, const int64_t *tile_offsets,
+                                       const int64_t *shard_counts, void *const *slice_keys, void *const *slice_values,
+                                       int64_t *const *count_dst, int64_t slice_rows, const int64_t *status,
+                                       int64_t *dest_index, void *stream) {
+  if (n < 0 || n > DOK_MAX_BATCH || n_shards < 1 || n_shards > DOK_MAX_SHARDS || slice_rows < 1) return DOK_BAD_ARG;
+  if (!shard_counts || !slice_keys || !count_dst || !status || key_bytes < 1) return DOK_BAD_ARG;
+  if (values && (!slice_values || value_bytes < 1 || value_bytes > DOK_MAX_VALUE_BYTES)) return DOK_BAD_ARG;
+  if (n > 0 && (!keys || !owners || !tile_offsets)) return DOK_BAD_ARG;
+  PartDest dst;
+  CountDest cd;
+  memset(&dst, 0, sizeof(dst));
+  memset(&cd, 0, sizeof(cd));
+  for (int o = 0; o < n_shards; o++) {
+    if (!slice_keys[o] || !count_dst[o] || (values && !slice_values[o])) return DOK_BAD_ARG;
+    dst.keys[o] = (char *)slice_keys[o];
+    dst.values[o] = values ? (char *)slice_values[o] : nullptr;
+    dst.row0[o] = 0;
+    cd.at[o] = (ll_t *)count_dst[o];
+  }
+  dst.slice_rows = slice_rows;
+  dst.status = (const ll_t *)status;
+  cudaStream_t st = (cudaStream_t)stream;
+  k_part_publish_counts<<<1, DOK_MAX_SHARDS, 0, st>>>((const ll_t *)shard_counts, n_shards, cd, (const ll_t *)status);
+  int rc = dok_check_launch();
+  if (rc != DOK_OK || n == 0) return rc;
+  RowKeys rk{keys, n};
+  return dok_launch_scatter(rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, (const ll_t *)tile_offsets,
+                            (const ll_t *)shard_counts, dst, (ll_t *)dest_index, st);
+}
+
+int dok_shard_token_prepare(const int64_t *status, int64_t signature, int64_t *token, void *stream) {
+  if (!status || !token) return DOK_BAD_ARG;
+  k_token_prepare<<<1, 1, 0, (cudaStream_t)stream>>>((const ll_t *)status, (ll_t)signature, (ll_t *)token);
+  return dok_check_launch();
+}
+
+int dok_shard_token_finish(int64_t *token, int64_t *status, void *stream) {
+  if (!status || !token) return DOK_BAD_ARG;
+  k_token_finish<<<1, 1, 0, (cudaStream_t)stream>>>((ll_t *)token, (ll_t *)status);
+  return dok_check_launch();
+}
+
+int dok_copy_counted(void *dst_a, const void *src_a, int row_bytes_a, void *dst_b, const void *src_b, int row_bytes_b,
+                     int64_t max_rows, const int64_t *count, const int64_t *abort_flag, void *stream) {
+  if (!count || max_rows < 0 || (dst_a && (!src_a || row_bytes_a < 1)) || (dst_b && (!src_b || row_bytes_b < 1))) return DOK_BAD_ARG;
+  if ((((uintptr_t)dst_a | (uintptr_t)src_a | (uintptr_t)dst_b | (uintptr_t)src_b) & 15) != 0) return DOK_BAD_ARG;
+  if (max_rows == 0 || (!dst_a && !dst_b)) return DOK_OK;
+  const ll_t pieces = (max_rows * (ll_t)(row_bytes_a > row_bytes_b ? row_bytes_a : row_bytes_b) + 15) / 16;
+  ll_t blocks = (pieces + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  k_copy_counted<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((char *)dst_a, (const char *)src_a, row_bytes_a, (char *)dst_b,
+                                                                     (const char *)src_b, row_bytes_b, max_rows,
+                                                                     (const ll_t *)count, (const ll_t *)abort_flag);
+  return dok_check_launch();
 }
 
 /* ---- exchange arena: device memory that the other ranks of the node map into their address space ------------ */

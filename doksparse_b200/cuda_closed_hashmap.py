@@ -67,6 +67,10 @@ class CudaClosedHashmap:
         self._alpha1, self._alpha2 = as_param(alpha1), as_param(alpha2)
         self._beta1, self._beta2 = as_param(beta1), as_param(beta2)
         self._n_elements = torch.zeros(size=(), device=self.device, dtype=torch.long)
+        # rows that a set could not store because the table was full (the reference drops them silently,
+        # closed_hashmap_impl_class.cu:426; here they are counted on the device and reported at the next point where
+        # the host synchronises anyway: n_elements, state_dict, the exact-count path of set)
+        self._n_failed = torch.zeros(size=(), device=self.device, dtype=torch.long)
         self._rehash_factor = rehash_factor
         self._rehash_threshold = rehash_threshold
         # Tombstone-aware maintenance (no counterpart in the reference, whose rehash looks at live items only,
@@ -399,6 +403,7 @@ class CudaClosedHashmap:
         else:
             new._uuid_only = cp(self._uuid_only)
         new._n_elements = cp(self._n_elements)
+        new._n_failed = cp(self._n_failed)
         if deepclone:
             # in-slot stamps were copied with the slots: continue their epochs; a separate array is copied too
             new._shared = {"stamp": None if self._shared["stamp"] is None else self._shared["stamp"].clone(),
@@ -410,10 +415,19 @@ class CudaClosedHashmap:
     # ------------------------------------------------------------------ sizes
     @property
     def n_elements(self):
-        n = int(self._n_elements.item())
+        n, failed = torch.stack([self._n_elements, self._n_failed]).tolist()      # one synchronisation for both
         self._shared["snapshots"].clear()
         self._shared["bound"] = n
+        if failed:
+            self._n_failed.zero_()
+            raise L.DokError(f"{failed} rows of earlier set calls were not stored: the table was full "
+                             f"({self._n_buckets} buckets); rehash() to a larger size and set them again")
         return n
+
+    @property
+    def last_set_failed(self):
+        """Rows that set calls could not store so far (table full); reading it synchronises."""
+        return int(self._n_failed.item())
 
     @property
     def n_buckets(self):
@@ -563,9 +577,7 @@ class CudaClosedHashmap:
         if fast:
             # whatever the number of new keys is, the reference would not rehash: insert and count on the device
             cnt = self._launch_set(new_keys, new_values, assume_unique)
-            self._n_elements += cnt[L.CNT_CLAIMED_EMPTY] + cnt[L.CNT_REUSED_REMOVED]
-            self._n_tombstones -= cnt[L.CNT_REUSED_REMOVED]
-            self._after_mutation(n)
+            self._account_set(cnt, n)
             return
         n_new = self._count_new(new_keys)
         n_elements = self.n_elements
@@ -573,9 +585,90 @@ class CudaClosedHashmap:
             self.rehash(int((n_elements + n_new) * self._rehash_factor))
         cnt = self._launch_set(new_keys, new_values, assume_unique)
         self._n_tombstones -= cnt[L.CNT_REUSED_REMOVED]
+        self._n_failed += cnt[L.CNT_FAILED]
         self._n_elements += n_new
         self._shared["snapshots"].clear()
         self._shared["bound"] = n_elements + n_new
+
+    def _account_set(self, cnt, rows):
+        """Device-side bookkeeping after a set launch that cannot have triggered a rehash."""
+        self._n_elements += cnt[L.CNT_CLAIMED_EMPTY] + cnt[L.CNT_REUSED_REMOVED]
+        self._n_tombstones -= cnt[L.CNT_REUSED_REMOVED]
+        self._n_failed += cnt[L.CNT_FAILED]
+        self._after_mutation(rows)
+
+    # ------------------------------------------------------------------ sliced batches (the inbox of a sharded map)
+    # keys / values / outputs hold n_slices * slice_rows rows; only the first counts[s] rows of slice s are in use, and
+    # the counts (device int64[n_slices]) are read by the kernels, so nothing here waits for them.  `abort` (device
+    # int64[1] or None): non-zero when the kernels run = do nothing.
+    def _sliced_check(self, keys, n_slices, slice_rows, counts):
+        assert self._slots is not None, "store something first"
+        assert keys.dtype == self._key_dtype and keys.device == self.device and keys.is_contiguous()
+        assert keys.shape == (n_slices * slice_rows,) + tuple(self._key_shape)
+        assert counts.dtype == torch.long and counts.shape == (n_slices,) and counts.is_contiguous()
+
+    def get_sliced(self, keys, n_slices, slice_rows, counts, abort, fallback_value, values, is_found):
+        self._sliced_check(keys, n_slices, slice_rows, counts)
+        fb, _keep = self._fallback_ptr(fallback_value)
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_map_get_sliced(self._c_table(), self._c_hash(), L.ptr(keys), n_slices, slice_rows,
+                                               L.ptr(counts), L.ptr(abort), L.ptr(values), L.ptr(is_found), fb, None,
+                                               L.stream_ptr(self.device)), "dok_map_get_sliced")
+
+    def remove_sliced(self, keys, n_slices, slice_rows, counts, abort, is_removed):
+        self._sliced_check(keys, n_slices, slice_rows, counts)
+        cnt = self._counters()
+        with torch.cuda.device(self.device):
+            L.check(L.lib().dok_map_remove_sliced(self._c_table(), self._c_hash(), L.ptr(keys), n_slices, slice_rows,
+                                                  L.ptr(counts), L.ptr(abort), L.ptr(is_removed), L.ptr(cnt),
+                                                  L.stream_ptr(self.device)), "dok_map_remove_sliced")
+        self._n_elements -= cnt[L.CNT_HITS]
+        self._n_tombstones += cnt[L.CNT_HITS]
+        self._tombstone_host_bound += n_slices * slice_rows
+        self._after_mutation(0)
+
+    def set_sliced(self, keys, values, n_slices, slice_rows, counts, abort, assume_unique=False):
+        """Insert-or-assign of a sliced batch.  As long as the table cannot reach its rehash threshold even if every
+        row of every slice were new, everything stays on the device.  Otherwise the counts are read (a synchronisation
+        of this rank only) and the slices go through `set` one after the other, which may rehash."""
+        self._sliced_check(keys, n_slices, slice_rows, counts)
+        assert values.dtype == self._value_dtype and values.is_contiguous()
+        assert values.shape == (n_slices * slice_rows,) + tuple(self._value_shape)
+        self._materialise_parameters()
+        rows = n_slices * slice_rows
+        limit = int(self._rehash_threshold * self.n_buckets)
+        fast = self._element_bound() + rows <= limit
+        if not fast:
+            torch.cuda.current_stream(self.device).synchronize()
+            fast = self.n_elements + rows <= limit
+        if fast:
+            cnt = self._counters()
+            with torch.cuda.device(self.device):
+                epoch, scratch = 0, None
+                if not assume_unique:
+                    epoch = self._next_epoch()
+                    scratch = torch.empty(rows + 1, device=self.device, dtype=torch.long)
+                L.check(L.lib().dok_map_set_sliced(self._c_table(), self._c_hash(), L.ptr(keys), L.ptr(values), n_slices,
+                                                   slice_rows, L.ptr(counts), L.ptr(abort), L.ptr(scratch), epoch,
+                                                   int(bool(assume_unique)), L.ptr(cnt), L.stream_ptr(self.device)),
+                        "dok_map_set_sliced")
+            self._account_set(cnt, rows)
+            return
+        if abort is not None and int(abort.item()) != 0:
+            return
+        for s, c in enumerate(counts.tolist()):
+            if c:
+                self.set(keys[s * slice_rows:s * slice_rows + c], values[s * slice_rows:s * slice_rows + c],
+                         assume_unique=assume_unique)
+
+    def _fallback_ptr(self, fallback_value):
+        """-> (host pointer for the C ABI or None, the host tensor that must stay alive for the call)"""
+        if fallback_value is None:
+            return None, None
+        if not isinstance(fallback_value, torch.Tensor):
+            fallback_value = torch.tensor(fallback_value, dtype=self._value_dtype)
+        host = torch.broadcast_to(fallback_value.to(dtype=self._value_dtype, device="cpu"), self.value_shape).contiguous()
+        return ctypes.c_void_p(host.data_ptr()), host
 
     # ------------------------------------------------------------------ get
     def get(self, keys, fallback_value=None, values=None, is_found=None):
@@ -589,12 +682,7 @@ class CudaClosedHashmap:
         assert keys.dtype == self._key_dtype
         assert keys.device == self.device
         assert keys.shape[1:] == self.key_shape
-        fb = None
-        if fallback_value is not None:
-            if not isinstance(fallback_value, torch.Tensor):
-                fallback_value = torch.tensor(fallback_value, dtype=self._value_dtype)
-            fb_host = torch.broadcast_to(fallback_value.to(dtype=self._value_dtype, device="cpu"), self.value_shape).contiguous()
-            fb = ctypes.c_void_p(fb_host.data_ptr())
+        fb, _keep = self._fallback_ptr(fallback_value)
         keys = keys.contiguous()
         n = keys.shape[0]
         if values is None:

@@ -45,7 +45,7 @@ class CudaShardOps:
         self._routing = {k: torch.as_tensor(v).cpu().tolist() for k, v in params.items()}
         self._hp = None
         self._pinned = None
-        self._peer = None
+        self._sx = None
         self._copy_stream = None
         self._in_flight = []
 
@@ -64,8 +64,8 @@ class CudaShardOps:
             self._hp = hp
         return ctypes.byref(self._hp)
 
-    # ------------------------------------------------------------------ peer exchange (NVLink, no exchange pass)
-    supports_peer = True
+    # ------------------------------------------------------------------ sliced exchange (NVLink, no host in the loop)
+    supports_sliced = True
 
     class _RawDeviceBytes:
         """Lets torch wrap device memory it did not allocate (the exchange arena, a peer's mapping of its arena)."""
@@ -73,25 +73,63 @@ class CudaShardOps:
         def __init__(self, ptr, nbytes):
             self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
 
-    def peer_setup(self, group, world, rank, capacity_rows, key_row, value_row):
-        """Collective.  Allocates this rank's exchange arena, maps every peer's, and returns True when all ranks
-        succeeded (otherwise the arena is dropped everywhere and the NCCL exchange stays in use).
-        key_row / value_row = (row shape, dtype).  Arena = two generations (alternating per batch) of
-        {inbox keys | inbox values | result values | result flags}, each for capacity_rows rows."""
-        lib = L.lib()
-        self._peer = None
+    @staticmethod
+    def sliced_geometry(world, capacity_rows, key_row, value_row, slack_sigmas=8.0):
+        """Arena layout for batches of up to `capacity_rows` rows per rank.  A slice holds the rows one source sends
+        to one owner: capacity / world on average; with a uniform owner hash the count is binomial, so a slack of a
+        few standard deviations (plus a constant for tiny batches) makes an overflow a non-event, and a batch that
+        overflows all the same (skewed keys) is repeated over the exact exchange.  One generation =
+        {inbox keys | inbox values | inbox counts | result values | result flags}, each for world slices; inbox slice s
+        holds what source rank s sent here, result slice o what owner rank o answered."""
         (kshape, kdtype), (vshape, vdtype) = key_row, value_row
         kb = int(np.prod(kshape)) * torch.empty((), dtype=kdtype).element_size()
         vb = int(np.prod(vshape)) * torch.empty((), dtype=vdtype).element_size()
-        cap = int(capacity_rows)
+        cap = max(int(capacity_rows), 1)
+        mean = cap / world
+        rows = int(np.ceil(mean + slack_sigmas * np.sqrt(mean) + 64))
+        rows = min(rows, cap)
+        rows = (rows + 255) // 256 * 256                   # slices start 16-byte aligned whatever the row width
         up = lambda x: (x + 255) // 256 * 256
-        sizes = [up(cap * kb), up(cap * vb), up(cap * vb), up(cap)]
-        gen_bytes = sum(sizes)
-        offs = [sum(sizes[:i]) for i in range(4)]
-        ok, base, handle = 1, ctypes.c_void_p(), (ctypes.c_uint8 * 64)()
+        sizes = [up(world * rows * kb), up(world * rows * vb), up(world * 8), up(world * rows * vb), up(world * rows)]
+        return dict(world=world, cap=cap, slice_rows=rows, kb=kb, vb=vb, kshape=tuple(kshape), kdtype=kdtype,
+                    vshape=tuple(vshape), vdtype=vdtype, sizes=sizes, offs=[sum(sizes[:i]) for i in range(5)],
+                    gen_bytes=sum(sizes))
+
+    def sliced_alloc(self, geometry):
+        """This rank's arena (two generations); returns its base address or None."""
+        base = ctypes.c_void_p()
         with torch.cuda.device(self.device):
-            if lib.dok_peer_alloc(2 * gen_bytes, ctypes.byref(base)) != 0 or lib.dok_peer_export(base, handle) != 0:
-                ok = 0
+            if L.lib().dok_peer_alloc(2 * geometry["gen_bytes"], ctypes.byref(base)) != 0:
+                return None
+        return base.value
+
+    def sliced_attach(self, geometry, bases, rank, group=None, group_apply=None, own_base=None, ipc=True):
+        """`bases[r]` = address of rank r's arena as THIS process sees it (its own allocation, a CUDA IPC mapping of a
+        peer's, or -- when several ranks are emulated in one process -- another local allocation)."""
+        g = dict(geometry)
+        w, rows = g["world"], g["slice_rows"]
+        views = [torch.as_tensor(self._RawDeviceBytes(b, 2 * g["gen_bytes"]), device=self.device) for b in bases]
+        g.update(bases=list(bases), views=views, rank=rank, group=group, group_apply=group_apply, own_base=own_base, ipc=ipc,
+                 status=torch.zeros(1, device=self.device, dtype=torch.long),
+                 token_apply=torch.zeros(1, device=self.device),
+                 answer_values=torch.empty((w * rows,) + g["vshape"], device=self.device, dtype=g["vdtype"]),
+                 answer_flags=torch.empty(w * rows, device=self.device, dtype=torch.bool))
+        for gen in range(2):                                   # counts start at zero
+            self._sx = g
+            self._region(rank, gen, 2).zero_()
+        self._sx = g
+
+    def sliced_setup(self, group, world, rank, capacity_rows, key_row, value_row):
+        """Collective.  Allocates this rank's arena, maps every peer's (CUDA IPC) and returns True when all ranks
+        succeeded; otherwise everything is released again and the exact exchange stays in use."""
+        lib = L.lib()
+        self._sx = None
+        geometry = self.sliced_geometry(world, capacity_rows, key_row, value_row)
+        base = self.sliced_alloc(geometry)
+        ok, handle = int(base is not None), (ctypes.c_uint8 * 64)()
+        if ok:
+            with torch.cuda.device(self.device):
+                ok = int(lib.dok_peer_export(ctypes.c_void_p(base), handle) == 0)
         handles = [None] * world
         dist.all_gather_object(handles, (ok, bytes(handle)), group=group)
         ok = min(h[0] for h in handles)
@@ -100,7 +138,7 @@ class CudaShardOps:
             with torch.cuda.device(self.device):
                 for r in range(world):
                     if r == rank:
-                        bases[r] = base.value
+                        bases[r] = base
                         continue
                     p = ctypes.c_void_p()
                     buf = (ctypes.c_uint8 * 64).from_buffer_copy(handles[r][1])
@@ -115,56 +153,155 @@ class CudaShardOps:
                 for r in range(world):
                     if bases[r] is not None and r != rank:
                         lib.dok_peer_close(ctypes.c_void_p(bases[r]))
-                if base.value:
-                    lib.dok_peer_free(base)
+                if base:
+                    lib.dok_peer_free(ctypes.c_void_p(base))
             return False
-        views = [torch.as_tensor(self._RawDeviceBytes(bases[r], 2 * gen_bytes), device=self.device) for r in range(world)]
         # a second communicator for the fences of the apply stage: collectives of one communicator run in issue order,
-        # and a fence that waits for table work must not hold up the count gather of the next operation's send stage
-        group_apply = None
-        if group is None or group is dist.group.WORLD:
-            group_apply = dist.new_group(backend="nccl")
-        self._peer = dict(group_apply=group_apply, world=world, rank=rank, cap=cap, kb=kb, vb=vb, kshape=tuple(kshape), kdtype=kdtype,
-                          vshape=tuple(vshape), vdtype=vdtype, gen_bytes=gen_bytes, offs=offs, bases=bases, views=views,
-                          own_base=base, token=torch.zeros(1, device=self.device),
-                          token_apply=torch.zeros(1, device=self.device), group=group)
+        # and a fence that waits for table work must not hold up the fence of the next operation's send stage
+        group_apply = dist.new_group(backend="nccl") if (group is None or group is dist.group.WORLD) else None
+        self.sliced_attach(geometry, bases, rank, group=group, group_apply=group_apply, own_base=base)
         return True
 
-    def peer_close(self):
+    def sliced_close(self):
         """Collective in effect: call it on every rank, after all of them have finished using the exchange."""
-        p, self._peer = getattr(self, "_peer", None), None
-        if not p:
+        p, self._sx = getattr(self, "_sx", None), None
+        if not p or p.get("own_base") is None:
             return
         lib = L.lib()
         torch.cuda.synchronize(self.device)
         with torch.cuda.device(self.device):
             for r in range(p["world"]):
-                if r != p["rank"]:
+                if r != p["rank"] and p["ipc"]:
                     lib.dok_peer_close(ctypes.c_void_p(p["bases"][r]))
-            lib.dok_peer_free(p["own_base"])
+            lib.dok_peer_free(ctypes.c_void_p(p["own_base"]))
 
-    def _peer_region(self, rank, generation, which, rows=None, row0=0):
-        """Typed view of region `which` (0 inbox keys, 1 inbox values, 2 result values, 3 result flags) of `rank`'s
-        arena, generation 0 / 1, rows [row0, row0 + rows)."""
-        p = self._peer
-        rows = p["cap"] - row0 if rows is None else rows
-        width, shape, dtype = [(p["kb"], p["kshape"], p["kdtype"]), (p["vb"], p["vshape"], p["vdtype"]),
+    def _region_ptr(self, rank, generation, which, row0=0):
+        p = self._sx
+        width = [p["kb"], p["vb"], 8, p["vb"], 1][which]
+        return p["bases"][rank] + generation * p["gen_bytes"] + p["offs"][which] + row0 * width
+
+    def _region(self, rank, generation, which, rows=None, row0=0):
+        """Typed view of region `which` (0 inbox keys, 1 inbox values, 2 inbox counts, 3 result values, 4 result
+        flags) of `rank`'s arena, generation 0 / 1, rows [row0, row0 + rows)."""
+        p = self._sx
+        total = p["world"] if which == 2 else p["world"] * p["slice_rows"]
+        rows = total - row0 if rows is None else rows
+        width, shape, dtype = [(p["kb"], p["kshape"], p["kdtype"]), (p["vb"], p["vshape"], p["vdtype"]), (8, (), torch.long),
                                (p["vb"], p["vshape"], p["vdtype"]), (1, (), torch.bool)][which]
         lo = generation * p["gen_bytes"] + p["offs"][which] + row0 * width
         flat = p["views"][rank][lo:lo + rows * width]
         return flat.view(dtype).view((rows,) + tuple(shape))
 
-    def peer_fence(self, apply_side=False):
-        """Every rank's earlier work on its stream (stores into peers' arenas included) is complete before any rank's
-        later work starts: a one-element all-reduce, ordered on the stream, not blocking the host.  `apply_side`
-        fences travel on the second communicator when there is one."""
-        p = self._peer
-        group = p["group_apply"] if (apply_side and p["group_apply"] is not None) else p["group"]
-        token = p["token_apply"] if apply_side else p["token"]
-        dist.all_reduce(token, group=group)
+    def sliced_send(self, keys, values, generation, want_dest, force_overflow=False):
+        """SEND stage: owner of every row, then every row into its owner's inbox slice for this rank and this rank's
+        row counts into the owners' count words -- plain stores, over NVLink for other ranks' memory.  A slice that
+        would overflow raises the sticky status word instead, and nothing is stored.  -> dest_index (or None)."""
+        lib = L.lib()
+        p = self._sx
+        w, rows, r = p["world"], p["slice_rows"], p["rank"]
+        n = keys.shape[0]
+        owners, offsets, counts = self.partition_count(keys, w)
+        arr_p = ctypes.c_void_p * w
+        slice_keys = arr_p(*[self._region_ptr(o, generation, 0, r * rows) for o in range(w)])
+        slice_values = arr_p(*[self._region_ptr(o, generation, 1, r * rows) for o in range(w)])
+        count_dst = arr_p(*[self._region_ptr(o, generation, 2, r) for o in range(w)])
+        dest = torch.empty(n, device=self.device, dtype=torch.long) if want_dest else None
+        with torch.cuda.device(self.device):
+            st = L.stream_ptr(self.device)
+            L.check(lib.dok_shard_partition_check_slices(L.ptr(counts), w, rows, int(bool(force_overflow)),
+                                                         L.ptr(p["status"]), st), "dok_shard_partition_check_slices")
+            L.check(lib.dok_shard_partition_scatter_sliced(
+                L.ptr(keys), p["kb"], L.ptr(values), 0 if values is None else p["vb"], n, w, L.ptr(owners), L.ptr(offsets),
+                L.ptr(counts), slice_keys, slice_values if values is not None else None, count_dst, rows,
+                L.ptr(p["status"]), L.ptr(dest), st), "dok_shard_partition_scatter_sliced")
+        return dest
+
+    def sliced_fence(self, token, signature=0):
+        """Closes a SEND stage.  token (device int64[3]) becomes the maximum over all ranks of {sticky status,
+        signature, -signature}: a non-zero token[0] tells every rank, on the device, that this operation (or an earlier
+        one) overflowed somewhere, or that the ranks did not submit the same operation (token[1] != -token[2]), and
+        must not be applied.  Being a collective ordered on the stream, it also orders every rank's stores before any
+        rank's reads.  The host does not wait."""
+        p = self._sx
+        lib = L.lib()
+        with torch.cuda.device(self.device):
+            L.check(lib.dok_shard_token_prepare(L.ptr(p["status"]), int(signature), L.ptr(token), L.stream_ptr(self.device)),
+                    "dok_shard_token_prepare")
+            if p["world"] > 1 and p["group"] is not False:
+                dist.all_reduce(token, op=dist.ReduceOp.MAX, group=p["group"])
+            L.check(lib.dok_shard_token_finish(L.ptr(token), L.ptr(p["status"]), L.stream_ptr(self.device)),
+                    "dok_shard_token_finish")
+
+    def sliced_apply_fence(self):
+        """Closes the answer deliveries of an APPLY stage (second communicator when there is one)."""
+        p = self._sx
+        if p["world"] > 1 and p["group"] is not False:
+            dist.all_reduce(p["token_apply"], group=p["group_apply"] if p["group_apply"] is not None else p["group"])
+
+    def sliced_reset_status(self):
+        self._sx["status"].zero_()
 
     def can_pipeline(self):
-        return self._peer is not None and self._peer["group_apply"] is not None
+        return getattr(self, "_sx", None) is not None
+
+    def sliced_apply_set(self, generation, abort, assume_unique):
+        p = self._sx
+        self.local.set_sliced(self._region(p["rank"], generation, 0), self._region(p["rank"], generation, 1), p["world"],
+                              p["slice_rows"], self._region(p["rank"], generation, 2), abort, assume_unique)
+
+    def sliced_apply_lookup(self, generation, abort, with_values, fallback_value):
+        """get (with_values) or remove of what this rank received, source by source, answers into the askers' result
+        regions: this rank's own rows directly, another rank's rows into a local buffer that a copy kernel on a side
+        stream carries over NVLink while the next source's rows are probed (row-sized stores from the probing kernel
+        itself use the link far worse).  Lookups commute, so the other ranks' rows go first; removals go in rank order,
+        because among equal keys of different ranks the earlier rank reports the removal."""
+        lib = L.lib()
+        p = self._sx
+        w, rows, r = p["world"], p["slice_rows"], p["rank"]
+        counts = self._region(r, generation, 2)
+        order = ([s for s in range(w) if s != r] + [r]) if with_values else list(range(w))
+        for s in order:
+            keys = self._region(r, generation, 0, rows=rows, row0=s * rows)
+            if s == r:
+                out_values = self._region(r, generation, 3, rows=rows, row0=r * rows) if with_values else None
+                out_flags = self._region(r, generation, 4, rows=rows, row0=r * rows)
+            else:
+                out_values = p["answer_values"][s * rows:(s + 1) * rows] if with_values else None
+                out_flags = p["answer_flags"][s * rows:(s + 1) * rows]
+            if with_values:
+                self.local.get_sliced(keys, 1, rows, counts[s:s + 1], abort, fallback_value, out_values, out_flags)
+            else:
+                self.local.remove_sliced(keys, 1, rows, counts[s:s + 1], abort, out_flags)
+            if s == r:
+                continue
+            if self._copy_stream is None:
+                self._copy_stream = torch.cuda.Stream(device=self.device)
+            answered = torch.cuda.Event()
+            answered.record()
+            with torch.cuda.stream(self._copy_stream):
+                self._copy_stream.wait_event(answered)
+                with torch.cuda.device(self.device):
+                    L.check(lib.dok_copy_counted(
+                        ctypes.c_void_p(self._region_ptr(s, generation, 3, r * rows)) if with_values else None,
+                        L.ptr(out_values), p["vb"], ctypes.c_void_p(self._region_ptr(s, generation, 4, r * rows)),
+                        L.ptr(out_flags), 1, rows, L.ptr(counts[s:s + 1]), L.ptr(abort), L.stream_ptr(self.device)),
+                        "dok_copy_counted")
+            self._in_flight.append(True)
+        self.answers_delivered()
+
+    def sliced_results(self, generation, dest, with_values):
+        """Inverse permutation of this rank's result region into the caller's row order."""
+        p = self._sx
+        values = self._region(p["rank"], generation, 3) if with_values else None
+        flags = self._region(p["rank"], generation, 4).view(torch.uint8)
+        out_values, out_flags = self.unpermute(values, flags, dest)
+        return out_values, out_flags.view(torch.bool)
+
+    def ensure_allocated(self, key_row, value_row):
+        """The local shard gets its storage at the first collective set, also on a rank that receives no row, so that
+        lookups can run on every rank from then on."""
+        if self.local._slots is None:
+            self.local._allocate(key_row[0], key_row[1], value_row[0], value_row[1])
 
     def partition_count(self, keys, world):
         """First pass of the partition -> (owners, tile offsets, counts[2 * world] on the device)."""
@@ -174,30 +311,11 @@ class CudaShardOps:
             tiles = lib.dok_partition_tiles(n)
             offsets = torch.empty(world * tiles + 1, device=self.device, dtype=torch.long)
             counts = torch.empty(2 * world, device=self.device, dtype=torch.long)
-            owners = torch.empty(n, device=self.device, dtype=torch.uint8)
+            owners = torch.empty(max(n, 1), device=self.device, dtype=torch.uint8)
             L.check(lib.dok_shard_partition_count(self._routing_hash(keys), L.ptr(keys), n, world, L.ptr(owners),
                                                   L.ptr(offsets), L.ptr(counts), L.stream_ptr(self.device)),
                     "dok_shard_partition_count")
         return owners, offsets, counts
-
-    def scatter_to_peers(self, keys, values, world, owners, offsets, counts, generation, row0, want_dest):
-        """Second pass with the owners' inboxes as destinations; row0[o] = first row of this rank's segment there."""
-        lib = L.lib()
-        p = self._peer
-        n = keys.shape[0]
-        gen = generation * p["gen_bytes"]
-        arr_p = ctypes.c_void_p * world
-        peer_keys = arr_p(*[p["bases"][o] + gen + p["offs"][0] for o in range(world)])
-        peer_values = arr_p(*[p["bases"][o] + gen + p["offs"][1] for o in range(world)])
-        rows = (ctypes.c_int64 * world)(*[int(r) for r in row0])
-        dest = torch.empty(n, device=self.device, dtype=torch.long) if want_dest else None
-        vb = 0 if values is None else p["vb"]
-        with torch.cuda.device(self.device):
-            L.check(lib.dok_shard_partition_scatter_peer(L.ptr(keys), p["kb"], L.ptr(values), vb, n, world, L.ptr(owners),
-                                                         L.ptr(offsets), L.ptr(counts), peer_keys,
-                                                         peer_values if values is not None else None, rows, L.ptr(dest),
-                                                         L.stream_ptr(self.device)), "dok_shard_partition_scatter_peer")
-        return dest
 
     def partition(self, keys, values, world, want_dest=True):
         """-> (grouped_keys, grouped_values or None, dest_index, counts[2, world] on the device): rows per owner, and
@@ -274,28 +392,6 @@ class CudaShardOps:
                 flags[start:start + rows] = self.local.remove_rows(keys[start:start + rows])
         return flags
 
-    def local_answer(self, keys, values, flags, fallback_value, remote):
-        """get (values given) or remove (values None) of one source's rows, answers delivered into `values` /
-        `flags`.  For another rank's rows (`remote`) those are views of the asker's memory: the kernel then answers
-        into local buffers and a bulk copy on a side stream carries them over NVLink while the next source's rows are
-        being probed -- row-sized stores from the probing kernel itself use the link far worse."""
-        if not remote:
-            self._answer(keys, values, flags, fallback_value)
-            return
-        local_values = None if values is None else torch.empty_like(values)
-        local_flags = torch.empty_like(flags)
-        self._answer(keys, local_values, local_flags, fallback_value)
-        if self._copy_stream is None:
-            self._copy_stream = torch.cuda.Stream(device=self.device)
-        answered = torch.cuda.Event()
-        answered.record()
-        with torch.cuda.stream(self._copy_stream):
-            self._copy_stream.wait_event(answered)
-            if values is not None:
-                values.copy_(local_values, non_blocking=True)
-            flags.copy_(local_flags, non_blocking=True)
-        self._in_flight.append((local_values, local_flags))
-
     def answers_delivered(self):
         """The current stream waits for the bulk copies of local_answer; their source buffers may then be reused."""
         if self._in_flight:
@@ -303,16 +399,6 @@ class CudaShardOps:
             done.record(self._copy_stream)
             torch.cuda.current_stream(self.device).wait_event(done)
             self._in_flight = []
-
-    def _answer(self, keys, values, flags, fallback_value):
-        if self.local._slots is None:              # this shard holds nothing yet: every row is a miss
-            if values is not None:
-                values[:] = torch.as_tensor(0 if fallback_value is None else fallback_value, dtype=values.dtype)
-            flags[:] = False
-        elif values is not None:
-            self.local.get(keys, fallback_value, values=values, is_found=flags)
-        else:
-            self.local.remove_rows(keys, is_removed=flags)
 
     def local_n_elements(self):
         return self.local._n_elements
@@ -347,6 +433,8 @@ class ShardedClosedHashmap:
     identical on all ranks: they define the uuid, which decides the owner shard.
     """
 
+    KINDS = {"get": 1, "set": 2, "remove": 3}
+
     def __init__(self, n_buckets_per_shard, prime1, prime2, alpha1, alpha2, beta1, beta2, group=None, device=None,
                  rehash_factor=2.0, rehash_threshold=0.75, ops=None, pipeline_chunks=2, peer_capacity_rows=0):
         self.group = group
@@ -361,29 +449,65 @@ class ShardedClosedHashmap:
             ops = CudaShardOps(device, n_buckets_per_shard, params, rehash_factor, rehash_threshold)
         self.ops = ops
         self.pipeline_chunks = max(1, int(pipeline_chunks))     # must be the same on every rank
-        # Peer exchange (ranks of ONE node, NVLink): with peer_capacity_rows > 0 (the same on every rank) the rows of
-        # a batch are stored straight into the owners' memory by the partition kernel, and answers straight into the
-        # askers', instead of travelling through all-to-all passes.  A batch that does not fit the capacity (rows
-        # received by any owner, or rows of any rank's own batch, padding included) takes the all-to-all path.
+        # Sliced exchange (ranks of ONE node, NVLink): with peer_capacity_rows > 0 (the same on every rank: the largest
+        # batch a rank submits) the rows of a batch are stored straight into fixed slices of the owners' memory by the
+        # partition kernel, and answers straight into the askers', with every count read on the device: no all-to-all
+        # pass, and no host waits anywhere between submission and result.  A batch that does not fit its slices is
+        # detected on the device, skipped by every rank, and repeated over the exact all-to-all exchange at wait().
         self._peer_capacity = int(peer_capacity_rows) if (self.world > 1 and self.world <= 16) else 0
-        self._peer_on = False
-        self._peer_seq = 0
+        self._sliced_on = False
+        self._seq = 0
         self._streams = None
         self._last_applied = None
+        self._pending = []            # submissions whose tokens have not been read yet: (operations, results, tokens)
         self._value_shape = None
         self._value_dtype = None
+        self._key_shape = None
+        self._key_dtype = None
+
+    # ------------------------------------------------------------------ argument checks (before anything is launched)
+    def _check_keys(self, keys):
+        """Same assertions as the single map (cuda_closed_hashmap.py:397-399 of the reference): a batch whose key
+        dtype or row shape differs from the first set would make the routing kernels read past its end."""
+        assert isinstance(keys, torch.Tensor) and keys.dim() >= 1, "keys must be a tensor of rows"
+        if self._key_shape is not None:
+            assert keys.dtype == self._key_dtype, f"key dtype {keys.dtype}, the map holds {self._key_dtype}"
+            assert tuple(keys.shape[1:]) == self._key_shape, f"key rows {tuple(keys.shape[1:])}, the map holds {self._key_shape}"
+
+    def _check_values(self, keys, values):
+        assert isinstance(values, torch.Tensor) and values.shape[0] == keys.shape[0], "one value row per key row"
+        if self._value_shape is not None:
+            assert values.dtype == self._value_dtype, f"value dtype {values.dtype}, the map holds {self._value_dtype}"
+            assert tuple(values.shape[1:]) == self._value_shape, f"value rows {tuple(values.shape[1:])}, the map holds {self._value_shape}"
+
+    def _check_operation(self, op):
+        assert op[0] in self.KINDS, f"unknown operation {op[0]!r}"
+        if op[0] != "set" and self._value_shape is None:
+            raise RuntimeError("store something first")
+        self._check_keys(op[1])
+        if op[0] == "set":
+            self._check_values(op[1], op[2])
+
+    def _signature(self, kind):
+        """What every rank must agree on for one collective operation, as one integer."""
+        return self.KINDS[kind]
 
     # ------------------------------------------------------------------ exchange plumbing
-    def _exchange_counts(self, counts):
+    def _exchange_counts(self, counts, signature=0):
         """counts[2, world] (device; rows and padded rows per owner) -> (send_padded, recv_rows, recv_padded) as host
-        lists; one synchronisation per batch."""
-        send = counts.t().contiguous()                       # [world, 2]: what goes to each owner
+        lists; one synchronisation per batch.  The operation's signature travels with the counts, so that ranks which
+        submitted different operations find out here, on every rank, instead of deadlocking in the row exchange."""
+        w = self.world
+        send = torch.cat([counts.t().contiguous(), counts.new_full((w, 1), int(signature))], dim=1)   # [world, 3]
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=self.group)
-        flat = self.ops.to_host(torch.stack([send, recv]))          # [2, world, 2] flattened
-        w = self.world
-        send_h = [flat[2 * i:2 * i + 2] for i in range(w)]
-        recv_h = [flat[2 * w + 2 * i:2 * w + 2 * i + 2] for i in range(w)]
+        flat = self.ops.to_host(torch.stack([send, recv]))          # [2, world, 3] flattened
+        send_h = [flat[3 * i:3 * i + 3] for i in range(w)]
+        recv_h = [flat[3 * w + 3 * i:3 * w + 3 * i + 3] for i in range(w)]
+        theirs = sorted({int(c[2]) for c in recv_h})
+        if theirs != [int(signature)]:
+            raise L.DokError(f"ranks submitted different operations to a collective call (signatures {theirs}, "
+                             f"rank {self.rank} has {int(signature)})")
         return [int(c[1]) for c in send_h], [int(c[0]) for c in recv_h], [int(c[1]) for c in recv_h]
 
     def _all_to_all_rows(self, rows, send, recv, async_op=False):
@@ -396,14 +520,14 @@ class ShardedClosedHashmap:
                                       async_op=async_op)
         return (out, work) if async_op else out
 
-    def _route(self, keys, values=None, want_dest=True, async_op=False):
+    def _route(self, keys, values=None, want_dest=True, async_op=False, signature=0):
         """-> (owned_keys, owned_values, segments, dest, send, recv[, works]); segments = [(start, rows)] per source
         rank.  With async_op the key / value exchanges are in flight on return and `works` must be waited for."""
         if self.world == 1:        # one shard owns everything: no partition, no exchange, no permutation
             out = (keys, values, [(0, keys.shape[0])], None, None, None)
             return out + ([],) if async_op else out
         grouped_keys, grouped_values, dest, counts = self.ops.partition(keys, values, self.world, want_dest=want_dest)
-        send, recv_rows, recv = self._exchange_counts(counts)
+        send, recv_rows, recv = self._exchange_counts(counts, signature)
         assert keys.shape[0] <= sum(send) <= grouped_keys.shape[0], "partition lost rows"
         works = []
         owned_keys, w = self._all_to_all_rows(grouped_keys[:sum(send)], send, recv, async_op=True)
@@ -425,193 +549,97 @@ class ShardedClosedHashmap:
         c = self.pipeline_chunks if (pipelined and self.world > 1) else 1
         return [(n * i // c, n * (i + 1) // c) for i in range(c)]
 
-    # ------------------------------------------------------------------ peer exchange
-    def _peer_plan(self, keys):
-        """First partition pass and the gathered count matrix -> plan, or None when this batch must take the
-        all-to-all path (the decision is made from the same matrix on every rank, so all ranks agree)."""
-        w, r = self.world, self.rank
-        keys = keys.contiguous()
-        owners, offsets, counts = self.ops.partition_count(keys, w)
-        matrix = self.ops.empty((w, 2 * w), torch.long)
-        dist.all_gather_into_tensor(matrix, counts, group=self.group)
-        flat = self.ops.to_host(matrix)
-        exact = [[int(flat[s * 2 * w + o]) for o in range(w)] for s in range(w)]        # [source][owner]
-        padded = [[int(flat[s * 2 * w + w + o]) for o in range(w)] for s in range(w)]
-        cap = self._peer_capacity
-        if max(sum(exact[s][o] for s in range(w)) for o in range(w)) > cap or max(sum(row) for row in padded) > cap:
-            return None
-        gen = self._peer_seq & 1
-        self._peer_seq += 1
-        # Inboxes are filled without gaps: the sources' segments follow each other in rank order at their exact row
-        # counts (stores need no alignment, unlike the all-to-all), so an owner can apply everything it received
-        # with one launch, in which row order is (source rank, row): the order that makes "last row wins" global.
-        # Result regions keep the padded starts of the asker's grouped order, which is what dest_index refers to.
-        starts, run = [], 0
-        for s in range(w):
-            starts.append(run)
-            run += exact[s][r]
-        return dict(keys=keys, owners=owners, offsets=offsets, counts=counts, exact=exact, padded=padded, gen=gen,
-                    row0=[sum(exact[s][o] for s in range(r)) for o in range(w)],
-                    segments=[(starts[s], exact[s][r]) for s in range(w)], inbox_rows=run)
-
-    # An operation over the peer exchange has two stages.  SEND: rows into the owners' inboxes (partition + stores
-    # over NVLink).  APPLY: the owner's table work on what it received, answers into the askers' result regions, the
-    # inverse permutation.  A fence (one-element all-reduce on the stream) separates them.
-    def _peer_send(self, plan, values, want_dest):
-        plan["dest"] = self.ops.scatter_to_peers(plan["keys"], values, self.world, plan["owners"], plan["offsets"],
-                                                 plan["counts"], plan["gen"], plan["row0"], want_dest=want_dest)
-
-    def _peer_apply_set(self, plan, assume_unique):
-        owned_keys = self.ops._peer_region(self.rank, plan["gen"], 0, rows=plan["inbox_rows"])
-        owned_values = self.ops._peer_region(self.rank, plan["gen"], 1, rows=plan["inbox_rows"])
-        self.ops.local_set(owned_keys, owned_values, [(0, plan["inbox_rows"])], assume_unique)     # one launch
-
-    def _peer_apply_lookup(self, plan, with_values, fallback_value):
-        w, r, ops = self.world, self.rank, self.ops
-        gen, padded = plan["gen"], plan["padded"]
-        owned_keys = ops._peer_region(r, gen, 0, rows=plan["inbox_rows"])
-        if with_values:
-            # lookups commute: other ranks' rows first, source by source, so that the copy of their answers over NVLink
-            # runs while the next source's rows (and last this rank's own) are probed
-            for s in [s for s in range(w) if s != r] + [r]:
-                start, rows = plan["segments"][s]
-                if not rows:
-                    continue
-                at = sum(padded[s][o] for o in range(r))    # my segment in source s's grouped order
-                ops.local_answer(owned_keys[start:start + rows], ops._peer_region(s, gen, 2, rows=rows, row0=at),
-                                 ops._peer_region(s, gen, 3, rows=rows, row0=at), fallback_value, remote=(s != r))
-        else:
-            # removals source by source in rank order, one launch each: among equal keys of different ranks the
-            # earlier rank reports the removal, and one launch over everything would leave that to the race
-            for s, (start, rows) in enumerate(plan["segments"]):
-                if rows:
-                    at = sum(padded[s][o] for o in range(r))
-                    ops.local_answer(owned_keys[start:start + rows], None, ops._peer_region(s, gen, 3, rows=rows, row0=at),
-                                     None, remote=(s != r))
-        ops.answers_delivered()
-        ops.peer_fence(apply_side=True)
-        n_mine = sum(padded[r])
-        res_flags = ops._peer_region(r, gen, 3, rows=n_mine).view(torch.uint8)
-        res_values = ops._peer_region(r, gen, 2, rows=n_mine) if with_values else None
-        out_values, out_flags = ops.unpermute(res_values, res_flags, plan["dest"])
-        return out_values, out_flags.view(torch.bool)
-
-    def _peer_lookup(self, plan, with_values, fallback_value):
-        """get / remove over the peer exchange, one operation at a time."""
-        self._peer_send(plan, None, want_dest=True)
-        self.ops.peer_fence()
-        return self._peer_apply_lookup(plan, with_values, fallback_value)
-
-    def run(self, operations, wait=True):
-        """Several operations as one software pipeline: [("get", keys[, fallback_value]), ("set", keys, values[,
+    # ------------------------------------------------------------------ sliced exchange: submission without host waits
+    def run(self, operations, wait=True, _force_overflow=False):
+        """Several operations as one submission: [("get", keys[, fallback_value]), ("set", keys, values[,
         assume_unique]), ("remove", keys)] -> list of results (get: (values, is_found); set: None; remove: flags).
         Collective: every rank passes the same sequence of operation kinds.  The operations are applied in order, as if
-        called one after the other; what overlaps is the SEND stage of operation k + 1 (it only reads the caller's
-        batch: partition, count gather, stores into the owners' other inbox generation over NVLink) with the APPLY
-        stage of operation k (table work in HBM), on two streams.  Without the peer exchange the operations simply
-        run one after the other.  Results are ready for the caller's current stream when the call returns -- unless
-        `wait=False`: then the call only enqueues, the next submission's first send may overlap this one's last table
-        work, and the caller calls `wait()` before it uses results or reuses / frees the input tensors (which must
-        already be complete on the current stream at the time of the call)."""
+        called one after the other.
+
+        Over the sliced exchange an operation has two stages.  SEND (it only reads the caller's batch): partition,
+        stores of the rows into the owners' inbox slices over NVLink, a fence.  APPLY: the owner's table work on its
+        inbox, answers into the askers' result regions, a fence, the inverse permutation.  The two stages run on two
+        streams, so the SEND of operation k + 1 overlaps the APPLY of operation k, and since every row count is read on
+        the device the host only enqueues: it never waits for a count, a fence or a kernel.
+
+        Results are ready for the caller's current stream when the call returns -- unless `wait=False`: then the call
+        only enqueues, the next submission's first send may overlap this one's last table work, and the caller calls
+        `wait()` before it uses results or reuses / frees the input tensors (which must already be complete on the
+        current stream at the time of the call).  Without the sliced exchange the operations simply run one after the
+        other over the all-to-all exchange."""
         if not operations:
             return []
-        if not self._peer_on or not self.ops.can_pipeline():
+        for op in operations:
+            self._check_operation(op)
+        if not self._sliced_on or not self.ops.can_pipeline():
             return [self._run_one(op) for op in operations]
         ops = self.ops
         device = ops.device
+        nvtx = torch.cuda.nvtx
         if self._streams is None:
             # the send stage runs at high priority: its kernels are short, and behind the big grids of the table work
             # they would otherwise only start when those have handed out all their blocks
             self._streams = (torch.cuda.Stream(device=device, priority=-1), torch.cuda.Stream(device=device))
         s_send, s_apply = self._streams
         main = torch.cuda.current_stream(device)
+        # copies that make the inputs contiguous run on the caller's stream, before the side streams branch off
+        prepared = [(op[0], op[1].contiguous(), op[2].contiguous() if op[0] == "set" else None) for op in operations]
         start = torch.cuda.Event()
         start.record(main)
         s_send.wait_event(start)
         s_apply.wait_event(start)
         results = [None] * len(operations)
-
-        def send(i):
-            """-> plan with the fence still to come, or None when the batch must take the all-to-all path"""
-            kind, keys = operations[i][0], operations[i][1]
+        with torch.cuda.stream(s_send):
+            tokens = torch.zeros((len(operations), 3), device=device, dtype=torch.long)
+        applied = self._last_applied          # table work of an earlier submission that was not waited for
+        keep = []
+        for i, op in enumerate(operations):
+            kind, keys, values = prepared[i]
+            generation = self._seq & 1
+            self._seq += 1
+            token = tokens[i]
+            nvtx.range_push(f"dok.sharded.{kind}.send")
             with torch.cuda.stream(s_send):
-                plan = self._peer_plan(keys)
-                if plan is not None:
-                    values = operations[i][2].contiguous() if kind == "set" else None
-                    self._peer_send(plan, values, want_dest=(kind != "set"))
-                    if plan["dest"] is not None:
-                        plan["dest"].record_stream(s_apply)
-            return plan
-
-        def fence(plan, applied):
-            """all ranks' sends of this operation and applies of the previous one are complete past this point"""
-            with torch.cuda.stream(s_send):
+                dest = ops.sliced_send(keys, values, generation, want_dest=(kind != "set"), force_overflow=_force_overflow)
                 if applied is not None:
+                    # the inbox generation that the NEXT operation's send overwrites is the one the previous
+                    # operation's apply reads: the fence below (all ranks) must come after that apply
                     s_send.wait_event(applied)
-                ops.peer_fence()
+                ops.sliced_fence(token, self._signature(kind))
                 sent = torch.cuda.Event()
                 sent.record(s_send)
-            return sent
-
-        def apply(i, plan, sent):
-            kind = operations[i][0]
+            keep.append((keys, values, dest))
+            nvtx.range_pop()
+            nvtx.range_push(f"dok.sharded.{kind}.apply")
             with torch.cuda.stream(s_apply):
                 s_apply.wait_event(sent)
+                abort = token[0:1]
                 if kind == "set":
-                    self._peer_apply_set(plan, operations[i][3] if len(operations[i]) > 3 else False)
-                elif kind == "get":
-                    results[i] = self._peer_apply_lookup(plan, True, operations[i][2] if len(operations[i]) > 2 else None)
+                    ops.sliced_apply_set(generation, abort, op[3] if len(op) > 3 else False)
+                    ops.sliced_apply_fence()      # nothing to deliver, but every kind issues the same collectives
                 else:
-                    results[i] = self._peer_apply_lookup(plan, False, None)[1]
-                for t in (results[i] if isinstance(results[i], tuple) else (results[i],)):
-                    if t is not None:
-                        t.record_stream(main)
+                    with_values = kind == "get"
+                    ops.sliced_apply_lookup(generation, abort, with_values, (op[2] if len(op) > 2 else None) if with_values else None)
+                    ops.sliced_apply_fence()
+                    out_values, out_flags = ops.sliced_results(generation, dest, with_values)
+                    results[i] = (out_values, out_flags) if with_values else out_flags
+                    for t in (out_values, out_flags):
+                        if t is not None:
+                            t.record_stream(main)
                 applied = torch.cuda.Event()
                 applied.record(s_apply)
-            return applied
-
-        def drain():
-            for s in (s_send, s_apply):
-                ev = torch.cuda.Event()
-                ev.record(s)
-                main.wait_event(ev)
-
-        assert all(op[0] in ("get", "set", "remove") for op in operations)
-        applied = self._last_applied          # table work of an earlier submission that was not waited for
-        plan = send(0)
-        sent = fence(plan, applied) if plan is not None else None
-        for i in range(len(operations)):
-            if plan is None:
-                # this batch does not fit the arena: everything so far completes, then the all-to-all path
-                drain()
-                self._last_applied = None
-                results[i] = self._run_one(operations[i], peer=False)
-                back = torch.cuda.Event()
-                back.record(main)
-                s_send.wait_event(back)
-                s_apply.wait_event(back)
-                applied = None
-                nxt = send(i + 1) if i + 1 < len(operations) else None
-            else:
-                applied = apply(i, plan, sent)                                # enqueued; the table work takes a while
-                nxt = send(i + 1) if i + 1 < len(operations) else None       # runs meanwhile (the host waits for counts)
-            if i + 1 < len(operations):
-                plan = nxt
-                sent = fence(plan, applied) if plan is not None else None
+            nvtx.range_pop()
         self._last_applied = applied
+        self._pending.append((list(operations), results, tokens, keep))
         if wait:
-            drain()
-            self._last_applied = None
+            self.wait()
         return results
 
-    def _settle(self):
-        """Operations called one at a time run on the caller's stream: anything still in flight from a submission
-        that was not waited for must be ordered before them."""
-        if self._last_applied is not None:
-            self.wait()
-
     def wait(self):
-        """The caller's current stream waits for everything submitted with run(..., wait=False)."""
+        """The caller's current stream waits for everything submitted with run(..., wait=False), and the host reads
+        the tokens of those submissions (one small copy): operations that some rank could not fit into its slices --
+        all ranks skipped them, and everything submitted after them -- are repeated now, in order, over the exact
+        all-to-all exchange, and their results are written into the tensors that run() handed out."""
         if self._streams is not None:
             main = torch.cuda.current_stream(self.ops.device)
             for s in self._streams:
@@ -619,10 +647,39 @@ class ShardedClosedHashmap:
                 ev.record(s)
                 main.wait_event(ev)
         self._last_applied = None
+        pending, self._pending = self._pending, []
+        if not pending:
+            return
+        flat = torch.cat([t for _, _, t, _ in pending]).cpu().tolist()         # waits for the device
+        redo, i = False, 0
+        for operations, results, _, _ in pending:
+            for k, op in enumerate(operations):
+                flag, sig_max, neg_sig_min = flat[i]
+                i += 1
+                if sig_max != -neg_sig_min:
+                    self.ops.sliced_reset_status()
+                    raise L.DokError(f"ranks submitted different operations to a collective call (operation {k}: "
+                                     f"signatures {-neg_sig_min} .. {sig_max}, rank {self.rank} has {self._signature(op[0])})")
+                if flag and not redo:
+                    redo = True
+                    self.ops.sliced_reset_status()
+                if redo:
+                    again = self._run_one(op, sliced=False)
+                    if op[0] == "get":
+                        results[k][0].copy_(again[0])
+                        results[k][1].copy_(again[1])
+                    elif op[0] == "remove":
+                        results[k].copy_(again)
 
-    def _run_one(self, op, peer=True):
+    def _settle(self):
+        """Anything still in flight from a submission that was not waited for is completed (and, if it overflowed,
+        repeated) before an operation that runs on the caller's stream."""
+        if self._last_applied is not None or self._pending:
+            self.wait()
+
+    def _run_one(self, op, sliced=True):
         kind = op[0]
-        saved, self._peer_on = self._peer_on, self._peer_on and peer
+        saved, self._sliced_on = self._sliced_on, self._sliced_on and sliced
         try:
             if kind == "set":
                 return self.set(op[1], op[2], assume_unique=op[3] if len(op) > 3 else False)
@@ -630,56 +687,77 @@ class ShardedClosedHashmap:
                 return self.get(op[1], op[2] if len(op) > 2 else None)
             return self.remove(op[1])
         finally:
-            self._peer_on = saved
+            self._sliced_on = saved
 
     # ------------------------------------------------------------------ operations
+    def _first_set(self, keys, values):
+        self._key_shape, self._key_dtype = tuple(keys.shape[1:]), keys.dtype
+        self._value_shape, self._value_dtype = tuple(values.shape[1:]), values.dtype
+        if hasattr(self.ops, "ensure_allocated"):
+            self.ops.ensure_allocated((self._key_shape, self._key_dtype), (self._value_shape, self._value_dtype))
+        self._start_sliced()
+
+    def _start_sliced(self):
+        if self._peer_capacity and not self._sliced_on and getattr(self.ops, "supports_sliced", False):
+            self._sliced_on = self.ops.sliced_setup(self.group, self.world, self.rank, self._peer_capacity,
+                                                    (self._key_shape, self._key_dtype), (self._value_shape, self._value_dtype))
+
     def set(self, keys, values, assume_unique=False):
         """Collective insert-or-assign.  `assume_unique` promises pairwise different keys across ALL ranks' batches."""
+        self._check_keys(keys)
+        self._check_values(keys, values)
         self._settle()
         if self._value_shape is None:
-            self._value_shape, self._value_dtype = tuple(values.shape[1:]), values.dtype
-            if self._peer_capacity and getattr(self.ops, "supports_peer", False):
-                self._peer_on = self.ops.peer_setup(self.group, self.world, self.rank, self._peer_capacity,
-                                                    (tuple(keys.shape[1:]), keys.dtype), (self._value_shape, self._value_dtype))
-        if self._peer_on:
-            plan = self._peer_plan(keys)
-            if plan is not None:
-                self._peer_send(plan, values.contiguous(), want_dest=False)
-                self.ops.peer_fence()
-                self._peer_apply_set(plan, assume_unique)
-                return
-        owned_keys, owned_values, segments, _, _, _ = self._route(keys, values, want_dest=False)
+            self._first_set(keys, values)
+        if self._sliced_on:
+            self.run([("set", keys, values, assume_unique)])
+            return
+        owned_keys, owned_values, segments, _, _, _ = self._route(keys, values, want_dest=False,
+                                                                  signature=self._signature("set"))
         self.ops.local_set(owned_keys, owned_values, segments, assume_unique)
 
     def state_dict(self):
         """This rank's shard (see CudaClosedHashmap.state_dict) plus the sharding it belongs to.  Every rank saves its
         own; a map rebuilt with the same world size and parameters routes every key to the shard that holds it."""
+        self._settle()
         return {"world": self.world, "rank": self.rank, "shard": self.ops.local.state_dict(),
-                "value_shape": self._value_shape, "value_dtype": self._value_dtype}
+                "value_shape": self._value_shape, "value_dtype": self._value_dtype,
+                "key_shape": self._key_shape, "key_dtype": self._key_dtype}
 
     def load_state_dict(self, state):
-        """Replaces this rank's shard by a saved one (same world size and rank)."""
+        """Replaces this rank's shard by a saved one (same world size and rank).  Collective when the sliced exchange
+        is configured: it is brought up here if the map has not stored anything yet."""
         assert state["world"] == self.world and state["rank"] == self.rank, "a shard belongs to its rank"
+        self._settle()
         self.ops.local = CudaClosedHashmap.from_state_dict(state["shard"], device=self.ops.device)
         self._value_shape, self._value_dtype = state["value_shape"], state["value_dtype"]
+        self._key_shape, self._key_dtype = state.get("key_shape"), state.get("key_dtype")
+        if self._key_shape is None and self.ops.local._slots is not None:
+            self._key_shape, self._key_dtype = tuple(self.ops.local.key_shape), self.ops.local.key_type
+        if self._value_shape is not None and self._key_shape is not None:
+            if hasattr(self.ops, "ensure_allocated"):
+                self.ops.ensure_allocated((self._key_shape, self._key_dtype), (self._value_shape, self._value_dtype))
+            self._start_sliced()
 
     def close(self):
-        """Releases the peer exchange arena (every rank, after the last operation)."""
-        if self._peer_on:
-            self._peer_on = False
-            self.ops.peer_close()
+        """Releases the exchange arena (every rank, after the last operation)."""
+        self._settle()
+        if self._sliced_on:
+            self._sliced_on = False
+            self.ops.sliced_close()
 
     def _lookup(self, keys, local_op, with_values, fallback_value=None):
-        """Shared body of get and remove.  For get the batch is cut into `pipeline_chunks` pieces that move through
-        partition -> key exchange -> local op -> result exchange -> inverse permutation as a software pipeline: the
-        exchanges are enqueued asynchronously, so the key exchange of piece i + 1 and the result exchange of piece
-        i - 1 run while the table is probed for piece i.  remove goes through in one piece: cutting it would let a
-        later rank's first piece overtake an earlier rank's second, and which of two equal keys reports the removal
-        is defined by rank order."""
+        """Shared body of get and remove over the all-to-all exchange.  For get the batch is cut into
+        `pipeline_chunks` pieces that move through partition -> key exchange -> local op -> result exchange -> inverse
+        permutation as a software pipeline: the exchanges are enqueued asynchronously, so the key exchange of piece
+        i + 1 and the result exchange of piece i - 1 run while the table is probed for piece i.  remove goes through in
+        one piece: cutting it would let a later rank's first piece overtake an earlier rank's second, and which of two
+        equal keys reports the removal is defined by rank order."""
         n = keys.shape[0]
         out_values = self.ops.empty((n,) + self._value_shape, self._value_dtype) if with_values else None
         out_flags = self.ops.empty((n,), torch.bool)
         bounds = self._chunk_bounds(n, pipelined=with_values)
+        signature = self._signature("get" if with_values else "remove")
         routed, returned = [], []
 
         def probe(i):
@@ -713,7 +791,7 @@ class ShardedClosedHashmap:
             returned.append((back_values, back_flags, dest, works))
 
         for i, (lo, hi) in enumerate(bounds):
-            routed.append(self._route(keys[lo:hi], async_op=True))
+            routed.append(self._route(keys[lo:hi], async_op=True, signature=signature))
             if i >= 1:
                 probe(i - 1)
         probe(len(bounds) - 1)
@@ -734,28 +812,26 @@ class ShardedClosedHashmap:
         """Collective lookup -> (values[n, *value_shape], is_found[n]) in the caller's row order."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
+        self._check_keys(keys)
         self._settle()
         if self.world == 1:
             if not self.ops.ready():
                 return self._lookup(keys, None, True, fallback_value)
             return self.ops.local_get(keys, [(0, keys.shape[0])], fallback_value)
-        if self._peer_on:
-            plan = self._peer_plan(keys)
-            if plan is not None:
-                return self._peer_lookup(plan, True, fallback_value)
+        if self._sliced_on:
+            return self.run([("get", keys, fallback_value)])[0]
         return self._lookup(keys, lambda k, seg: self.ops.local_get(k, seg, fallback_value), True, fallback_value)
 
     def remove(self, keys):
         """Collective removal -> is_removed[n] aligned to the caller's rows (equal keys report once)."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
+        self._check_keys(keys)
         self._settle()
         if self.world == 1 and self.ops.ready():
             return self.ops.local_remove(keys, [(0, keys.shape[0])])
-        if self._peer_on:
-            plan = self._peer_plan(keys)
-            if plan is not None:
-                return self._peer_lookup(plan, False, None)[1]
+        if self._sliced_on:
+            return self.run([("remove", keys)])[0]
         return self._lookup(keys, lambda k, seg: self.ops.local_remove(k, seg), False)[1]
 
     @property

@@ -15,7 +15,9 @@
  *
  * Storage of a table (owned by the caller, 128-byte aligned, sized by dok_table_layout): n_slots slots of
  * slot_bytes (32, 64, 128, or a larger multiple of 128 for very wide rows):
- *     { int64 tag | int64 stamp (if it fits without growing the slot) | value (padded to 8) | key row (padded to 8) }
+ *     { int64 tag | value (padded to 8) | key row (padded to 8) | int64 stamp (if it fits without growing the slot) }
+ * at the offsets dok_table_layout reports (value_offset is always 8, key_offset = 8 + padded value bytes, stamp_offset
+ * behind the key row or -1).
  * tag = uuid, -1 empty, -3 tombstone, -2 blocked padding slot (slots n_buckets .. n_slots-1).  These are the
  * reference's _uuid, _values and _keys arrays interleaved.  On B200 every access instruction that touches a table
  * much larger than L2 costs the same, whatever it moves, while lanes that fall into one 128-byte line share the
@@ -195,6 +197,37 @@ int64_t dok_static_scratch_max_rows(void);
 int dok_map_count_new_static(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n,
                              int64_t *counters, void *stream);
 
+/* ---- sliced batches -------------------------------------------------------------------------------------
+ * The same three operations on a batch that arrives as n_slices slices of slice_rows rows each (keys / values /
+ * outputs are [n_slices * slice_rows] rows, slice s at row s * slice_rows), of which only the first
+ * slice_counts[s] rows (device int64[n_slices]) are in use.  The counts are read ON THE DEVICE, so a caller that
+ * does not know them yet -- an owner shard whose inbox other GPUs are still filling when it enqueues its work -- can
+ * launch without a host synchronisation: the grid covers whole slices and blocks beyond the count leave at once.
+ * Batch order (what decides "last row wins") is slice by slice.  abort_flag (device int64, may be NULL): a non-zero
+ * value when the kernel runs turns the whole call into a no-op.  Outputs of unused rows are not written.
+ * slot_scratch: int64[n_slices * slice_rows + 1].  No counterpart in the reference (single GPU, sizes known). */
+int dok_map_get_sliced(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n_slices,
+                       int64_t slice_rows, const int64_t *slice_counts, const int64_t *abort_flag, void *out_values,
+                       uint8_t *out_found, const void *fallback, int64_t *counters, void *stream);
+int dok_map_set_sliced(const dok_table *t, const dok_hash_params *hp, const void *keys, const void *values,
+                       int64_t n_slices, int64_t slice_rows, const int64_t *slice_counts, const int64_t *abort_flag,
+                       int64_t *slot_scratch, int64_t epoch, int assume_unique, int64_t *counters, void *stream);
+int dok_map_remove_sliced(const dok_table *t, const dok_hash_params *hp, const void *keys, int64_t n_slices,
+                          int64_t slice_rows, const int64_t *slice_counts, const int64_t *abort_flag,
+                          uint8_t *out_removed, int64_t *counters, void *stream);
+
+/* ---- tables beyond the TLB's reach ------------------------------------------------------------------------
+ * A random access into a slot array larger than what the GPU's TLB covers (64 GiB on B200) costs a page walk, and
+ * the lookup rate falls to a third at 114 GB.  Every entry point above therefore works through such a table in
+ * PASSES over the batch: pass w serves only the rows whose probe chain starts in the w-th window of the slot array,
+ * so that one launch touches a range the TLB covers.  Results are identical to a single pass; the caller sees
+ * nothing but the launch count.  A table of at most single_pass_limit bytes is served in one pass, a larger one in
+ * ceil(bytes / window_bytes) windows (defaults 72 GiB and 58 GiB).  The setting is process-wide; tests use small
+ * values to exercise the passes on small tables.  dok_table_passes reports the passes for a table (-1: bad table).
+ * No counterpart in the reference (32-bit bucket indices keep its tables far below this size). */
+int dok_set_window_bytes(int64_t single_pass_limit, int64_t window_bytes);
+int dok_table_passes(const dok_table *t);
+
 /* Live-slot compaction in slot order (replaces nonempty_mask + the boolean-mask gathers of
  * cuda_closed_hashmap.py:157-172, 233-234).  Step 1 counts per tile and scans:
  *   tile_offsets: device int64[dok_compact_tiles(n_buckets) + 1]; the last element is the live count.
@@ -287,6 +320,36 @@ int dok_shard_partition_scatter_peer(const void *keys, int key_bytes, const void
                                      int n_shards, const uint8_t *owners, const int64_t *tile_offsets,
                                      const int64_t *shard_counts, void *const *peer_keys, void *const *peer_values,
                                      const int64_t *peer_row0, int64_t *dest_index, void *stream);
+
+/* Sliced exchange: every (source rank, owner) pair has a slice of slice_rows rows at a fixed place in the owner's
+ * inbox, so a source needs nobody else's counts to know where its rows go, and no rank's host ever waits for a count.
+ *  - dok_shard_partition_check_slices (after dok_shard_partition_count): raises the sticky word *status to 1 when an
+ *    owner's rows exceed slice_rows, or when force != 0 (the caller already knows the batch cannot go this way).
+ *  - dok_shard_partition_scatter_sliced: stores this rank's rows for owner o at slice_keys[o] / slice_values[o]
+ *    (the start of this rank's slice in owner o's inbox: peer memory, or local for o == this rank), stores the row
+ *    count at count_dst[o] (int64 in the owner's memory; always, also for n == 0), and writes dest_index[i] =
+ *    owner * slice_rows + position: where the answer for row i will be in this rank's result region.  With
+ *    *status != 0 nothing but zero counts is stored.
+ *  - dok_copy_counted: min(*count, max_rows) rows of up to two row arrays (answer values and flags) to another
+ *    place -- the asker's result region on another GPU -- in 16-byte pieces; a no-op when *abort_flag != 0.
+ *    All four pointers 16-byte aligned; dst_b / src_b may be NULL.
+ *  - dok_shard_token_prepare / dok_shard_token_finish bracket the all-reduce(MAX) that closes a send stage: prepare
+ *    writes token[3] = {*status, signature, -signature}; after the reduction finish sets token[0] non-zero when any
+ *    rank overflowed or the ranks' signatures differ (they submitted different operations), and raises *status to it.
+ *    token[0] is the abort_flag of that operation's apply kernels.
+ * The owner applies what it received with the *_sliced map operations.  The caller orders the stages with
+ * stream-ordered collectives (nothing here waits on another GPU).  No counterpart in the reference. */
+int dok_shard_partition_check_slices(const int64_t *shard_counts, int n_shards, int64_t slice_rows, int force,
+                                     int64_t *status, void *stream);
+int dok_shard_partition_scatter_sliced(const void *keys, int key_bytes, const void *values, int value_bytes, int64_t n,
+                                       int n_shards, const uint8_t *owners, const int64_t *tile_offsets,
+                                       const int64_t *shard_counts, void *const *slice_keys, void *const *slice_values,
+                                       int64_t *const *count_dst, int64_t slice_rows, const int64_t *status,
+                                       int64_t *dest_index, void *stream);
+int dok_shard_token_prepare(const int64_t *status, int64_t signature, int64_t *token, void *stream);
+int dok_shard_token_finish(int64_t *token, int64_t *status, void *stream);
+int dok_copy_counted(void *dst_a, const void *src_a, int row_bytes_a, void *dst_b, const void *src_b, int row_bytes_b,
+                     int64_t max_rows, const int64_t *count, const int64_t *abort_flag, void *stream);
 
 /* Exchange arena: device memory of this process that other processes of the node map (CUDA IPC, peer access over
  * NVLink).  dok_peer_alloc allocates outside any caching allocator (an IPC handle names a whole allocation);

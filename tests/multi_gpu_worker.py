@@ -1,8 +1,11 @@
 """Worker of tests/test_sharded_multi_gpu.py (one process per GPU, launched by torch.distributed.run).
 
 The same operation stream goes through two sharded maps, one exchanging rows with NCCL all-to-all and one storing
-them straight into the peers' memory (operation by operation and as pipelined submissions), and -- gathered on rank 0 -- through ONE serial CPU oracle table that receives
-the ranks' batches in rank order.  Everything a caller can observe must agree bit for bit."""
+them straight into fixed slices of the peers' memory (operation by operation and as pipelined submissions that the
+host never waits for), and -- gathered on rank 0 -- through ONE serial CPU oracle table that receives the ranks'
+batches in rank order.  Everything a caller can observe must agree bit for bit.  Batches larger than the slices, and
+a skewed batch whose rows all go to one owner, take the overflow route: skipped by every rank on the device and
+repeated over the all-to-all exchange.  argv[1] = value columns (default 2)."""
 import os
 import sys
 
@@ -20,6 +23,7 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=device)
+    value_columns = int(sys.argv[1]) if len(sys.argv) > 1 else 2
     np.random.seed(7)
     params = port.draw_hash_parameters(1 << 17, 1)
     nb = 1 << 17
@@ -37,7 +41,9 @@ def main():
     for step in range(7):
         n = [9000, 0, 12000, 5, 40000, 7000, 15000][(step + rank) % 7]     # 40000 rows exceed the capacity: all-to-all
         keys = rng.integers(0, 50000, size=(n, 1), dtype=np.int64)          # duplicates within and across ranks
-        values = rng.standard_normal((n, 2)).astype(np.float32)
+        if step == 5 and rank == 0:
+            keys[:] = 12345                              # fits the capacity, but every row goes to ONE owner: slice overflow
+        values = rng.standard_normal((n, value_columns)).astype(np.float32)
         queries = rng.integers(0, 60000, size=(n // 2 + 3, 1), dtype=np.int64)
         doomed = np.unique(rng.integers(0, 60000, size=(n // 5 + 1, 1), dtype=np.int64), axis=0)
         tk, tv = torch.from_numpy(keys).to(device), torch.from_numpy(values).to(device)
@@ -72,7 +78,26 @@ def main():
             for _, _, _, d, _, _, got_r in everything:
                 assert np.array_equal(got_r, single.remove_rows(d)), f"remove flags differ from the single table, step {step}"
             assert single.n_elements == b[3]
-    assert via_peer._peer_on, "the peer exchange was not in use"
+    assert via_peer._sliced_on, "the sliced exchange was not in use"
+    # a shard checkpoint restored into a fresh map brings the sliced exchange up again and answers like the old one
+    restored = ShardedClosedHashmap(nb, device=device, peer_capacity_rows=cap, **params)
+    restored.load_state_dict(via_peer.state_dict())
+    assert restored._sliced_on
+    probe = torch.from_numpy(rng.integers(0, 60000, size=(5000 + rank, 1), dtype=np.int64)).to(device)
+    (v1, f1), (v2, f2) = via_peer.get(probe, -1.0), restored.get(probe, -1.0)
+    assert torch.equal(f1, f2) and torch.equal(v1, v2), "restored shard answers differently"
+    # ranks that submit different operations find out on every rank instead of hanging
+    from doksparse_b200._lib import DokError
+    for table in (via_nccl, via_peer):
+        try:
+            if rank == 0:
+                table.get(probe)
+            else:
+                table.remove(probe)
+            raise AssertionError("mismatched operations went unnoticed")
+        except DokError as exc:
+            assert "different operations" in str(exc)
+    restored.close()
     via_peer.close()
     dist.barrier()
     dist.destroy_process_group()

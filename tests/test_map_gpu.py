@@ -189,8 +189,10 @@ def test_operation_stream_matches_oracle(kd, ks, vd, vs, lo, hi):
 
 
 def test_tiny_tables_wraparound_and_full():
-    """8..64 bucket tables driven to 100 % load: probe wrap-around, a full table refuses silently
-    (closed_hashmap_impl_class.cu:426), tombstones are reused."""
+    """8..64 bucket tables driven to 100 % load: probe wrap-around, tombstones are reused.  A full table stores no
+    further row, like the reference (closed_hashmap_impl_class.cu:426, which drops them without a word); here the
+    refused rows are counted on the device and reported once, at the next host-side read of n_elements."""
+    from doksparse_b200._lib import DokError
     for nb in (8, 13, 64):
         rng = np.random.default_rng(nb)
         p = Pair(seed=nb, n_buckets=nb, rehash_threshold=100.0, **good_parameters(nb, 1, seed=nb))
@@ -202,11 +204,14 @@ def test_tiny_tables_wraparound_and_full():
         assert host(p.c._uuid != -1).all()                     # 100 % load
         ov, of = p.get(keys)
         assert of[:nb].all() and not of[nb:].any()
-        # a full table: further distinct keys are not stored (the reference drops them without an error)
+        # a full table: further distinct keys are not stored
         p.c.set(dev(second), dev(vals[nb:]), assume_unique=True)
         cv, cf = p.c.get(dev(second))
         assert not host(cf).any()
-        p.c._n_elements.fill_(nb); p.c._shared["bound"] = nb    # bookkeeping of the refused rows is not compared
+        assert p.c.last_set_failed == nb
+        with pytest.raises(DokError, match="table was full"):
+            p.c.n_elements
+        assert p.c.last_set_failed == 0 and p.c.n_elements == nb      # reported once; nothing was added
         removed = p.remove(first[::2])
         assert removed.all()
         assert p.c.n_tombstones == len(first[::2])

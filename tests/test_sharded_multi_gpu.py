@@ -11,11 +11,13 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpus_nccl_and_peer_exchange_match_one_table():
+@pytest.mark.parametrize("world,value_columns", [(2, 2), (2, 5), (4, 2), (8, 2)])
+def test_ranks_on_real_gpus_match_one_table(world, value_columns):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29533", os.path.join(HERE, "multi_gpu_worker.py")]
-    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
-    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29533 + world), os.path.join(HERE, "multi_gpu_worker.py"), str(value_columns)]
+    done = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-6000:]
     assert "multi-gpu parity ok" in done.stdout
