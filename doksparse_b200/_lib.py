@@ -106,7 +106,7 @@ def _declare(lib):
         "dok_shard_partition_count": ([HP, P, I64, I, P, P, P, P], I),
         "dok_partition_capacity": ([I64, I], I64),
         "dok_shard_partition_scatter": ([P, I, P, I, I64, I, P, P, P, P, P, P, P], I),
-        "dok_shard_unpermute": ([P, P, P, I, I64, P, P, P], I),
+        "dok_shard_unpermute": ([P, P, P, I, I64, P, P, P, P], I),
         "dok_words_to_pinned": ([P, P, I, P], I),
         "dok_dok_rekey_insert": ([TP, HP, P, TP, HP, P, P, P], I),
         "dok_map_reinsert": ([TP, TP, HP, P, P], I),

@@ -278,7 +278,9 @@ static __global__ void __launch_bounds__(256) k_copy_counted(char *__restrict__ 
 static __global__ void __launch_bounds__(DOK_TPB) k_unpermute(const char *__restrict__ grouped_values,
                                                               const uint8_t *__restrict__ grouped_found,
                                                               const ll_t *__restrict__ dest_index, int vb, ll_t n,
-                                                              char *__restrict__ out_values, uint8_t *__restrict__ out_found) {
+                                                              char *__restrict__ out_values, uint8_t *__restrict__ out_found,
+                                                              const ll_t *abort) {
+  if (abort != nullptr && *abort != 0) return;      // the operation was skipped: dest_index was never written
   const ll_t i = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
   if (i >= n) return;
   const ll_t g = dest_index[i];
@@ -462,12 +464,14 @@ int dok_peer_close(void *ptr) {
 }
 
 int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found, const int64_t *dest_index,
-                        int value_bytes, int64_t n, void *out_values, uint8_t *out_found, void *stream) {
+                        int value_bytes, int64_t n, void *out_values, uint8_t *out_found, const int64_t *abort_flag,
+                        void *stream) {
   if (n < 0 || n > DOK_MAX_BATCH) return DOK_BAD_ARG;
   if (n == 0) return DOK_OK;
   if (!dest_index || (out_values && (!grouped_values || value_bytes < 1)) || (out_found && !grouped_found)) return DOK_BAD_ARG;
   k_unpermute<<<(unsigned)((n + DOK_TPB - 1) / DOK_TPB), DOK_TPB, 0, (cudaStream_t)stream>>>(
-      (const char *)grouped_values, grouped_found, (const ll_t *)dest_index, value_bytes, n, (char *)out_values, out_found);
+      (const char *)grouped_values, grouped_found, (const ll_t *)dest_index, value_bytes, n, (char *)out_values, out_found,
+      (const ll_t *)abort_flag);
   return dok_check_launch();
 }
 

@@ -289,12 +289,13 @@ class CudaShardOps:
             self._in_flight.append(True)
         self.answers_delivered()
 
-    def sliced_results(self, generation, dest, with_values):
-        """Inverse permutation of this rank's result region into the caller's row order."""
+    def sliced_results(self, generation, dest, with_values, abort=None):
+        """Inverse permutation of this rank's result region into the caller's row order (nothing happens when the
+        operation was skipped: dest was never written then)."""
         p = self._sx
         values = self._region(p["rank"], generation, 3) if with_values else None
         flags = self._region(p["rank"], generation, 4).view(torch.uint8)
-        out_values, out_flags = self.unpermute(values, flags, dest)
+        out_values, out_flags = self.unpermute(values, flags, dest, abort=abort)
         return out_values, out_flags.view(torch.bool)
 
     def ensure_allocated(self, key_row, value_row):
@@ -347,7 +348,7 @@ class CudaShardOps:
                                                     L.ptr(grouped_values), L.ptr(dest), st), "dok_shard_partition_scatter")
         return grouped_keys, grouped_values, dest, counts.view(2, world)
 
-    def unpermute(self, grouped_values, grouped_flags, dest, out_values=None, out_flags=None):
+    def unpermute(self, grouped_values, grouped_flags, dest, out_values=None, out_flags=None, abort=None):
         """out[i] = grouped[dest[i]]; writes into out_values / out_flags (contiguous, dest.shape[0] rows) when given."""
         lib = L.lib()
         n = dest.shape[0]
@@ -364,7 +365,7 @@ class CudaShardOps:
                 assert out_flags.is_contiguous() and out_flags.shape[0] == n
             L.check(lib.dok_shard_unpermute(L.ptr(grouped_values), L.ptr(grouped_flags), L.ptr(dest), vb, n,
                                             L.ptr(out_values) if grouped_values is not None else None,
-                                            L.ptr(out_flags) if grouped_flags is not None else None,
+                                            L.ptr(out_flags) if grouped_flags is not None else None, L.ptr(abort),
                                             L.stream_ptr(self.device)), "dok_shard_unpermute")
         return (out_values if grouped_values is not None else None), (out_flags if grouped_flags is not None else None)
 
@@ -621,7 +622,7 @@ class ShardedClosedHashmap:
                     with_values = kind == "get"
                     ops.sliced_apply_lookup(generation, abort, with_values, (op[2] if len(op) > 2 else None) if with_values else None)
                     ops.sliced_apply_fence()
-                    out_values, out_flags = ops.sliced_results(generation, dest, with_values)
+                    out_values, out_flags = ops.sliced_results(generation, dest, with_values, abort)
                     results[i] = (out_values, out_flags) if with_values else out_flags
                     for t in (out_values, out_flags):
                         if t is not None:

@@ -366,9 +366,12 @@ int dok_peer_close(void *ptr);
  * does not queue behind bulk device-to-host copies of other streams.  Complete when the stream reaches this point. */
 int dok_words_to_pinned(const int64_t *src, int64_t *pinned_dst, int n_words, void *stream);
 
-/* out_values[i] = grouped_values[dest_index[i]], out_found[i] = grouped_found[dest_index[i]] */
+/* out_values[i] = grouped_values[dest_index[i]], out_found[i] = grouped_found[dest_index[i]].  abort_flag (device
+ * int64, may be NULL): non-zero when the kernel runs = nothing is read or written (the operation was skipped and
+ * dest_index holds nothing). */
 int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found, const int64_t *dest_index,
-                        int value_bytes, int64_t n, void *out_values, uint8_t *out_found, void *stream);
+                        int value_bytes, int64_t n, void *out_values, uint8_t *out_found, const int64_t *abort_flag,
+                        void *stream);
 
 /* Diagnostic: n_reads independent random 16-byte reads over buf[0, bytes) (one per thread).  Timed by the caller,
  * it gives the rate at which this GPU serves random requests; for buffers much larger than L2 that rate bounds
