@@ -1,13 +1,14 @@
 #!/usr/bin/env python
-"""Benchmark of the hash-map hot path: batched get + set (+ remove of the rows the set inserted) on a
-hash-sharded CudaClosedHashmap.
+"""Benchmark of the hash-map hot path: batched get + set (+ remove of the rows the set inserted) on the
+hash-sharded CudaClosedHashmap of BASELINE.json configs[4].
 
-Workload (BASELINE.json configs[4], per-GPU shard, weak scaling): every GPU holds 2^28 int64 keys drawn
-uniformly from [0, 2^62) mapped to float32[2] values in a shard of 447,392,427 buckets (load 0.6); a step is,
-per GPU, a get of 32 Mi queries (80 % stored keys of ANY shard, 20 % absent), a set of 32 Mi rows (80 %
-stored keys -> overwrite, 20 % new keys) and the removal of the rows that set inserted, which keeps the load
-stationary.  With N GPUs the table has N * 2^28 keys and each rank routes its batch to the owning shards
-(stable partition + NCCL all-to-all) and gets the results back; N = 8 is exactly the 2^31-key configuration.
+Workload (default, strong scaling): 2^31 int64 keys drawn uniformly from [0, 2^62) mapped to float32[2] values at load
+0.6, spread over the N GPUs by hash; a step is a get of 2^28 queries (80 % stored keys, 20 % absent), a set of 2^28
+rows (80 % stored keys -> overwrite, 20 % new keys) and the removal of the rows that set inserted, which keeps the
+load stationary; every rank submits 1/N of each batch.  N = 1 is the whole table on one GPU (114.5 GB of slots, worked
+through in two passes per batch because it exceeds the 64 GiB the TLB covers); with N > 1 each rank routes its rows
+to the owning shards over NVLink (sliced exchange) and gets the results back.  `--scaling weak` keeps 2^28 keys and
+2^25-row batches PER GPU instead (N = 8 is then the same 2^31-key table).
 
   python bench.py [--gpus N] [--steps K] [--warmup W]            candidate (CUDA), one process per GPU
   python bench.py --impl reference ...                            the reference's own kernels on the host cores
@@ -33,7 +34,7 @@ M62 = (1 << 62) - 1
 KEY_BYTES, VALUE_BYTES = 8, 8
 HIT_FRACTION = 0.8
 LOAD_FACTOR = 0.6
-N_BATCHES = 4          # distinct query/update batches rotated over the steps (each is larger than L2)
+N_BATCHES = 4          # distinct query/update batches rotated over the steps (each is larger than L2); 2 for huge batches
 # DRAM bytes per operation of the kernels, dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture divided by
 # the rows of the launch (profiles/k_*_c5_shard_2e26keys.md; the capture ran at 2^26 keys and 2^24 rows, traffic per row
 # does not depend on the size once the table is much larger than L2)
@@ -46,8 +47,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["candidate", "reference"], default="candidate")
-    ap.add_argument("--keys-log2", type=int, default=28, help="stored keys per GPU (default 2^28)")
-    ap.add_argument("--batch-log2", type=int, default=25, help="queries per GPU and step (default 2^25 = 32 Mi)")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong",
+                    help="strong (default): --keys-log2 / --batch-log2 are TOTALS split over the GPUs; weak: per GPU")
+    ap.add_argument("--keys-log2", type=int, default=None, help="stored keys: total 2^31 (strong) or 2^28 per GPU (weak)")
+    ap.add_argument("--batch-log2", type=int, default=None, help="rows per operation and step: total 2^28 (strong) or 2^25 per GPU (weak)")
     ap.add_argument("--no-ref-gpu", action="store_true",
                     help="reference arm: skip the extra leg that runs the reference's kernels on the GPU")
     ap.add_argument("--no-peer", action="store_true",
@@ -56,7 +59,22 @@ def parse_args():
                     help="multi-GPU: call get / set / remove one after the other instead of one pipelined submission")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    return ap.parse_args()
+    ap.add_argument("--no-shard-point", action="store_true",
+                    help="1 GPU, strong scaling: skip the extra leg on a 2^28-key table (the size the reference's kernels can hold)")
+    ap.add_argument("--no-extras", action="store_true", help="1 GPU: skip the legs on BASELINE configs 1', 2, 3 and 4")
+    args = ap.parse_args()
+    if args.keys_log2 is None:
+        args.keys_log2 = 31 if args.scaling == "strong" else 28
+    if args.batch_log2 is None:
+        args.batch_log2 = 28 if args.scaling == "strong" else 25
+    return args
+
+
+def sizes_per_gpu(args, world):
+    """(stored keys, rows per operation and step) of ONE rank"""
+    if args.scaling == "strong":
+        return (1 << args.keys_log2) // world, (1 << args.batch_log2) // world
+    return 1 << args.keys_log2, 1 << args.batch_log2
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -226,11 +244,45 @@ def cpu_arm(steps, warmup, sample_keys_log2=24, sample_batch_log2=22, budget_s=N
     return mops, dt / max(done, 1) * 1e3, desc
 
 
-def reference_kernels_on_gpu(args, steps=5, warmup=3):
+SHARD_POINT_KEYS_LOG2, SHARD_POINT_BATCH_LOG2 = 28, 25      # the largest power-of-two table the reference's kernels hold
+
+
+def make_batches(torch, device, n_batches, q, total_keys, rank, keep_idx=(0,)):
+    """Seeded batches of one rank: get keys (80 % stored anywhere in the table, 20 % absent), set rows (80 % stored ->
+    overwrite, 20 % new) and the new keys (removed again at the end of a step)."""
+    n_hit = int(q * HIT_FRACTION)
+    g = torch.Generator(device=device).manual_seed(1234 + rank)
+    batches = []
+    for b in range(n_batches):
+        j = torch.arange(n_hit, device=device, dtype=torch.long)
+        hit_idx = (j * 7919 + 104729 * (b + 1) + 15485863 * rank) % total_keys
+        del j
+        base = (b << 34) + (rank << 30)
+        tail = torch.arange(q - n_hit, device=device, dtype=torch.long)
+        miss_idx, new_idx = (1 << 40) + base + tail, (1 << 41) + base + tail
+        del tail
+        perm = torch.randperm(q, device=device, generator=g)
+        get_idx = torch.cat([hit_idx, miss_idx])[perm]
+        del miss_idx
+        set_idx = torch.cat([hit_idx, new_idx])[perm]
+        del hit_idx, perm
+        d = {"get_keys": mix62_torch(get_idx)[:, None].contiguous(),
+             "set_keys": mix62_torch(set_idx)[:, None].contiguous(), "set_values": value_of_index(set_idx, torch).contiguous(),
+             "fresh_keys": mix62_torch(new_idx)[:, None].contiguous()}
+        if b in keep_idx:
+            d["get_idx"], d["set_idx"] = get_idx, set_idx
+        del get_idx, set_idx, new_idx
+        batches.append(d)
+    return batches
+
+
+def reference_kernels_on_gpu(steps=5, warmup=3):
     """The reference's own get / set / remove kernels (its kernel text compiled ahead of time by nvcc, since CuPy is
-    not available) on cuda:0, on this bench's per-GPU workload: same table size and load, same batch construction,
-    same operation order.  Kernels only -- the reference's Python bookkeeping around them (a pre-get, a row-sort
-    unique and host synchronisations per set; a unique per remove) is left out, which favours the reference.
+    not available) on cuda:0, on a table of 2^28 keys at load 0.6 with 2^25-row batches -- one shard of the 8-GPU
+    configuration, and the largest power-of-two size its 32-bit bucket indices hold (closed_hashmap_impl_class.cu:184)
+    -- with the same batch construction and operation order as the candidate's `shard_point` leg.  Kernels only: the
+    reference's Python bookkeeping around them (a pre-get, a row-sort unique and host synchronisations per set; a
+    unique per remove) is left out, which favours the reference; `api_path` adds it back.
     Returns a dict for the JSON line, or a reason string when it cannot run here."""
     try:
         import torch
@@ -242,7 +294,7 @@ def reference_kernels_on_gpu(args, steps=5, warmup=3):
     if not ref_gpu.available(torch.int64, 1, torch.float32, 2):
         return "oracle/_ref/refgpu_map_i64x1_f32x2.so not built"
     device = torch.device("cuda", 0)
-    n_keys, q = 1 << args.keys_log2, 1 << args.batch_log2
+    n_keys, q = 1 << SHARD_POINT_KEYS_LOG2, 1 << SHARD_POINT_BATCH_LOG2
     nb = int(n_keys / LOAD_FACTOR)
     if nb * 2 > ref_gpu.RefGpuMap.MAX_ELEMENTS:
         return "table beyond the reference's 32-bit bucket indices"
@@ -251,23 +303,13 @@ def reference_kernels_on_gpu(args, steps=5, warmup=3):
     for lo in range(0, n_keys, chunk):
         idx = torch.arange(lo, lo + chunk, device=device, dtype=torch.long)
         table.set(mix62_torch(idx)[:, None].contiguous(), value_of_index(idx, torch).contiguous())
-    n_hit = int(q * HIT_FRACTION)
-    g = torch.Generator(device=device).manual_seed(1234)
-    batches = []
-    for b in range(N_BATCHES):
-        j = torch.arange(n_hit, device=device, dtype=torch.long)
-        hit_idx = (j * 7919 + 104729 * (b + 1)) % n_keys
-        miss_idx = (1 << 40) + (b << 32) + torch.arange(q - n_hit, device=device, dtype=torch.long)
-        new_idx = (1 << 41) + (b << 32) + torch.arange(q - n_hit, device=device, dtype=torch.long)
-        perm = torch.randperm(q, device=device, generator=g)
-        get_idx, set_idx = torch.cat([hit_idx, miss_idx])[perm], torch.cat([hit_idx, new_idx])[perm]
-        batches.append((mix62_torch(get_idx)[:, None].contiguous(), get_idx, mix62_torch(set_idx)[:, None].contiguous(),
-                        value_of_index(set_idx, torch).contiguous(), mix62_torch(new_idx)[:, None].contiguous()))
+    batches = make_batches(torch, device, N_BATCHES, q, n_keys, 0)
 
     def step(b, events=None):
-        gk, _, sk, sv, fk = batches[b % N_BATCHES]
+        d = batches[b % N_BATCHES]
         marks = []
-        for fn in (lambda: table.get(gk), lambda: table.set(sk, sv), lambda: table.remove(fk), None):
+        for fn in (lambda: table.get(d["get_keys"]), lambda: table.set(d["set_keys"], d["set_values"]),
+                   lambda: table.remove(d["fresh_keys"]), None):
             if events is not None:
                 marks.append(torch.cuda.Event(enable_timing=True)); marks[-1].record()
             if fn is not None:
@@ -275,9 +317,9 @@ def reference_kernels_on_gpu(args, steps=5, warmup=3):
         if events is not None:
             events.append(marks)
 
-    values, found = table.get(batches[0][0])
-    expect = batches[0][1] < (1 << 40)
-    ok = bool(torch.equal(found, expect)) and bool(torch.equal(values[expect], value_of_index(batches[0][1][expect], torch)))
+    values, found = table.get(batches[0]["get_keys"])
+    expect = batches[0]["get_idx"] < (1 << 40)
+    ok = bool(torch.equal(found, expect)) and bool(torch.equal(values[expect], value_of_index(batches[0]["get_idx"][expect], torch)))
     for s in range(warmup):
         step(s)
     torch.cuda.synchronize()
@@ -294,10 +336,10 @@ def reference_kernels_on_gpu(args, steps=5, warmup=3):
     # the same step the way a user of the reference calls it: with the Python bookkeeping of its set / remove
     # (pre-get, row-wise unique, host read of n_elements) around the kernels
     def api_step(b):
-        gk, _, sk, sv, fk = batches[b % N_BATCHES]
-        table.get(gk)
-        table.api_set(sk, sv, rehash_threshold=0.95)
-        table.api_remove(fk)
+        d = batches[b % N_BATCHES]
+        table.get(d["get_keys"])
+        table.api_set(d["set_keys"], d["set_values"], rehash_threshold=0.95)
+        table.api_remove(d["fresh_keys"])
 
     table.n_elements = torch.tensor(n_keys, device=device)
     api_step(0)
@@ -312,6 +354,7 @@ def reference_kernels_on_gpu(args, steps=5, warmup=3):
     api_ms = a0.elapsed_time(a1) / api_steps
     live = int(((table.all_uuids != -1) & (table.all_uuids != -3)).sum().item())
     return {"value": 2 * q / (ms * 1e-3) / 1e6, "unit": "Mops/s", "ms_per_step": ms,
+            "keys": n_keys, "batch": q,
             "get_ms": phase[0], "set_ms": phase[1], "remove_ms": phase[2], "steps": steps, "results_ok": ok,
             "live_keys_after": live, "live_keys_expected": n_keys,
             "api_path": {"value": 2 * q / (api_ms * 1e-3) / 1e6, "unit": "Mops/s", "ms_per_step": api_ms, "steps": api_steps,
@@ -320,47 +363,165 @@ def reference_kernels_on_gpu(args, steps=5, warmup=3):
                                  "per set, unique(dim=0) per remove), i.e. what a caller of the reference API pays"},
             "what": "the reference's closed_hashmap_get/set/remove kernels (closed_hashmap_impl.cu), nvcc -O3 for sm_100a, "
                     "launched like closed_hashmap_impl.py does, incl. its output allocation and fallback fill; "
-                    "no Python-side pre-get / unique / rehash logic"}
+                    "no Python-side pre-get / unique / rehash logic; 2^28 keys, 2^25-row batches (compare with the "
+                    "candidate's shard_point)"}
+
+
+CPU_SAMPLE_KEYS_LOG2, CPU_SAMPLE_BATCH_LOG2 = 24, 22
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    mops, ms, desc = cpu_arm(args.steps, args.warmup)
-    gpu_leg = None if args.no_ref_gpu else reference_kernels_on_gpu(args)
+    mops, ms, desc = cpu_arm(args.steps, args.warmup, CPU_SAMPLE_KEYS_LOG2, CPU_SAMPLE_BATCH_LOG2)
+    gpu_leg = None if args.no_ref_gpu else reference_kernels_on_gpu()
+    gpu_configs = None
+    if not args.no_ref_gpu and not args.no_extras and isinstance(gpu_leg, dict):
+        try:
+            import torch
+            import bench_configs
+            torch.cuda.empty_cache()
+            gpu_configs = bench_configs.run_reference_kernels(torch, torch.device("cuda", 0))
+        except Exception as exc:
+            gpu_configs = f"{type(exc).__name__}: {exc}"
+    config = workload_config(args, world=args.gpus)
+    # what this arm really ran: a bounded sample of the workload on the host cores
+    config.update({"sample_of_workload": True, "sample_keys": 1 << CPU_SAMPLE_KEYS_LOG2, "sample_batch": 1 << CPU_SAMPLE_BATCH_LOG2,
+                   "sample": desc["sample"]})
     line = {
         "impl": "reference", "metric": "hashmap get/set Mops/s", "value": mops, "unit": "Mops/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": args.scaling,
         "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-        "config": workload_config(args, world=args.gpus),
+        "config": config,
         "cpu_baseline": desc,
         "e2e": {"value": mops, "unit": "Mops/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         # extra: the same reference kernel text run on this box's GPU (kernel-only, 1 GPU); not the line's value
         "reference_kernels_gpu": gpu_leg,
+        "reference_kernels_gpu_configs": gpu_configs,
     }
     print(json.dumps(line))
 
 
 def workload_config(args, world):
+    n_keys, q = sizes_per_gpu(args, world)
+    n_batches = N_BATCHES if q < (1 << 27) else 2
     return {
         "workload": "BASELINE configs[4]: hash-sharded CudaClosedHashmap, int64 keys uniform in [0,2^62) -> float32[2], "
-                    f"2^{args.keys_log2} keys per GPU at load {LOAD_FACTOR}, per GPU and step: get 2^{args.batch_log2} "
-                    f"(80% hits) + set 2^{args.batch_log2} (80% overwrite, 20% insert) + remove of the inserted rows",
-        "keys_per_gpu": 1 << args.keys_log2, "buckets_per_gpu": int((1 << args.keys_log2) / LOAD_FACTOR),
-        "batch_per_gpu": 1 << args.batch_log2, "shards": world,
-        "l2_policy": f"inputs larger than L2: {N_BATCHES} rotating batches of {(1 << args.batch_log2) * 8 >> 20} MiB keys, "
-                     f"table {(int((1 << args.keys_log2) / LOAD_FACTOR) * 32) >> 20} MiB per GPU",
+                    f"{n_keys * world} keys in total ({n_keys} per GPU) at load {LOAD_FACTOR}; a step = get of {q * world} rows "
+                    f"(80% hits) + set of {q * world} rows (80% overwrite, 20% insert) + remove of the inserted rows, "
+                    f"{q} rows per GPU and operation",
+        "total_keys": n_keys * world, "total_batch": q * world,
+        "keys_per_gpu": n_keys, "buckets_per_gpu": int(n_keys / LOAD_FACTOR),
+        "batch_per_gpu": q, "shards": world,
+        "l2_policy": f"inputs larger than L2: {n_batches} rotating batches of {q * 8 >> 20} MiB keys per GPU, "
+                     f"table {(int(n_keys / LOAD_FACTOR) * 32) >> 20} MiB per GPU",
         "parallelism": ("single GPU" if world == 1 else
                         f"hash-sharded x{world}, " + ("NCCL all-to-all" if getattr(args, "no_peer", False) else
-                                                      "rows stored into the owners' memory over NVLink (peer exchange)")),
+                                                      "rows stored into fixed slices of the owners' memory over NVLink "
+                                                      "(sliced exchange, no host waits)")),
     }
 
 
 # ---------------------------------------------------------------------------------------------------------------
 # candidate arm
 # ---------------------------------------------------------------------------------------------------------------
+
+def build_table(torch, table, n_keys, rank, device):
+    """rank r inserts key indices [r * n_keys, (r + 1) * n_keys), routed to their owners (untimed)"""
+    chunk = min(n_keys, 1 << 25)
+    for lo in range(rank * n_keys, (rank + 1) * n_keys, chunk):
+        idx = torch.arange(lo, lo + chunk, device=device, dtype=torch.long)
+        table.set(mix62_torch(idx)[:, None], value_of_index(idx, torch), assume_unique=True)
+
+
+def time_steps(torch, step, steps, first):
+    """K sequential steps with per-operation CUDA events -> (ms per step, [get, set, remove] ms)"""
+    events = []
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for s in range(steps):
+        step(first + s, events)
+    t1.record()
+    torch.cuda.synchronize()
+    phase = [0.0, 0.0, 0.0]
+    for s in range(steps):
+        e = events[4 * s: 4 * s + 4]
+        for i in range(3):
+            phase[i] += e[i].elapsed_time(e[i + 1]) / steps
+    return t0.elapsed_time(t1) / steps, phase
+
+
+def random_request_rate(torch, L, buf, nbytes, device, n_reads=1 << 26):
+    """G random 16-byte reads per second over buf[0, nbytes): the ceiling of any probing kernel on that range"""
+    lib = L.lib()
+    lib.dok_diag_random_reads(L.ptr(buf), nbytes, n_reads, 1, None, L.stream_ptr(device))
+    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    r0.record()
+    for rep in range(3):
+        lib.dok_diag_random_reads(L.ptr(buf), nbytes, n_reads, 100 + rep, None, L.stream_ptr(device))
+    r1.record()
+    torch.cuda.synchronize()
+    return 3 * n_reads / (r0.elapsed_time(r1) * 1e-3) / 1e9
+
+
+def shard_point(torch, device):
+    """This library's kernels on the table size the reference's kernels can hold (2^28 keys, 2^25-row batches, one GPU,
+    device-resident): the leg to put beside `reference_kernels_gpu` of the reference arm."""
+    from doksparse_b200 import CudaClosedHashmap
+    n_keys, q = 1 << SHARD_POINT_KEYS_LOG2, 1 << SHARD_POINT_BATCH_LOG2
+    table = CudaClosedHashmap(n_buckets=int(n_keys / LOAD_FACTOR), device=device, rehash_threshold=0.95, **fixed_parameters())
+    build_table(torch, table, n_keys, 0, device)
+    batches = make_batches(torch, device, N_BATCHES, q, n_keys, 0)
+
+    def step(b, events=None):
+        d = batches[b % N_BATCHES]
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        marks[0].record()
+        values, found = table.get(d["get_keys"])
+        marks[1].record()
+        table.set(d["set_keys"], d["set_values"])
+        marks[2].record()
+        table.remove_rows(d["fresh_keys"])
+        marks[3].record()
+        if events is not None:
+            events.extend(marks)
+        return values, found
+
+    values, found = step(0)
+    expect = batches[0]["get_idx"] < (1 << 40)
+    ok = bool(torch.equal(found, expect)) and bool(torch.equal(values[expect], value_of_index(batches[0]["get_idx"][expect], torch)))
+    for s in range(1, 4):
+        step(s)
+    torch.cuda.synchronize()
+    ms, phase = time_steps(torch, step, 10, 4)
+    # load 0.5, the point the north-star is worded on: the same keys in a table of 2 * n_keys buckets
+    half = CudaClosedHashmap(n_buckets=2 * n_keys, device=device, rehash_threshold=0.95, **fixed_parameters())
+    build_table(torch, half, n_keys, 0, device)
+    for s in range(3):
+        half.get(batches[s % N_BATCHES]["get_keys"])
+    h0, h1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    h0.record()
+    for s in range(8):
+        half.get(batches[s % N_BATCHES]["get_keys"])
+    h1.record()
+    torch.cuda.synchronize()
+    get_half_ms = h0.elapsed_time(h1) / 8
+    probes, _ = table.probe_stats(batches[0]["get_keys"])
+    probes_half, _ = half.probe_stats(batches[0]["get_keys"])
+    peak, _ = measured_peak_gbs()
+    return {"keys": n_keys, "batch": q, "value": 2 * q / (ms * 1e-3) / 1e6, "unit": "Mops/s", "ms_per_step": ms,
+            "get_ms": phase[0], "set_ms": phase[1], "remove_ms": phase[2], "results_ok": ok,
+            "get_frac": algorithmic_bytes("get") * q / (phase[0] * 1e-3) / 1e9 / peak,
+            "set_frac": algorithmic_bytes("set") * q / (phase[1] * 1e-3) / 1e9 / peak,
+            "remove_frac": algorithmic_bytes("remove") * (q - int(q * HIT_FRACTION)) / (phase[2] * 1e-3) / 1e9 / peak,
+            "mean_probe_groups_load_0.6": probes,
+            "get_load_0.5": {"ms": get_half_ms, "mops": q / (get_half_ms * 1e-3) / 1e6, "mean_probe_groups": probes_half,
+                             "frac": algorithmic_bytes("get") * q / (get_half_ms * 1e-3) / 1e9 / peak},
+            "what": "one shard of the 8-GPU configuration on one GPU, device-resident, operations called one after the "
+                    "other; compare with reference_kernels_gpu of the reference arm (same table, same batches)"}
+
 
 def run_candidate(args):
     import torch
@@ -376,46 +537,23 @@ def run_candidate(args):
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"        # keep NCCL's banner off stdout: one JSON line only
-        # the small collectives of the exchange (count gather, fences) must not queue behind the big probing grids
+        # the small collectives of the exchange (fences) must not queue behind the big probing grids
         os.environ.setdefault("TORCH_NCCL_HIGH_PRIORITY", "1")
         dist.init_process_group("nccl", device_id=device)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
 
-    n_keys, q = 1 << args.keys_log2, 1 << args.batch_log2
+    n_keys, q = sizes_per_gpu(args, world)
     total_keys = n_keys * world
     nb = int(n_keys / LOAD_FACTOR)
-    # rows of a batch go straight into the owners' memory over NVLink (sized for a batch plus skew and padding);
-    # --no-peer keeps the NCCL all-to-all exchange
-    peer_rows = 0 if (world == 1 or args.no_peer) else int(q * 1.25) + 16 * world
+    n_batches = N_BATCHES if q < (1 << 27) else 2
+    # rows of a batch go straight into fixed slices of the owners' memory over NVLink; --no-peer keeps the NCCL
+    # all-to-all exchange
+    peer_rows = 0 if (world == 1 or args.no_peer) else q
     table = ShardedClosedHashmap(nb, device=device, rehash_threshold=0.95, peer_capacity_rows=peer_rows, **fixed_parameters())
-
-    # ---- build (untimed): rank r inserts key indices [r * n_keys, (r + 1) * n_keys), routed to their owners
-    chunk = min(n_keys, 1 << 25)
-    for lo in range(rank * n_keys, (rank + 1) * n_keys, chunk):
-        idx = torch.arange(lo, lo + chunk, device=device, dtype=torch.long)
-        table.set(mix62_torch(idx)[:, None], value_of_index(idx, torch), assume_unique=True)
-    del idx
+    build_table(torch, table, n_keys, rank, device)
     assert table.n_elements == total_keys, "build lost keys"
-
-    # ---- batches
+    batches = make_batches(torch, device, n_batches, q, total_keys, rank)
     n_hit = int(q * HIT_FRACTION)
-    g = torch.Generator(device=device).manual_seed(1234 + rank)
-    batches = []
-    for b in range(N_BATCHES):
-        j = torch.arange(n_hit, device=device, dtype=torch.long)
-        hit_idx = (j * 7919 + 104729 * (b + 1) + 15485863 * rank) % total_keys
-        base = (b << 32) + (rank << 28)
-        miss_idx = (1 << 40) + base + torch.arange(q - n_hit, device=device, dtype=torch.long)
-        new_idx = (1 << 41) + base + torch.arange(q - n_hit, device=device, dtype=torch.long)
-        perm = torch.randperm(q, device=device, generator=g)
-        get_idx = torch.cat([hit_idx, miss_idx])[perm]
-        set_idx = torch.cat([hit_idx, new_idx])[perm]
-        batches.append({
-            "get_keys": mix62_torch(get_idx)[:, None].contiguous(), "get_idx": get_idx,
-            "set_keys": mix62_torch(set_idx)[:, None].contiguous(), "set_values": value_of_index(set_idx, torch).contiguous(),
-            "fresh_keys": mix62_torch(new_idx)[:, None].contiguous(),
-        })
-    del j, hit_idx, miss_idx, new_idx, perm, set_idx
 
     def barrier():
         if world > 1:
@@ -425,38 +563,54 @@ def run_candidate(args):
     pipelined = world > 1 and not args.no_peer and not args.no_pipeline
 
     def step(b, events=None):
-        d = batches[b % N_BATCHES]
+        d = batches[b % n_batches]
         if pipelined and events is None:
-            # one submission: the send stage of each operation overlaps the table work of the one before
-            # (wait=False: the first send of the next step may overlap this step's last table work; the timed loop
-            # and the check wait once, at their end)
+            # one submission per step, not waited for: the host only enqueues, the send stage of each operation
+            # overlaps the table work of the one before, also across steps (the timed loop waits once, at its end)
             (values, found), _, _ = table.run([("get", d["get_keys"]), ("set", d["set_keys"], d["set_values"]),
                                                ("remove", d["fresh_keys"])], wait=False)
             return values, found
-        if events is not None:
-            events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        marks[0].record()
         values, found = table.get(d["get_keys"])
-        if events is not None:
-            events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
+        marks[1].record()
         table.set(d["set_keys"], d["set_values"])
-        if events is not None:
-            events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
+        marks[2].record()
         table.remove(d["fresh_keys"])
+        marks[3].record()
         if events is not None:
-            events.append(torch.cuda.Event(enable_timing=True)); events[-1].record()
+            events.extend(marks)
         return values, found
 
-    # ---- correctness of what is being timed (first batch, before any timing)
+    # ---- correctness of what is being timed (first batch, before any timing): every operation against what the
+    # synthetic data says it must return, through the same calls (and, with several GPUs, the same exchange)
+    d0 = batches[0]
     values, found = step(0)
     if pipelined:
         table.wait()
-    d0 = batches[0]
     expect_found = d0["get_idx"] < (1 << 40)
     checks = {"found_flags_ok": bool(torch.equal(found, expect_found)),
               "hit_values_ok": bool(torch.equal(values[expect_found], value_of_index(d0["get_idx"][expect_found], torch))),
               "miss_values_zero": bool((values[~expect_found] == 0).all()),
               "n_elements_stationary": table.n_elements == total_keys}
-    del values, found, expect_found
+    del values, found
+    marked = d0["set_values"] + 0.5                                   # values no other row carries
+    table.set(d0["set_keys"], marked)
+    back, back_found = table.get(d0["set_keys"])
+    checks["set_then_get_returns_set_values"] = bool(back_found.all()) and bool(torch.equal(back, marked))
+    checks["n_elements_after_insert"] = table.n_elements == total_keys + (q - n_hit) * world
+    checks["remove_reports_every_inserted_row"] = bool(table.remove(d0["fresh_keys"]).all())
+    checks["second_remove_reports_none"] = not bool(table.remove(d0["fresh_keys"]).any())
+    stored = d0["set_idx"] < (1 << 40)
+    table.set(d0["set_keys"][stored], d0["set_values"][stored])       # the original values back
+    if world > 1 and not args.no_peer:
+        # a batch that does not fit its slices: skipped by every rank on the device, repeated over the all-to-all exchange
+        (v_over, f_over), = table.run([("get", d0["get_keys"])], _force_overflow=True)
+        checks["overflow_fallback_ok"] = bool(torch.equal(f_over, expect_found)) and bool(
+            torch.equal(v_over[expect_found], value_of_index(d0["get_idx"][expect_found], torch)))
+        del v_over, f_over
+    checks["n_elements_restored"] = table.n_elements == total_keys
+    del back, back_found, marked, stored, expect_found
 
     sampler = ClockSampler(local_rank) if rank == 0 else None      # started early: its start-up must not fall into the timed region
     for s in range(1, args.warmup):
@@ -484,8 +638,8 @@ def run_candidate(args):
     elapsed_ms = torch.tensor([t_start.elapsed_time(t_stop)], device=device)
     phase_steps = args.steps
     if pipelined:
-        # the timed steps were single pipelined submissions; the per-operation times come from a short separate
-        # pass that calls the operations one after the other (they add up to more than a pipelined step)
+        # the timed steps were pipelined submissions; the per-operation times come from a short separate pass that
+        # calls the operations one after the other (they add up to more than a pipelined step)
         phase_steps = 3
         step(0, [])                                   # warm the sequential path (allocator pools of the main stream)
         barrier()
@@ -509,10 +663,17 @@ def run_candidate(args):
     # ---- end to end: host (pinned) buffers in, host buffers out, through the public API
     e2e = None
     if not args.no_e2e:
-        host = [{k: v.cpu().pin_memory() for k, v in d.items() if k != "get_idx"} for d in batches[:2]]
-        out_values = torch.empty(q, 2, dtype=torch.float32).pin_memory()
-        out_found = torch.empty(q, dtype=torch.bool).pin_memory()
-        h2d = sum(host[0][k].numel() * host[0][k].element_size() for k in ("get_keys", "set_keys", "set_values", "fresh_keys"))
+        names = ("get_keys", "set_keys", "set_values", "fresh_keys")
+        host = []
+        for d in batches[:2]:
+            h = {}
+            for k in names:
+                h[k] = torch.empty(d[k].shape, dtype=d[k].dtype, pin_memory=True)
+                h[k].copy_(d[k])
+            host.append(h)
+        out_values = torch.empty(q, 2, dtype=torch.float32, pin_memory=True)
+        out_found = torch.empty(q, dtype=torch.bool, pin_memory=True)
+        h2d = sum(host[0][k].numel() * host[0][k].element_size() for k in names)
         d2h = out_values.numel() * 4 + out_found.numel()
 
         # what the host link gives when every rank copies at once and nothing else runs: the bound of the e2e leg
@@ -532,14 +693,14 @@ def run_candidate(args):
 
         from doksparse_b200.host_batch import HostBatch
         # chunks of 4 Mi rows on three streams (copy in | kernels | copy out); routed batches use larger chunks
-        pipe = HostBatch(table, device, chunk_rows=(1 << 22) if world == 1 else (1 << 23))
+        pipe = HostBatch(table, device, chunk_rows=(1 << 22) if world == 1 else min(q, 1 << 23))
 
         def e2e_step(b):
             h = host[b % 2]
             pipe.run([("get", h["get_keys"], out_values, out_found), ("set", h["set_keys"], h["set_values"]),
                       ("remove_rows", h["fresh_keys"])])
 
-        e2e_steps = max(3, min(args.steps, 10))
+        e2e_steps = max(3, min(args.steps, 10 if q < (1 << 27) else 4))
         e2e_step(0)
         pipe.join()
         barrier()
@@ -551,7 +712,11 @@ def run_candidate(args):
         pipe.join()
         t1.record()
         barrier()
-        e2e_checks = {"e2e_found_ok": bool(torch.equal(out_found.to(device), batches[e2e_steps % 2]["get_idx"] < (1 << 40)))}
+        last = e2e_steps % 2
+        e2e_found = out_found.to(device)
+        e2e_checks = {"e2e_found_ok": bool(torch.equal(e2e_found, batches[0]["get_idx"] < (1 << 40))) if last == 0 else
+                      int(e2e_found.sum()) == n_hit}
+        del e2e_found
         e_ms = torch.tensor([t0.elapsed_time(t1)], device=device)
         if world > 1:
             dist.all_reduce(e_ms, op=dist.ReduceOp.MAX)
@@ -562,23 +727,20 @@ def run_candidate(args):
                "h2d_gbs_per_gpu": h2d / (float(e_ms.item()) / e2e_steps * 1e-3) / 1e9,
                "h2d_copy_only_gbs_per_gpu": float(probe_gbs.item()),   # all ranks copying at once, slowest rank
                **e2e_checks}
+        del host, out_values, out_found, pipe
 
-    # ---- what the hardware gives a probing kernel: independent random 16-byte reads over this GPU's slot array
-    slots = table.ops.local._slots
-    n_reads = 1 << 26
-    lib = L.lib()
-    lib.dok_diag_random_reads(L.ptr(slots), slots.numel(), n_reads, 1, None, L.stream_ptr(device))
-    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    r0.record()
-    for rep in range(3):
-        lib.dok_diag_random_reads(L.ptr(slots), slots.numel(), n_reads, 100 + rep, None, L.stream_ptr(device))
-    r1.record()
-    torch.cuda.synchronize()
-    request_ceiling = 3 * n_reads / (r0.elapsed_time(r1) * 1e-3) / 1e9          # G requests/s, this GPU
+    # ---- what the hardware gives a probing kernel: independent random 16-byte reads over this GPU's slot array, over
+    # all of it and over one window of it (tables beyond the TLB's reach are served window by window)
+    local = table.ops.local
+    slots = local._slots
+    passes = L.lib().dok_table_passes(local._c_table())
+    ceiling_whole = random_request_rate(torch, L, slots, slots.numel(), device)
+    ceiling_window = ceiling_whole if passes <= 1 else random_request_rate(torch, L, slots, slots.numel() // passes, device)
+    probe_len, _ = local.probe_stats(batches[0]["get_keys"][: 1 << 22]) if world == 1 else (None, None)
 
     # ---- roofline of the dominant kernel and of the other two
     peak, peak_source = measured_peak_gbs()
-    local_rows = {"get": q, "set": q, "remove": q - n_hit}       # rows each GPU processes per step (weak scaling)
+    local_rows = {"get": q, "set": q, "remove": q - n_hit}       # rows each GPU processes per step
     kernel_ms = {"get": get_ms, "set": set_ms, "remove": remove_ms}
     per_kernel = {}
     for op in ("get", "set", "remove"):
@@ -586,36 +748,56 @@ def run_candidate(args):
         gops = local_rows[op] / (kernel_ms[op] * 1e-3) / 1e9
         per_kernel[op] = {"ms": kernel_ms[op], "mops_per_gpu": gops * 1e3, "bytes_per_op": algorithmic_bytes(op),
                           "achieved_gbs": achieved, "frac": achieved / peak,
-                          "frac_of_random_request_ceiling": gops / request_ceiling}
+                          "frac_of_random_request_ceiling": gops / ceiling_window}
         if TRAFFIC_BYTES_PER_OP.get(op) and world == 1:
-            # what DRAM really moves (ncu: whole 128-byte lines per probed group), as a rate and against the peak
-            dram = TRAFFIC_BYTES_PER_OP[op] * local_rows[op] / (kernel_ms[op] * 1e-3) / 1e9
+            # what DRAM really moves (ncu: a whole 128-byte line per probed group), as a rate and against the peak;
+            # a table served in several passes reads the batch once per pass
+            extra = (passes - 1) * (KEY_BYTES if op != "set" else KEY_BYTES + VALUE_BYTES) if passes > 1 else 0
+            dram = (TRAFFIC_BYTES_PER_OP[op] + extra) * local_rows[op] / (kernel_ms[op] * 1e-3) / 1e9
             per_kernel[op].update({"dram_traffic_gbs": dram, "dram_traffic_frac": dram / peak})
     top = max(kernel_ms, key=kernel_ms.get)
     roofline = {"bound": "hbm", "kernel": {"get": "k_get", "set": "k_set_claim (+ k_set_resolve, idle without duplicates)",
                                            "remove": "k_find<remove>"}[top],
                 "achieved": per_kernel[top]["achieved_gbs"], "peak": peak, "unit": "GB/s", "frac": per_kernel[top]["frac"],
-                "traffic": TRAFFIC_BYTES_PER_OP.get(top, 0) * local_rows[top] if TRAFFIC_BYTES_PER_OP.get(top) else None,
-                "peak_source": peak_source,
-                "random_request_ceiling_greq_s": request_ceiling,
+                "traffic": TRAFFIC_BYTES_PER_OP.get(top, 0) * local_rows[top] * passes if TRAFFIC_BYTES_PER_OP.get(top) else None,
+                "peak_source": peak_source, "launches_per_operation": passes,
+                "random_request_ceiling_greq_s": ceiling_window,
+                "random_request_ceiling_whole_table_greq_s": ceiling_whole,
+                "table_passes": passes,
                 "note": ("phase time includes routing and exchange when shards > 1" +
                          (", measured with the operations called one after the other (the timed steps pipeline them); "
                           if pipelined else "; ") if world > 1 else "") +
-                        "DRAM serves a random access with a whole 128-byte line (~48 G lines/s = the HBM bandwidth), "
-                        "so a probing kernel is bound by lines touched per operation, not by the bytes it needs: "
-                        "see kernels.*.dram_traffic_frac for the share of the HBM peak each kernel really moves"}
+                        "DRAM answers a random access with a whole 128-byte line whatever the request size (ncu: 122.7 B "
+                        "read per 8-byte request, unchanged by cudaLimitMaxL2FetchGranularity), so a probing kernel is "
+                        "bound by lines touched per operation (~46 G lines/s = the HBM bandwidth), not by the bytes it "
+                        "needs; a slot array beyond the 64 GiB the TLB covers is served in passes over windows "
+                        "(table_passes), see kernels.*.dram_traffic_frac for the share of the HBM peak each kernel moves"}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        _, _, cpu_baseline = cpu_arm(steps=4, warmup=1, budget_s=25.0)
+        _, _, cpu_baseline = cpu_arm(steps=4, warmup=1, sample_keys_log2=CPU_SAMPLE_KEYS_LOG2,
+                                     sample_batch_log2=CPU_SAMPLE_BATCH_LOG2, budget_s=25.0)
+
+    extra = {}
+    if rank == 0 and world == 1:
+        table.close()
+        del table, local, slots, batches
+        torch.cuda.empty_cache()
+        if args.scaling == "strong" and not args.no_shard_point:
+            extra["shard_point"] = shard_point(torch, device)
+            torch.cuda.empty_cache()
+        if not args.no_extras:
+            import bench_configs
+            extra["configs"] = bench_configs.run_all(torch, device, measured_peak_gbs()[0])
 
     if rank == 0:
         line = {
             "metric": "hashmap get/set Mops/s", "value": value, "unit": "Mops/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "int64", "data": "synthetic", "config": workload_config(args, world),
             "roofline": roofline, "kernels": per_kernel, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks, "checks": checks,
+            "mean_probe_groups": probe_len, **extra,
         }
         print(json.dumps(line))
     if world > 1:

@@ -41,7 +41,7 @@ class CudaClosedHashmap:
         key_perm=None,
         rehash_factor=2.0,
         rehash_threshold=0.75,
-        tombstone_threshold=None,
+        tombstone_threshold="auto",
     ):
         self._empty_marker = -1
         self._removed_marker = -3
@@ -74,10 +74,12 @@ class CudaClosedHashmap:
         self._rehash_factor = rehash_factor
         self._rehash_threshold = rehash_threshold
         # Tombstone-aware maintenance (no counterpart in the reference, whose rehash looks at live items only,
-        # cuda_closed_hashmap.py:365, so that chains only ever grow under churn): with a threshold t, a removal that
-        # leaves live + tombstone slots above t * n_buckets rebuilds the table at its size, which drops the tombstones.
-        # Off by default: a rebuild draws new hash parameters, which a bit-for-bit comparison with the reference
-        # would see.
+        # cuda_closed_hashmap.py:365: under insert / remove churn its empty slots run out, miss lookups walk ever longer
+        # chains, and with none left they walk the whole table).  A removal that leaves live + tombstone slots above
+        # t * n_buckets rebuilds the table IN PLACE: same size, same hash parameters (nothing is drawn from the random
+        # state), same contents, no tombstones -- invisible to the caller except through `n_tombstones` and `_uuid`.
+        # "auto" (the default): t = 0.95, and only once the tombstones are worth a rebuild (2 % of the buckets).
+        # None: never (the reference's behaviour).  A number: that t, for any number of tombstones.
         self._tombstone_threshold = tombstone_threshold
         self._n_tombstones = torch.zeros(size=(), device=self.device, dtype=torch.long)   # upper bound, on the device
         self._tombstone_host_bound = 0                                                  # looser bound, on the host
@@ -346,6 +348,18 @@ class CudaClosedHashmap:
                         "dok_map_compact_scatter")
         return k, v, u
 
+    def count_live(self):
+        """Live slots, counted by the compaction's first pass (one read of the tags, tile sums, one scan) instead of
+        a mask tensor plus a reduction."""
+        if self._slots is None:
+            return 0
+        lib = L.lib()
+        with torch.cuda.device(self.device):
+            tiles = lib.dok_compact_tiles(self._n_buckets)
+            offsets = torch.empty(tiles + 1, device=self.device, dtype=torch.long)
+            L.check(lib.dok_map_compact_count(self._c_table(), L.ptr(offsets), L.stream_ptr(self.device)), "dok_map_compact_count")
+            return int(offsets[-1].item())
+
     @property
     def nonempty_mask(self):
         return (self._uuid != self._empty_marker) & (self._uuid != self._removed_marker)
@@ -590,6 +604,21 @@ class CudaClosedHashmap:
         self._shared["snapshots"].clear()
         self._shared["bound"] = n_elements + n_new
 
+    def set_rows(self, keys, values, assume_unique=False):
+        """Kernel only, like `remove_rows`: insert-or-assign without the reference's bookkeeping around it -- no count
+        of the distinct new keys, no rehash decision, no host synchronisation.  New slots are counted on the device.
+        The caller guarantees room (rows that find the table full are counted in `last_set_failed`)."""
+        assert keys.shape[0] == values.shape[0]
+        if self._slots is None:
+            self._allocate(keys.shape[1:], keys.dtype, values.shape[1:], values.dtype)
+        assert keys.dtype == self._key_dtype and keys.shape[1:] == self._key_shape and keys.device == self.device
+        assert values.dtype == self._value_dtype and values.shape[1:] == self._value_shape and values.device == self.device
+        if keys.shape[0] == 0:
+            return
+        self._materialise_parameters()
+        cnt = self._launch_set(keys.contiguous(), values.contiguous(), assume_unique)
+        self._account_set(cnt, keys.shape[0])
+
     def _account_set(self, cnt, rows):
         """Device-side bookkeeping after a set launch that cannot have triggered a rehash."""
         self._n_elements += cnt[L.CNT_CLAIMED_EMPTY] + cnt[L.CNT_REUSED_REMOVED]
@@ -733,17 +762,53 @@ class CudaClosedHashmap:
         return is_removed
 
     def _maintain(self):
-        """Rebuild at the same size when live + tombstone slots exceed tombstone_threshold * n_buckets.  The host
-        first looks at its own upper bounds (no synchronisation) and reads the device counts only when they cross."""
+        """Rebuild in place when live + tombstone slots exceed the tombstone threshold.  The host first looks at its
+        own upper bounds (no synchronisation) and reads the device counts only when they cross."""
         if self._tombstone_threshold is None or self._slots is None:
             return
-        limit = self._tombstone_threshold * self.n_buckets
-        if self._element_bound() + self._tombstone_host_bound <= limit:
+        auto = self._tombstone_threshold == "auto"
+        limit = (0.95 if auto else self._tombstone_threshold) * self.n_buckets
+        least = max(1, int(0.02 * self.n_buckets)) if auto else 1
+        if self._tombstone_host_bound < least or self._element_bound() + self._tombstone_host_bound <= limit:
             return
         tombstones = int(self._n_tombstones.item())
         self._tombstone_host_bound = tombstones
-        if self.n_elements + tombstones > limit and tombstones > 0:
-            self.rehash(self.n_buckets)
+        if tombstones >= least and self.n_elements + tombstones > limit:
+            try:
+                self.rebuild()
+            except torch.OutOfMemoryError:
+                import warnings
+                warnings.warn("no room for a second slot array: the table keeps its tombstones "
+                              f"({tombstones} of {self.n_buckets} buckets)")
+                self._tombstone_host_bound = 0
+
+    def rebuild(self):
+        """The same table without its tombstones: a fresh slot array of the same geometry, every live slot re-inserted
+        with the SAME hash parameters (one kernel, dok_map_reinsert).  Lookups, sizes and parameters are unchanged;
+        shallow clones made before keep the old slot array (as after a rehash in the reference)."""
+        if self._slots is None:
+            return
+        old_slots, old_stamp = self._slots, self._shared["stamp"]
+        source = L.Table()
+        source.slots = old_slots.data_ptr()
+        source.stamp = old_stamp.data_ptr() if old_stamp is not None else None
+        source.n_buckets = self._n_buckets
+        source.slot_bytes = self._layout.slot_bytes
+        source.value_bytes, source.key_bytes = self._value_bytes, self._key_bytes
+        fresh = torch.empty(self._layout.total_bytes, device=self.device, dtype=torch.uint8)     # may raise: nothing changed yet
+        self._slots = fresh
+        self._shared["stamp"] = None
+        self._shared["epoch"] = 0
+        cnt = self._counters()
+        with torch.cuda.device(self.device):
+            st = L.stream_ptr(self.device)
+            L.check(L.lib().dok_map_init(self._c_table(), st), "dok_map_init")
+            L.check(L.lib().dok_map_reinsert(ctypes.byref(source), self._c_table(), self._c_hash(), L.ptr(cnt), st),
+                    "dok_map_reinsert")
+        old_slots.record_stream(torch.cuda.current_stream(self.device))
+        self._n_failed += cnt[L.CNT_FAILED]
+        self._n_tombstones.zero_()
+        self._tombstone_host_bound = 0
 
     @property
     def tombstone_bound(self):
@@ -772,7 +837,7 @@ class CudaClosedHashmap:
                           rehash_factor=self._rehash_factor, rehash_threshold=self._rehash_threshold,
                           tombstone_threshold=self._tombstone_threshold)
             return
-        live = int((self._uuid >= 0).sum().item())
+        live = self.count_live()
         old_slots, old_stamp = self._slots, self._shared["stamp"]          # kept alive until the kernel has run
         source = L.Table()
         source.slots = old_slots.data_ptr()

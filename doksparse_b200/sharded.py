@@ -671,6 +671,9 @@ class ShardedClosedHashmap:
                         results[k][1].copy_(again[1])
                     elif op[0] == "remove":
                         results[k].copy_(again)
+        maintain = getattr(self.ops.local, "_maintain", None)
+        if maintain is not None:
+            maintain()              # the sliced removals only counted their tombstones; rebuild here if it is time
 
     def _settle(self):
         """Anything still in flight from a submission that was not waited for is completed (and, if it overflowed,

@@ -430,7 +430,7 @@ class SparseDOKTensor(object):
         hashmap = self._hashmap
         if hashmap._values is None:
             return SparseDOKTensor(size=new_shape, device=self.device, dtype=self.dtype)
-        live = int((hashmap._uuid >= 0).sum().item())
+        live = hashmap.count_live()
         out = CudaClosedHashmap(n_buckets=next_power_of_2(live), device=self.device)
         out._begin_bulk_insert((len(new_shape),), torch.long, (1,), self.dtype, live)
         if live:
@@ -457,7 +457,7 @@ class SparseDOKTensor(object):
         if len(new_shape) == 1:
             return self.flatten()
         if self._hashmap._values is not None:
-            live = int((self._hashmap._uuid >= 0).sum().item())
+            live = self._hashmap.count_live()
             util.consume_fresh_map_draws(next_power_of_2(live), 1, live)
         return self._rekeyed(new_shape)
 

@@ -402,8 +402,8 @@ def test_large_roundtrip_properties():
 
 
 def test_tombstone_aware_maintenance():
-    """With tombstone_threshold the table is rebuilt at its size once live + tombstone slots exceed it: tombstones go,
-    contents stay.  Without it (the reference's behaviour) tombstones only accumulate."""
+    """With a tombstone threshold the table is rebuilt in place once live + tombstone slots exceed it: tombstones go;
+    contents, size and hash parameters stay.  With None (the reference's behaviour) tombstones only accumulate."""
     from doksparse_b200 import CudaClosedHashmap
     rng = np.random.default_rng(3)
     nb = 1 << 16
@@ -431,11 +431,39 @@ def test_tombstone_aware_maintenance():
         got = {int(a): tuple(b) for a, b in zip(host(keys)[:, 0], host(vals))}
         assert got == live
         tables[name] = table
-    # a rebuild draws new hash parameters: that is how it shows from outside
+    # a rebuild keeps the hash parameters and draws nothing from the random state
     assert int(tables["plain"].prime2[0]) == first_prime["plain"]
-    assert int(tables["maintained"].prime2[0]) != first_prime["maintained"]
+    assert int(tables["maintained"].prime2[0]) == first_prime["maintained"] == first_prime["plain"]
     assert tables["maintained"].n_tombstones < tables["plain"].n_tombstones
     assert tables["maintained"].n_elements + tables["maintained"].n_tombstones <= 0.4 * nb + 10000
+
+
+def test_default_maintenance_keeps_a_churned_table_from_running_out_of_empty_slots():
+    """Insert / remove churn at high load uses up the empty slots of a table that never rebuilds (the reference's
+    behaviour, tombstone_threshold=None): in the end a miss walks the whole table.  The default rebuilds in place
+    before that, with identical answers."""
+    from doksparse_b200 import CudaClosedHashmap
+    rng = np.random.default_rng(5)
+    nb = 1 << 12
+    params = good_parameters(nb, 1, seed=9)
+    plain = CudaClosedHashmap(n_buckets=nb, device="cuda:0", rehash_threshold=2.0, tombstone_threshold=None, **params)
+    kept = CudaClosedHashmap(n_buckets=nb, device="cuda:0", rehash_threshold=2.0, **params)
+    base = rng.permutation(1 << 30)[:3000].astype(np.int64)[:, None]
+    for t in (plain, kept):
+        t.set(dev(base), dev(np.ones((3000, 1), np.float32)))
+    for step in range(40):                                  # 500 fresh keys in, the same 500 out again
+        fresh = rng.permutation(1 << 30)[:500].astype(np.int64)[:, None] + (1 << 31)
+        for t in (plain, kept):
+            t.set(dev(fresh), dev(np.full((500, 1), step, np.float32)))
+            assert bool(t.remove_rows(dev(fresh)).all())
+    assert plain.n_tombstones + plain.n_elements >= 0.99 * nb          # no empty slot left to stop a miss
+    assert kept.n_tombstones + kept.n_elements <= 0.95 * nb + 500
+    probe = dev(rng.permutation(1 << 30)[:2000].astype(np.int64)[:, None] + (1 << 32))
+    (pv, pf), (kv, kf) = plain.get(probe), kept.get(probe)
+    assert not pf.any() and not kf.any()
+    assert plain.probe_stats(probe)[0] > 20 * kept.probe_stats(probe)[0]
+    (pv, pf), (kv, kf) = plain.get(dev(base)), kept.get(dev(base))
+    assert pf.all() and kf.all() and torch.equal(pv, kv)
 
 
 def test_state_dict_round_trip(tmp_path):
