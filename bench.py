@@ -376,15 +376,6 @@ def run_reference(args):
         return
     mops, ms, desc = cpu_arm(args.steps, args.warmup, CPU_SAMPLE_KEYS_LOG2, CPU_SAMPLE_BATCH_LOG2)
     gpu_leg = None if args.no_ref_gpu else reference_kernels_on_gpu()
-    gpu_configs = None
-    if not args.no_ref_gpu and not args.no_extras and isinstance(gpu_leg, dict):
-        try:
-            import torch
-            import bench_configs
-            torch.cuda.empty_cache()
-            gpu_configs = bench_configs.run_reference_kernels(torch, torch.device("cuda", 0))
-        except Exception as exc:
-            gpu_configs = f"{type(exc).__name__}: {exc}"
     config = workload_config(args, world=args.gpus)
     # what this arm really ran: a bounded sample of the workload on the host cores
     config.update({"sample_of_workload": True, "sample_keys": 1 << CPU_SAMPLE_KEYS_LOG2, "sample_batch": 1 << CPU_SAMPLE_BATCH_LOG2,
@@ -399,7 +390,6 @@ def run_reference(args):
         "gpu_launches": 0,
         # extra: the same reference kernel text run on this box's GPU (kernel-only, 1 GPU); not the line's value
         "reference_kernels_gpu": gpu_leg,
-        "reference_kernels_gpu_configs": gpu_configs,
     }
     print(json.dumps(line))
 

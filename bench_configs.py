@@ -3,8 +3,11 @@ their full sizes, each with its operation rates and the fraction of the HBM byte
 (bytes per operation as in bench.algorithmic_bytes; streaming passes = bytes read + bytes written).  Seeded synthetic
 inputs with the configurations' shapes, sizes and value distributions; none of this is in the timed headline.
 
-`run_all` is the candidate's side.  `run_reference_kernels` (used by `bench.py --impl reference`) times the
-reference's own kernels on the GPU for the two configurations its 32-bit indices can hold (1' and 4)."""
+The reference's own kernels are not run on these configurations: 2, 3 and the 2^31-key table exceed its 32-bit
+indices, and at config 4's load of 0.9 its bucket hash -- a value in [0, prime1), prime1 between n_buckets and
+2 * n_buckets, folded with `% n_buckets` (closed_hashmap_impl_class.cu:87-96, cuda_closed_hashmap.py:66-76), which
+doubles the key density of the first prime1 - n_buckets buckets -- overfills that part of the table, so that one probe
+cluster spans a large share of it and the pre-fill alone did not finish within a quarter of an hour on a B200."""
 import time
 
 import numpy as np
@@ -277,61 +280,4 @@ def run_all(torch, device, peak):
         except Exception as exc:                                # the headline line must still be printed
             out[name] = {"error": f"{type(exc).__name__}: {exc}"}
         torch.cuda.empty_cache()
-    return out
-
-
-# ---------------------------------------------------------------------------------------------------------------
-# reference arm: the reference's own kernels on the GPU, where its 32-bit indices allow
-# ---------------------------------------------------------------------------------------------------------------
-
-def run_reference_kernels(torch, device):
-    from oracle import ref_gpu
-    out = {}
-    # config 1'
-    if ref_gpu.available(torch.float32, 3, torch.int64, 5):
-        n_keys, q = 1 << C1_KEYS_LOG2, 1 << C1_BATCH_LOG2
-        np.random.seed(1)
-        from oracle import port
-        params = port.draw_hash_parameters(1 << (C1_KEYS_LOG2 + 1), 3)
-        table = ref_gpu.RefGpuMap(1 << (C1_KEYS_LOG2 + 1), torch.float32, 3, torch.int64, 5, params, device)
-        for lo in range(0, n_keys, 1 << 24):
-            idx = torch.arange(lo, lo + (1 << 24), device=device)
-            table.set(c1_keys(torch, idx), c1_values(torch, idx))
-        idx, absent, doomed = c1_batches(torch, device)
-        keys, values = c1_keys(torch, idx), c1_values(torch, idx)
-        absent_keys, doomed_keys = c1_keys(torch, absent), c1_keys(torch, doomed)
-        _, found = table.get(keys)
-        out["config1_prime"] = {"results_ok": bool(torch.equal(found, idx < (1 << 40))),
-                                "get_ms": _timed(torch, lambda: table.get(keys), 5),
-                                "set_ms": _timed(torch, lambda: table.set(keys, values), 1, warm=0),
-                                "remove_of_inserted_ms": _timed(torch, lambda: table.remove(absent_keys), 1, warm=0),
-                                "remove_ms": _timed(torch, lambda: table.remove(doomed_keys), 1, warm=0)}
-        del table
-        torch.cuda.empty_cache()
-    # config 4 (kernels only, 5 batches: the reference's set kernel is racy on duplicates, results are not compared)
-    if ref_gpu.available(torch.int64, 1, torch.float32, 4):
-        g = torch.Generator(device=device).manual_seed(0)
-        n_fill = int(0.9 * C4_CAP)
-        np.random.seed(0)
-        from oracle import port
-        params = port.draw_hash_parameters(C4_CAP, 1)
-        table = ref_gpu.RefGpuMap(C4_CAP, torch.int64, 1, torch.float32, 4, params, device)
-        live = torch.arange(n_fill, device=device, dtype=torch.long) * 61 + 7
-        for lo in range(0, n_fill, 1 << 26):
-            part = live[lo:lo + (1 << 26)]
-            table.set(part[:, None].contiguous(), c4_value_of(torch, part))
-        del live
-        get_ms, set_ms, rem_ms = [], [], []
-        for batch in range(5):
-            ids = bounded_zipf(torch, g, 64_000_000, 1 << 34, 0.99, device)
-            gets, sets, rems = ids[:44_800_000, None].contiguous(), ids[44_800_000:57_600_000, None].contiguous(), ids[57_600_000:, None].contiguous()
-            sv = c4_value_of(torch, sets[:, 0])
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-            ev[0].record(); table.get(gets)
-            ev[1].record(); table.set(sets, sv)
-            ev[2].record(); table.remove(rems)
-            ev[3].record(); torch.cuda.synchronize()
-            get_ms.append(ev[0].elapsed_time(ev[1])); set_ms.append(ev[1].elapsed_time(ev[2])); rem_ms.append(ev[2].elapsed_time(ev[3]))
-        out["config4"] = {"get_ms": float(np.mean(get_ms)), "set_kernel_ms": float(np.mean(set_ms)),
-                          "remove_kernel_ms_with_duplicates": float(np.mean(rem_ms)), "batches": 5}
     return out
