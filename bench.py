@@ -62,6 +62,14 @@ def parse_args():
     ap.add_argument("--no-shard-point", action="store_true",
                     help="1 GPU, strong scaling: skip the extra leg on a 2^28-key table (the size the reference's kernels can hold)")
     ap.add_argument("--no-extras", action="store_true", help="1 GPU: skip the legs on BASELINE configs 1', 2, 3 and 4")
+    ap.add_argument("--hw-probe", action="store_true",
+                    help="instead of the benchmark: rate of random requests of 8..128 bytes over buffers of --probe-mib "
+                         "MiB (what bounds every probing kernel); one JSON line")
+    ap.add_argument("--probe-mib", type=int, nargs="+", default=[256, 1024, 4096, 16384, 65536, 73728, 81920, 98304, 116736])
+    ap.add_argument("--probe-requests-log2", type=int, default=25)
+    ap.add_argument("--probe-reps", type=int, default=5)
+    ap.add_argument("--l2-fetch-granularity", type=int, default=0,
+                    help="--hw-probe: cudaDeviceSetLimit(cudaLimitMaxL2FetchGranularity, N) for this process first (32/64/128)")
     args = ap.parse_args()
     if args.keys_log2 is None:
         args.keys_log2 = 31 if args.scaling == "strong" else 28
@@ -794,9 +802,59 @@ def run_candidate(args):
         dist.destroy_process_group()
 
 
+def hw_probe(args):
+    """Random-request rates of this GPU: the physical ceiling the roofline discussion rests on.  For every footprint
+    and request shape, G requests/s over a buffer of that size.  Run under `ncu --metrics dram__bytes_read.sum` (one
+    small footprint, --probe-reps 1) the same launches give the DRAM bytes per request."""
+    import ctypes
+    import torch
+    from doksparse_b200 import _lib as L
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    torch.zeros(1, device=device)
+    limit = {"requested": args.l2_fetch_granularity}
+    cudart = ctypes.CDLL("libcudart.so.12")
+    if args.l2_fetch_granularity:
+        limit["set_rc"] = cudart.cudaDeviceSetLimit(5, ctypes.c_size_t(args.l2_fetch_granularity))    # cudaLimitMaxL2FetchGranularity
+    got = ctypes.c_size_t(0)
+    cudart.cudaDeviceGetLimit(ctypes.byref(got), 5)
+    limit["reads_back"] = got.value
+    shapes = [(8, 1), (16, 1), (32, 1), (32, 2), (32, 4), (16, 4)]
+    n = 1 << args.probe_requests_log2
+    lib = L.lib()
+    rows = []
+    for mib in args.probe_mib:
+        try:
+            buf = torch.empty(mib << 20, device=device, dtype=torch.uint8)
+        except torch.OutOfMemoryError:
+            rows.append({"mib": mib, "error": "out of memory"})
+            continue
+        buf.fill_(1)
+        row = {"mib": mib}
+        for b, lanes in shapes:
+            if args.probe_reps > 1:
+                L.check(lib.dok_diag_random_requests(L.ptr(buf), buf.numel(), n, b, lanes, 1, None, L.stream_ptr(device)), "probe")
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for rep in range(args.probe_reps):
+                L.check(lib.dok_diag_random_requests(L.ptr(buf), buf.numel(), n, b, lanes, 100 + rep * n, None,
+                                                     L.stream_ptr(device)), "probe")
+            t1.record()
+            torch.cuda.synchronize()
+            row[f"{b * lanes}B_by_{lanes}_lane{'s' if lanes > 1 else ''}" + ("_16B_each" if (b, lanes) == (16, 4) else "")] = \
+                round(args.probe_reps * n / (t0.elapsed_time(t1) * 1e-3) / 1e9, 2)
+        rows.append(row)
+        del buf
+        torch.cuda.empty_cache()
+    print(json.dumps({"hw_probe": "G random requests per second", "requests_per_launch": n,
+                      "l2_fetch_granularity_limit": limit, "rows": rows}))
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.hw_probe:
+        hw_probe(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_candidate(args)

@@ -123,6 +123,7 @@ def _declare(lib):
         "dok_peer_close": ([P], I),
         "dok_shard_owner": ([HP, P, I64, I, P, P], I),
         "dok_diag_random_reads": ([P, I64, I64, ctypes.c_uint64, P, P], I),
+        "dok_diag_random_requests": ([P, I64, I64, I, I, ctypes.c_uint64, P, P], I),
     }
     for name, (argtypes, restype) in sig.items():
         fn = getattr(lib, name)

@@ -14,7 +14,7 @@
 // get
 // ---------------------------------------------------------------------------------------------------------
 template <int SB, int LW, class Keys>
-__global__ void __launch_bounds__(DOK_TPB, (LW == 2 ? 8 : 1)) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
+__global__ void __launch_bounds__(DOK_TPB, (LW == 2 ? (SB == 32 ? 8 : 6) : 1)) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
                                                     uint8_t *__restrict__ out_found, Fallback fb, ll_t *counters,
                                                     int count_probes) {
   __shared__ BlockTally tally;
@@ -67,10 +67,10 @@ inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, vo
   if (fallback) memcpy(&fb, fallback, (size_t)t.vb);
   const dim3 grid = dok_grid(keys);
   int rc = DOK_OK;
-  if (t.sb == 32 && t.vb <= 8)      // tag and value fit the first 16 bytes of the slot: half the load width
-    DOK_FOR_WINDOWS(t, rc, (k_get<32, 2, Keys><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, (char *)out_values, out_found, fb,
-                                                                         (ll_t *)counters, count_probes)));
-  else
+  if (t.vb <= 8 && t.sb <= 128) {   // tag and value fit the first 16 bytes of the slot: half the load width (or less)
+    DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_get<(SB == 0 ? 32 : SB), 2, Keys><<<grid, DOK_TPB, 0, st>>>(
+                                                  wt, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes))));
+  } else
     DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_get<SB, 4, Keys><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, (char *)out_values, out_found,
                                                                                            fb, (ll_t *)counters, count_probes))));
   return rc;

@@ -823,7 +823,12 @@ class CudaClosedHashmap:
         assert keys.dtype == self._key_dtype
         assert keys.device == self.device
         assert keys.shape[1:] == self.key_shape
-        unique_keys = keys.unique(dim=0)
+        if int(np.prod(self._key_shape)) == 1 and keys.dtype not in L.FLOAT_DTYPES:
+            # one integer column: a flat radix-sort unique gives the rows of `unique(dim=0)` in the same (sorted) order
+            # without the lexicographic row sort
+            unique_keys = torch.unique(keys.reshape(-1)).reshape((-1,) + tuple(self._key_shape))
+        else:
+            unique_keys = keys.unique(dim=0)
         return self.remove_rows(unique_keys)
 
     # ------------------------------------------------------------------ rehash

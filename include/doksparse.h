@@ -377,6 +377,11 @@ int dok_shard_unpermute(const void *grouped_values, const uint8_t *grouped_found
  * it gives the rate at which this GPU serves random requests; for buffers much larger than L2 that rate bounds
  * every probing kernel.  sink may be NULL.  No counterpart in the reference. */
 int dok_diag_random_reads(const void *buf, int64_t bytes, int64_t n_reads, uint64_t seed, int64_t *sink, void *stream);
+/* The same with a chosen request shape: `lanes` adjacent lanes read bytes_per_lane each of one random aligned unit
+ * (supported: 8x1, 16x1, 32x1, 32x2, 32x4, 16x4 = requests of 8 ... 128 bytes).  Under a profiler the DRAM bytes per
+ * request of the different shapes show the granule of a random access (128 bytes on B200, whatever is asked for). */
+int dok_diag_random_requests(const void *buf, int64_t bytes, int64_t n_requests, int bytes_per_lane, int lanes,
+                             uint64_t seed, int64_t *sink, void *stream);
 
 /* owner_out[i] = owner shard of row i (diagnostics; the partition computes the same value internally) */
 int dok_shard_owner(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, int32_t *owner_out,
