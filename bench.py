@@ -625,8 +625,10 @@ def run_candidate(args):
     barrier()
     t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
+    host_t0 = time.perf_counter()
     for s in range(args.steps):
         step(s + args.warmup, None if pipelined else events)
+    host_enqueue_ms = (time.perf_counter() - host_t0) * 1e3 / args.steps      # host time per step before the final wait
     if pipelined:
         table.wait()
     t_stop.record()
@@ -795,7 +797,7 @@ def run_candidate(args):
             "vs_baseline": None, "dtype": "int64", "data": "synthetic", "config": workload_config(args, world),
             "roofline": roofline, "kernels": per_kernel, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks, "checks": checks,
-            "mean_probe_groups": probe_len, **extra,
+            "mean_probe_groups": probe_len, "host_enqueue_ms_per_step": host_enqueue_ms, **extra,
         }
         print(json.dumps(line))
     if world > 1:

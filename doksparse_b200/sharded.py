@@ -184,13 +184,19 @@ class CudaShardOps:
         """Typed view of region `which` (0 inbox keys, 1 inbox values, 2 inbox counts, 3 result values, 4 result
         flags) of `rank`'s arena, generation 0 / 1, rows [row0, row0 + rows)."""
         p = self._sx
+        cache = p.setdefault("region_cache", {})
+        hit = cache.get((rank, generation, which, rows, row0))
+        if hit is not None:
+            return hit
+        asked = (rank, generation, which, rows, row0)
         total = p["world"] if which == 2 else p["world"] * p["slice_rows"]
         rows = total - row0 if rows is None else rows
         width, shape, dtype = [(p["kb"], p["kshape"], p["kdtype"]), (p["vb"], p["vshape"], p["vdtype"]), (8, (), torch.long),
                                (p["vb"], p["vshape"], p["vdtype"]), (1, (), torch.bool)][which]
         lo = generation * p["gen_bytes"] + p["offs"][which] + row0 * width
         flat = p["views"][rank][lo:lo + rows * width]
-        return flat.view(dtype).view((rows,) + tuple(shape))
+        cache[asked] = view = flat.view(dtype).view((rows,) + tuple(shape))
+        return view
 
     def sliced_send(self, keys, values, generation, want_dest, force_overflow=False):
         """SEND stage: owner of every row, then every row into its owner's inbox slice for this rank and this rank's
@@ -258,34 +264,41 @@ class CudaShardOps:
         lib = L.lib()
         p = self._sx
         w, rows, r = p["world"], p["slice_rows"], p["rank"]
-        counts = self._region(r, generation, 2)
-        order = ([s for s in range(w) if s != r] + [r]) if with_values else list(range(w))
-        for s in order:
-            keys = self._region(r, generation, 0, rows=rows, row0=s * rows)
-            if s == r:
-                out_values = self._region(r, generation, 3, rows=rows, row0=r * rows) if with_values else None
-                out_flags = self._region(r, generation, 4, rows=rows, row0=r * rows)
-            else:
-                out_values = p["answer_values"][s * rows:(s + 1) * rows] if with_values else None
-                out_flags = p["answer_flags"][s * rows:(s + 1) * rows]
+        plan = p.setdefault("lookup_plans", {}).get((generation, with_values))
+        if plan is None:                                  # views and addresses of a generation never change: build once
+            counts = self._region(r, generation, 2)
+            plan = []
+            for s in (([s for s in range(w) if s != r] + [r]) if with_values else list(range(w))):
+                keys = self._region(r, generation, 0, rows=rows, row0=s * rows)
+                if s == r:
+                    out_values = self._region(r, generation, 3, rows=rows, row0=r * rows) if with_values else None
+                    out_flags = self._region(r, generation, 4, rows=rows, row0=r * rows)
+                    remote = None
+                else:
+                    out_values = p["answer_values"][s * rows:(s + 1) * rows] if with_values else None
+                    out_flags = p["answer_flags"][s * rows:(s + 1) * rows]
+                    remote = (ctypes.c_void_p(self._region_ptr(s, generation, 3, r * rows)) if with_values else None,
+                              ctypes.c_void_p(self._region_ptr(s, generation, 4, r * rows)))
+                plan.append((keys, counts[s:s + 1], out_values, out_flags, remote))
+            p["lookup_plans"][(generation, with_values)] = plan
+        for keys, count, out_values, out_flags, remote in plan:
             if with_values:
-                self.local.get_sliced(keys, 1, rows, counts[s:s + 1], abort, fallback_value, out_values, out_flags)
+                self.local.get_sliced(keys, 1, rows, count, abort, fallback_value, out_values, out_flags)
             else:
-                self.local.remove_sliced(keys, 1, rows, counts[s:s + 1], abort, out_flags)
-            if s == r:
+                self.local.remove_sliced(keys, 1, rows, count, abort, out_flags)
+            if remote is None:
                 continue
             if self._copy_stream is None:
-                self._copy_stream = torch.cuda.Stream(device=self.device)
+                # high priority: the copy kernel's few blocks must not queue behind the big grid of the next source's
+                # probing, which they are meant to overlap
+                self._copy_stream = torch.cuda.Stream(device=self.device, priority=-1)
             answered = torch.cuda.Event()
             answered.record()
             with torch.cuda.stream(self._copy_stream):
                 self._copy_stream.wait_event(answered)
                 with torch.cuda.device(self.device):
-                    L.check(lib.dok_copy_counted(
-                        ctypes.c_void_p(self._region_ptr(s, generation, 3, r * rows)) if with_values else None,
-                        L.ptr(out_values), p["vb"], ctypes.c_void_p(self._region_ptr(s, generation, 4, r * rows)),
-                        L.ptr(out_flags), 1, rows, L.ptr(counts[s:s + 1]), L.ptr(abort), L.stream_ptr(self.device)),
-                        "dok_copy_counted")
+                    L.check(lib.dok_copy_counted(remote[0], L.ptr(out_values), p["vb"], remote[1], L.ptr(out_flags), 1, rows,
+                                                 L.ptr(count), L.ptr(abort), L.stream_ptr(self.device)), "dok_copy_counted")
             self._in_flight.append(True)
         self.answers_delivered()
 
