@@ -68,9 +68,6 @@ struct DevTable {
   // worked through in passes, each pass taking only the rows whose chain STARTS inside its window, so that one
   // pass touches a range the TLB covers.
   ll_t win_lo, win_hi;
-  // Windowed passes: a block looks at `pick` candidate rows per thread (span = rows per block), keeps the ones whose
-  // chain starts in the window and works on those with all lanes busy (RowPicker).
-  int pick, span;
 };
 
 #define DOK_BLOCKED (-2LL)   // tag of padding slots: never empty, never a tombstone, never a uuid (uuids are >= 0)
@@ -152,19 +149,19 @@ struct RowKeys {          // contiguous [n, ks] rows of the key dtype (closed_ha
   const ll_t *slice_counts = nullptr;
   const ll_t *abort = nullptr;
   __device__ __forceinline__ ll_t count() const { return n; }
-  // batch element at position j of the batch (of slice blockIdx.y for sliced batches) and whether it exists
-  __device__ __forceinline__ bool at(ll_t j, ll_t &e) const {
+  // batch element of the calling thread and whether it exists
+  __device__ __forceinline__ bool row(ll_t &e) const {
+    const ll_t j = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x;
     if (slice_rows == 0) { e = j; return j < n; }
     e = (ll_t)blockIdx.y * slice_rows + j;
     return j < slice_rows && j < slice_counts[blockIdx.y];
   }
-  // block-uniform: nothing for a block whose first position is `first` to do
-  __device__ __forceinline__ bool idle(ll_t first) const {
+  // block-uniform: nothing for this block to do
+  __device__ __forceinline__ bool idle() const {
     if (slice_rows == 0) return false;
     if (abort != nullptr && *abort != 0) return true;
-    return first >= slice_counts[blockIdx.y];
+    return (ll_t)blockIdx.x * DOK_TPB >= slice_counts[blockIdx.y];
   }
-  __device__ __forceinline__ ll_t rows_per_grid_row() const { return slice_rows == 0 ? n : slice_rows; }
   // get_uuid of the reference (closed_hashmap_impl_class.cu:98-107) and the chain-decorrelating product, in one
   // pass over the key
   __device__ __forceinline__ KeyHash hash(const DevHash &hp, ll_t e) const {
@@ -202,8 +199,8 @@ struct SelKeys {
   dok_selectors s;
   ll_t n;
   __device__ __forceinline__ ll_t count() const { return n; }
-  __device__ __forceinline__ bool at(ll_t j, ll_t &e) const { e = j; return j < n; }
-  __device__ __forceinline__ bool idle(ll_t) const { return false; }
+  __device__ __forceinline__ bool row(ll_t &e) const { e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x; return e < n; }
+  __device__ __forceinline__ bool idle() const { return false; }
   // element offsets of batch element e into each of the ndim index tensors (fully unrolled over the
   // maximum ndim with predication, so `off` stays in registers)
   __device__ __forceinline__ void offsets(ll_t e, ll_t (&off)[DOK_MAX_KEY_SIZE]) const {
@@ -254,88 +251,6 @@ struct SelKeys {
       if (d < s.ndim) ((ll_t *)dst_row)[hp.perm[d]] = s.ptr[d][off[d]];
   }
 };
-
-// ---------------------------------------------------------------------------------------------------------
-// Which rows a block works on.  Plain launch: thread t of block b owns row b * 256 + t, once.  Windowed pass (the
-// table is served window by window, DevTable::win_lo): only 1 / passes of the rows belong to the pass, and a warp
-// that walked with most lanes idle would pay the walk's instructions for nothing; so the block first looks at
-// `pick` candidate rows per thread (hash + window test, cheap), collects the positions of those that belong to the
-// pass in shared memory (any order: results are addressed by row, and "last row wins" by the row index in the
-// stamp), and then works through them 256 at a time with every lane busy.  The span is a little under
-// 256 * pick so that the collected rows usually fit ONE round.
-// ---------------------------------------------------------------------------------------------------------
-#define DOK_PICK_MAX 4
-struct PickShared { int count; unsigned short rel[DOK_TPB * DOK_PICK_MAX]; };
-
-template <class Keys>
-struct RowPicker {
-  const DevTable &t;
-  const DevHash &hp;
-  const Keys &keys;
-  PickShared &sm;
-  ll_t first;          // position of the block's first candidate row
-  int round, total;    // rounds of 256 rows done / rows collected
-  // every thread of the block must construct it (block-uniform control flow, one barrier when windowed)
-  __device__ __forceinline__ RowPicker(const DevTable &t_, const DevHash &hp_, const Keys &keys_, PickShared &sm_)
-      : t(t_), hp(hp_), keys(keys_), sm(sm_), round(0) {
-    first = (ll_t)blockIdx.x * t.span;
-    if (threadIdx.x == 0) sm.count = 0;
-    __syncthreads();
-    for (int c = 0; c < t.pick; c++) {
-      const int j = c * DOK_TPB + (int)threadIdx.x;
-      ll_t e;
-      bool mine = j < t.span && keys.at(first + j, e);
-      if (mine) mine = dok_in_window(t, keys.hash(hp, e), true);
-      const unsigned votes = __ballot_sync(0xffffffffu, mine);
-      int at = 0;
-      if ((threadIdx.x & 31) == 0 && votes) at = atomicAdd(&sm.count, __popc(votes));
-      at = __shfl_sync(0xffffffffu, at, 0);
-      if (mine) sm.rel[at + __popc(votes & ((1u << (threadIdx.x & 31)) - 1u))] = (unsigned short)j;
-    }
-    __syncthreads();
-    total = sm.count;
-  }
-  __device__ __forceinline__ bool more() const { return round * DOK_TPB < total; }          // block-uniform
-  // the calling thread's row of this round: batch element, its hash, and whether there is one
-  __device__ __forceinline__ bool take(ll_t &e, KeyHash &kh) {
-    const int i = round * DOK_TPB + (int)threadIdx.x;
-    const bool active = i < total;
-    e = 0;
-    if (active) keys.at(first + sm.rel[i], e);
-    kh = KeyHash{0, 0};
-    if (active) kh = keys.hash(hp, e);
-    round++;
-    return active;
-  }
-};
-
-// The rows of the calling block, one call of body(e, hash, active) per round for every thread.  PICK = false: the
-// plain launch (one round, thread t owns row blockIdx.x * 256 + t); PICK = true: a windowed pass through RowPicker.
-// Every thread of the block must call it; `sm` is only touched when PICK.
-template <bool PICK, class Keys, class Body>
-__device__ __forceinline__ void dok_for_rows(const DevTable &t, const DevHash &hp, const Keys &keys, PickShared *sm,
-                                             const Body &body) {
-  if constexpr (!PICK) {
-    ll_t e;
-    const bool active = keys.at((ll_t)blockIdx.x * DOK_TPB + threadIdx.x, e);
-    KeyHash kh{0, 0};
-    if (active) kh = keys.hash(hp, e);
-    body(e, kh, active);
-  } else {
-    RowPicker<Keys> rows(t, hp, keys, *sm);
-    while (rows.more()) {
-      ll_t e;
-      KeyHash kh;
-      const bool active = rows.take(e, kh);
-      body(e, kh, active);
-    }
-  }
-}
-// block-uniform: nothing for this block to do (sliced batches: beyond the slice's count, or the launch was aborted)
-template <bool PICK, class Keys>
-__device__ __forceinline__ bool dok_block_idle(const DevTable &t, const Keys &keys) {
-  return keys.idle((ll_t)blockIdx.x * (PICK ? t.span : DOK_TPB));
-}
 
 // ---------------------------------------------------------------------------------------------------------
 // Slot access
@@ -394,7 +309,6 @@ __device__ __forceinline__ Located dok_locate_serial(const DevTable &t, const Ke
 
 // No-op hit handler for walks that only need the slot.
 struct NoEmit {
-  static constexpr bool EMITS = false;
   template <int LW>
   __device__ __forceinline__ void operator()(ll_t, int, const ull_t (&)[LW]) const {}
 };
@@ -425,11 +339,10 @@ __device__ __forceinline__ void dok_load_words(const char *p, ull_t (&w)[LW]) {
 // rounds in which no quad of the warp has work are skipped (the decision is warp-uniform).
 // On a hit, `emit(e_r, slot_in_group, words)` runs on all four lanes while they still hold the line: e_r is the
 // batch element of the key, words the calling lane's chunk.
-// Every lane of the warp must call this (inactive lanes pass active = false).  CONSEC: consecutive lanes hold
-// consecutive batch elements e (a plain launch); otherwise the emitter's row is fetched from its owner lane.
-// SB = slot bytes (32, 64, 128).  Slot indices are 32-bit here: the host refuses cooperative
+// Every lane of the warp must call this (inactive lanes pass active = false), with CONSECUTIVE batch elements e in
+// consecutive lanes.  SB = slot bytes (32, 64, 128).  Slot indices are 32-bit here: the host refuses cooperative
 // tables of 2^32 - 1 slots or more.
-template <int SB, int LW, bool TOMB, bool CONSEC, class Emit>
+template <int SB, int LW, bool TOMB, class Emit>
 __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyHash &kh, ll_t e, bool active,
                                                    int *probes, const Emit &emit) {
   constexpr int SPG = 128 / SB;
@@ -438,6 +351,7 @@ __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyH
   const unsigned lane = threadIdx.x & 31u, l = lane & 3u, base = lane & ~3u;
   const bool has_tag = ((32u * l) % SB) == 0;         // does this lane's chunk start with a slot's tag?
   const unsigned my_slot = (32u * l) / SB;            // slot (within the group) the chunk belongs to
+  const ll_t e_quad = e - l;                          // batch element of the quad's first lane (elements are consecutive)
   const unsigned n_groups = (unsigned)t.n_groups;     // < 2^32 (checked on the host)
   const char *my_base = t.slots + 32 * l;
   // results as 32-bit group-relative codes until the end: slot = group * SPG + position
@@ -492,11 +406,9 @@ __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyH
 #pragma unroll
     for (unsigned r = 0; r < 4; r++) {                // hits: hand the line to the emitter while it is in registers
       const unsigned m = (bits >> (8u * r)) & 0xfu, me = (m | (bits >> (8u * r + 4u))) & 0xfu;
-      ll_t e_r = e - l + r;                            // consecutive rows in consecutive lanes ...
-      if constexpr (Emit::EMITS && !CONSEC) e_r = __shfl_sync(FULL, e, base + r);     // ... or rows picked from anywhere
       if (me) {
         const int pos = __ffs(me) - 1;
-        if ((m >> pos) & 1u) emit(e_r, pos, w[r]);
+        if ((m >> pos) & 1u) emit(e_quad + r, pos, w[r]);
       }
     }
     if (group != NONE) {
@@ -522,11 +434,9 @@ __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyH
     bits |= __shfl_xor_sync(FULL, bits, 1);
     bits |= __shfl_xor_sync(FULL, bits, 2);
     const unsigned m = bits & 0xfu, me = (bits | (bits >> 4)) & 0xfu;
-    ll_t e_r = e - l + r;
-    if constexpr (Emit::EMITS && !CONSEC) e_r = __shfl_sync(FULL, e, base + r);
     if (me) {
       const int pos = __ffs(me) - 1;
-      if ((m >> pos) & 1u) emit(e_r, pos, wl);
+      if ((m >> pos) & 1u) emit(e_quad + r, pos, wl);
     }
     if (l == r && group != NONE) advance(m, me, (bits >> 8) & 0xfu);
   }
@@ -542,7 +452,6 @@ __device__ __forceinline__ Located dok_locate_quad(const DevTable &t, const KeyH
 // a hit needs no second access to the table.  LW = 2 serves 32-byte slots whose value is one word behind the tag.
 template <int SB, int LW>
 struct EmitValue {
-  static constexpr bool EMITS = true;
   const DevTable &t;
   char *out_values;
   __device__ __forceinline__ void operator()(ll_t e_r, int pos, const ull_t (&w)[LW]) const {
@@ -566,7 +475,7 @@ struct EmitValue {
 };
 
 // SB == 0 selects the serial walk (slots wider than one line); emit is not called there.
-template <int SB, int LW, bool TOMB, bool CONSEC = true, class Emit>
+template <int SB, int LW, bool TOMB, class Emit>
 __device__ __forceinline__ Located dok_locate(const DevTable &t, const KeyHash &kh, ll_t e, bool active, int *probes,
                                               const Emit &emit) {
   if constexpr (SB == 0) {
@@ -574,7 +483,7 @@ __device__ __forceinline__ Located dok_locate(const DevTable &t, const KeyHash &
     if (probes) *probes = 0;
     return Located{-1, -1, -1};
   } else {
-    return dok_locate_quad<SB, LW, TOMB, CONSEC>(t, kh, e, active, probes, emit);
+    return dok_locate_quad<SB, LW, TOMB>(t, kh, e, active, probes, emit);
   }
 }
 

@@ -112,8 +112,6 @@ inline bool dok_make_table(const dok_table *t, DevTable *out) {
   out->stamp_off = lay.stamp_off;
   out->vwords = (t->value_bytes + 7) / 8;
   out->win_lo = out->win_hi = 0;
-  out->pick = 1;
-  out->span = DOK_TPB;
   if (lay.sb <= 128 && out->n_slots >= 0xffffffffLL) return false;    // the cooperative walk keeps slot indices in 32 bits
   return true;
 }
@@ -137,15 +135,9 @@ inline int dok_window_passes(const DevTable &t) {
 inline DevTable dok_window(const DevTable &t, int w, int passes) {
   DevTable o = t;
   o.win_lo = o.win_hi = 0;
-  o.pick = 1;
-  o.span = DOK_TPB;
   if (passes > 1) {
     o.win_lo = (ll_t)((__int128)t.n_groups * w / passes);
     o.win_hi = (ll_t)((__int128)t.n_groups * (w + 1) / passes);
-    // a block's candidates: `pick` rows per thread, a little under 256 * pick in all so that the 1 / passes of them
-    // that belong to the pass usually fit one round of 256
-    o.pick = passes < DOK_PICK_MAX ? passes : DOK_PICK_MAX;
-    o.span = (DOK_TPB * o.pick * 15 / 16) & ~31;
   }
   return o;
 }

@@ -13,31 +13,33 @@
 // ---------------------------------------------------------------------------------------------------------
 // get
 // ---------------------------------------------------------------------------------------------------------
-template <int SB, int LW, bool PICK, class Keys>
-__global__ void __launch_bounds__(DOK_TPB, (PICK ? 4 : LW == 2 ? (SB == 32 ? 8 : 6) : 1))
-k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values, uint8_t *__restrict__ out_found, Fallback fb,
-      ll_t *counters, int count_probes) {
+template <int SB, int LW, class Keys>
+__global__ void __launch_bounds__(DOK_TPB, (LW == 2 ? (SB == 32 ? 8 : 6) : 1)) k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values,
+                                                    uint8_t *__restrict__ out_found, Fallback fb, ll_t *counters,
+                                                    int count_probes) {
   __shared__ BlockTally tally;
-  __shared__ PickShared picked[1];                             // used by windowed passes only
-  if (dok_block_idle<PICK>(t, keys)) return;
+  if (keys.idle()) return;
   if (counters) dok_tally_begin(tally);
-  dok_for_rows<PICK>(t, hp, keys, picked, [&](ll_t e, const KeyHash &kh, bool active) {
-    int probes = 0;
-    // on a hit the quad writes the value from the registers that hold the line
-    const Located loc = dok_locate<SB, LW, false, !PICK>(t, kh, e, active, &probes, EmitValue<(SB == 0 ? 32 : SB), LW>{t, out_values});
-    const int hit = active && loc.found >= 0;
-    if (active) {
-      char *dst = out_values + e * (ll_t)t.vb;
-      if (SB == 0 && hit) dok_load_value(t, loc.found, dst);
-      if (!hit) dok_store_fallback(t, fb, dst);
-    }
-    if (active && out_found) out_found[e] = (uint8_t)hit;
-    if (counters) {
-      dok_tally_add(tally, DOK_CNT_HITS, hit);
-      if (count_probes) dok_warp_add(counters + DOK_CNT_PROBES, probes);
-    }
-  });
-  if (counters) dok_tally_flush(tally, counters, nullptr);
+  ll_t e;
+  bool active = keys.row(e);
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
+  int probes = 0;
+  // on a hit the quad writes the value from the registers that hold the line
+  const Located loc = dok_locate<SB, LW, false>(t, kh, e, active, &probes, EmitValue<(SB == 0 ? 32 : SB), LW>{t, out_values});
+  const int hit = active && loc.found >= 0;
+  if (active) {
+    char *dst = out_values + e * (ll_t)t.vb;
+    if (SB == 0 && hit) dok_load_value(t, loc.found, dst);
+    if (!hit) dok_store_fallback(t, fb, dst);
+  }
+  if (active && out_found) out_found[e] = (uint8_t)hit;
+  if (counters) {
+    dok_tally_add(tally, DOK_CNT_HITS, hit);
+    dok_tally_flush(tally, counters, nullptr);
+    if (count_probes) dok_warp_add(counters + DOK_CNT_PROBES, probes);
+  }
 }
 
 #define DOK_DISPATCH_SB(t, CALL)                        \
@@ -47,24 +49,13 @@ k_get(DevTable t, DevHash hp, Keys keys, char *__restrict__ out_values, uint8_t 
     case 128: { constexpr int SB = 128; CALL; break; }  \
     default: { constexpr int SB = 0; CALL; break; }     \
   }
-// PICK = the table is served in windowed passes (see RowPicker): a kernel variant of its own, so that the plain
-// launch carries none of its registers or shared memory
-#define DOK_DISPATCH_PICK(t, CALL)                                        \
-  if (dok_window_passes(t) > 1) { constexpr bool PICK = true; CALL; }     \
-  else { constexpr bool PICK = false; CALL; }
 
-// launch grid of a batch: 256 rows per block for a plain launch, the picker's span for a windowed pass (wt = the
-// DevTable of the launch); sliced batches put the slice in gridDim.y
-inline ll_t dok_block_rows(const DevTable &wt) { return wt.win_hi == 0 ? DOK_TPB : wt.span; }
-inline dim3 dok_grid(const RowKeys &k, const DevTable &wt) {
-  const ll_t per = dok_block_rows(wt);
-  if (k.slice_rows == 0) return dim3((unsigned)((k.n + per - 1) / per));
-  return dim3((unsigned)((k.slice_rows + per - 1) / per), (unsigned)(k.n / k.slice_rows));
+// launch grid of a batch: one thread per row; sliced batches put the slice in gridDim.y
+inline dim3 dok_grid(const RowKeys &k) {
+  if (k.slice_rows == 0) return dim3((unsigned)((k.n + DOK_TPB - 1) / DOK_TPB));
+  return dim3((unsigned)((k.slice_rows + DOK_TPB - 1) / DOK_TPB), (unsigned)(k.n / k.slice_rows));
 }
-inline dim3 dok_grid(const SelKeys &k, const DevTable &wt) {
-  const ll_t per = dok_block_rows(wt);
-  return dim3((unsigned)((k.n + per - 1) / per));
-}
+inline dim3 dok_grid(const SelKeys &k) { return dim3((unsigned)((k.n + DOK_TPB - 1) / DOK_TPB)); }
 
 template <class Keys>
 inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, void *out_values, uint8_t *out_found,
@@ -74,13 +65,14 @@ inline int launch_get(const DevTable &t, const DevHash &hp, const Keys &keys, vo
   Fallback fb;
   memset(&fb, 0, sizeof(fb));
   if (fallback) memcpy(&fb, fallback, (size_t)t.vb);
+  const dim3 grid = dok_grid(keys);
   int rc = DOK_OK;
   if (t.vb <= 8 && t.sb <= 128) {   // tag and value fit the first 16 bytes of the slot: half the load width (or less)
-    DOK_DISPATCH_SB(t, DOK_DISPATCH_PICK(t, DOK_FOR_WINDOWS(t, rc, (k_get<(SB == 0 ? 32 : SB), 2, PICK, Keys><<<dok_grid(keys, wt), DOK_TPB, 0, st>>>(
-                                                  wt, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes)))));
+    DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_get<(SB == 0 ? 32 : SB), 2, Keys><<<grid, DOK_TPB, 0, st>>>(
+                                                  wt, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes))));
   } else
-    DOK_DISPATCH_SB(t, DOK_DISPATCH_PICK(t, DOK_FOR_WINDOWS(t, rc, (k_get<SB, 4, PICK, Keys><<<dok_grid(keys, wt), DOK_TPB, 0, st>>>(
-                                                  wt, hp, keys, (char *)out_values, out_found, fb, (ll_t *)counters, count_probes)))));
+    DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_get<SB, 4, Keys><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, (char *)out_values, out_found,
+                                                                                           fb, (ll_t *)counters, count_probes))));
   return rc;
 }
 
@@ -101,28 +93,30 @@ __device__ __forceinline__ void dok_write_row(const DevTable &t, const DevHash &
 }
 
 // One kernel, for batches whose rows have pairwise different uuids.
-template <int SB, bool PICK, class Keys, class Values>
+template <int SB, class Keys, class Values>
 __global__ void __launch_bounds__(DOK_TPB, 4) k_set_unique(DevTable t, DevHash hp, Keys keys, Values values,
                                                         uint8_t *__restrict__ out_stored, ll_t *counters) {
   __shared__ BlockTally tally;
-  __shared__ PickShared picked[1];
-  if (dok_block_idle<PICK>(t, keys)) return;
+  if (keys.idle()) return;
   if (counters) dok_tally_begin(tally);
-  dok_for_rows<PICK>(t, hp, keys, picked, [&](ll_t e, const KeyHash &kh, bool active) {
-    int outcome = -1;
-    const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
-    if (active) {
-      if (slot >= 0) dok_write_row(t, hp, keys, values, e, slot, outcome != DOK_OUT_FOUND || hp.dtype >= DOK_F16);
-      if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
-    }
-    if (counters) {
-      dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
-      dok_tally_add(tally, DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
-      dok_tally_add(tally, DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
-      dok_tally_add(tally, DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
-    }
-  });
-  if (counters) dok_tally_flush(tally, counters, nullptr);
+  ll_t e;
+  bool active = keys.row(e);
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
+  int outcome = -1;
+  const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
+  if (active) {
+    if (slot >= 0) dok_write_row(t, hp, keys, values, e, slot, outcome != DOK_OUT_FOUND || hp.dtype >= DOK_F16);
+    if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
+  }
+  if (counters) {
+    dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
+    dok_tally_add(tally, DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
+    dok_tally_add(tally, DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
+    dok_tally_add(tally, DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
+    dok_tally_flush(tally, counters, nullptr);
+  }
 }
 
 // Stamp word of a slot during a general set: (epoch << 33) | (row << 1) | conflict.  The epoch of a call is
@@ -134,41 +128,43 @@ __device__ __forceinline__ ll_t dok_stamp(ll_t epoch, ll_t row) { return (epoch 
 // for a batch without equal uuids that is all there is to do.  A row that finds the slot already stamped in
 // this epoch sets the conflict bit and counts a duplicate (in slot_out[n], zeroed by the host before the
 // launch); the second kernel then lets the slot's last row rewrite it.
-template <int SB, bool PICK, class Keys, class Values>
-__global__ void __launch_bounds__(DOK_TPB, (PICK ? 4 : 6)) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
-                                                                    ll_t *__restrict__ slot_out, ll_t epoch,
-                                                                    uint8_t *__restrict__ out_stored, ll_t *counters) {
+template <int SB, class Keys, class Values>
+__global__ void __launch_bounds__(DOK_TPB, 6) k_set_claim(DevTable t, DevHash hp, Keys keys, Values values,
+                                                       ll_t *__restrict__ slot_out, ll_t epoch,
+                                                       uint8_t *__restrict__ out_stored, ll_t *counters) {
   __shared__ BlockTally tally;
-  __shared__ PickShared picked[1];
-  if (dok_block_idle<PICK>(t, keys)) return;
+  if (keys.idle()) return;
   dok_tally_begin(tally);
-  dok_for_rows<PICK>(t, hp, keys, picked, [&](ll_t e, const KeyHash &kh, bool active) {
-    int outcome = -1, dup = 0;
-    const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
-    if (active) {
-      slot_out[e] = slot;
-      if (slot >= 0) {
-        // the row is stored without waiting for the stamp's answer: the two requests travel together.  If the slot
-        // turns out to be shared, whatever the racing stores left is rewritten by the second kernel.
-        ll_t *stamp = dok_stamp_ptr(t, slot);
-        dok_write_row(t, hp, keys, values, e, slot, outcome != DOK_OUT_FOUND || hp.dtype >= DOK_F16);
-        const ll_t old = (ll_t)atomicMax(stamp, dok_stamp(epoch, e));
-        if ((old >> 33) == epoch) {
-          atomicOr((ull_t *)stamp, 1ULL);
-          dup = 1;
-        }
+  ll_t e;
+  bool active = keys.row(e);
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
+  int outcome = -1, dup = 0;
+  const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
+  if (active) {
+    slot_out[e] = slot;
+    if (slot >= 0) {
+      // the row is stored without waiting for the stamp's answer: the two requests travel together.  If the slot
+      // turns out to be shared, whatever the racing stores left is rewritten by the second kernel.
+      ll_t *stamp = dok_stamp_ptr(t, slot);
+      dok_write_row(t, hp, keys, values, e, slot, outcome != DOK_OUT_FOUND || hp.dtype >= DOK_F16);
+      const ll_t old = (ll_t)atomicMax(stamp, dok_stamp(epoch, e));
+      if ((old >> 33) == epoch) {
+        atomicOr((ull_t *)stamp, 1ULL);
+        dup = 1;
       }
-      if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
     }
-    dok_tally_add(tally, DOK_TALLY_EXTRA, dup);
-    if (counters) {
-      dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
-      dok_tally_add(tally, DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
-      dok_tally_add(tally, DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
-      dok_tally_add(tally, DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
-      dok_tally_add(tally, DOK_CNT_DUPLICATES, dup);
-    }
-  });
+    if (out_stored) out_stored[e] = (uint8_t)(slot >= 0);
+  }
+  dok_tally_add(tally, DOK_TALLY_EXTRA, dup);
+  if (counters) {
+    dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
+    dok_tally_add(tally, DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
+    dok_tally_add(tally, DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
+    dok_tally_add(tally, DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
+    dok_tally_add(tally, DOK_CNT_DUPLICATES, dup);
+  }
   dok_tally_flush(tally, counters, slot_out + keys.count());
 }
 
@@ -179,9 +175,9 @@ template <class Keys, class Values>
 __global__ void __launch_bounds__(DOK_TPB) k_set_resolve(DevTable t, DevHash hp, Keys keys, Values values,
                                                          const ll_t *__restrict__ slot_in, ll_t epoch) {
   if (slot_in[keys.count()] == 0) return;        // the first kernel met no duplicate: every row is already in place
-  if (keys.idle((ll_t)blockIdx.x * DOK_TPB)) return;
+  if (keys.idle()) return;
   ll_t e;
-  if (!keys.at((ll_t)blockIdx.x * DOK_TPB + threadIdx.x, e)) return;
+  if (!keys.row(e)) return;
   const ll_t slot = slot_in[e];
   if (slot < 0) return;
   if (t.win_hi != 0) {                           // windowed passes: by the slot's own group (each slot has one pass)
@@ -192,16 +188,17 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_resolve(DevTable t, DevHash hp,
   dok_write_row(t, hp, keys, values, e, slot, true);
 }
 
+// contiguous value rows [n, value_bytes]
 template <class Keys, class Values>
 inline int launch_set_general(const DevTable &t, const DevHash &hp, const Keys &keys, const Values &values,
                               int64_t *slot_scratch, int64_t epoch, uint8_t *out_stored, int64_t *counters, cudaStream_t st) {
   if (cudaMemsetAsync(slot_scratch + keys.n, 0, sizeof(int64_t), st) != cudaSuccess) return dok_check_launch();
+  const dim3 grid = dok_grid(keys);
   int rc = DOK_OK;
-  DOK_DISPATCH_SB(t, DOK_DISPATCH_PICK(t, DOK_FOR_WINDOWS(t, rc, (k_set_claim<SB, PICK><<<dok_grid(keys, wt), DOK_TPB, 0, st>>>(
-                                                 wt, hp, keys, values, (ll_t *)slot_scratch, (ll_t)epoch, out_stored, (ll_t *)counters)))));
+  DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_set_claim<SB><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, values, (ll_t *)slot_scratch,
+                                                                                       (ll_t)epoch, out_stored, (ll_t *)counters))));
   if (rc != DOK_OK) return rc;
-  // the second kernel looks at every row once: plain grid, and in windowed passes it filters by the row's SLOT
-  DOK_FOR_WINDOWS(t, rc, (k_set_resolve<<<dok_grid(keys, t), DOK_TPB, 0, st>>>(wt, hp, keys, values, (const ll_t *)slot_scratch, (ll_t)epoch)));
+  DOK_FOR_WINDOWS(t, rc, (k_set_resolve<<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, values, (const ll_t *)slot_scratch, (ll_t)epoch)));
   return rc;
 }
 
@@ -214,9 +211,9 @@ inline int launch_set(const DevTable &t, const DevHash &hp, const RowKeys &keys,
 inline int launch_set_unique(const DevTable &t, const DevHash &hp, const RowKeys &keys, const char *values,
                              uint8_t *out_stored, int64_t *counters, cudaStream_t st) {
   RowValues rv{values};
+  const dim3 grid = dok_grid(keys);
   int rc = DOK_OK;
-  DOK_DISPATCH_SB(t, DOK_DISPATCH_PICK(t, DOK_FOR_WINDOWS(t, rc, (k_set_unique<SB, PICK><<<dok_grid(keys, wt), DOK_TPB, 0, st>>>(
-                                                 wt, hp, keys, rv, out_stored, (ll_t *)counters)))));
+  DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_set_unique<SB><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, rv, out_stored, (ll_t *)counters))));
   return rc;
 }
 
@@ -226,29 +223,33 @@ inline int launch_set_unique(const DevTable &t, const DevHash &hp, const RowKeys
 
 // REMOVE = 1: the tag is swapped to the tombstone by CAS so that equal uuids in one batch report exactly once
 // (ClosedHashmap::remove, closed_hashmap_impl_class.cu:459-484, stores it non-atomically).
-template <int SB, int REMOVE, bool PICK, class Keys>
+template <int SB, int REMOVE, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_find(DevTable t, DevHash hp, Keys keys, uint8_t *__restrict__ out_flags,
                                                   ll_t *counters) {
   __shared__ BlockTally tally;
-  __shared__ PickShared picked[1];
-  if (dok_block_idle<PICK>(t, keys)) return;
+  if (keys.idle()) return;
   if (counters) dok_tally_begin(tally);
-  dok_for_rows<PICK>(t, hp, keys, picked, [&](ll_t e, const KeyHash &kh, bool active) {
-    const Located loc = dok_locate<SB, 1, false>(t, kh, e, active, nullptr, NoEmit());
-    int hit = active && loc.found >= 0;
-    if (REMOVE && hit) hit = dok_cas_tag(t, loc.found, kh.uuid, DOK_REMOVED) == kh.uuid;
-    if (active && out_flags) out_flags[e] = (uint8_t)hit;
-    if (counters) dok_tally_add(tally, DOK_CNT_HITS, hit);
-  });
-  if (counters) dok_tally_flush(tally, counters, nullptr);
+  ll_t e;
+  bool active = keys.row(e);
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
+  const Located loc = dok_locate<SB, 1, false>(t, kh, e, active, nullptr, NoEmit());
+  int hit = active && loc.found >= 0;
+  if (REMOVE && hit) hit = dok_cas_tag(t, loc.found, kh.uuid, DOK_REMOVED) == kh.uuid;
+  if (active && out_flags) out_flags[e] = (uint8_t)hit;
+  if (counters) {
+    dok_tally_add(tally, DOK_CNT_HITS, hit);
+    dok_tally_flush(tally, counters, nullptr);
+  }
 }
 
 template <int REMOVE, class Keys>
 inline int launch_find(const DevTable &t, const DevHash &hp, const Keys &keys, uint8_t *out_flags, int64_t *counters,
                        cudaStream_t st) {
+  const dim3 grid = dok_grid(keys);
   int rc = DOK_OK;
-  DOK_DISPATCH_SB(t, DOK_DISPATCH_PICK(t, DOK_FOR_WINDOWS(t, rc, (k_find<SB, REMOVE, PICK><<<dok_grid(keys, wt), DOK_TPB, 0, st>>>(
-                                                 wt, hp, keys, out_flags, (ll_t *)counters)))));
+  DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_find<SB, REMOVE><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, out_flags, (ll_t *)counters))));
   return rc;
 }
 
@@ -258,31 +259,33 @@ static __global__ void k_fill_i64(ll_t *p, ll_t n, ll_t v) {
 
 // Rows absent from the table insert their uuid into a scratch tag set; the number of successful claims is the
 // number of distinct absent uuids.
-template <int SB, bool PICK, class Keys>
+template <int SB, class Keys>
 __global__ void __launch_bounds__(DOK_TPB) k_count_new(DevTable t, DevHash hp, Keys keys, ll_t *__restrict__ scratch,
                                                        ll_t scratch_slots, ll_t *counters) {
   __shared__ BlockTally tally;
-  __shared__ PickShared picked[1];
-  if (dok_block_idle<PICK>(t, keys)) return;
+  if (keys.idle()) return;
   dok_tally_begin(tally);
-  dok_for_rows<PICK>(t, hp, keys, picked, [&](ll_t e, const KeyHash &kh, bool active) {
-    const Located loc = dok_locate<SB, 1, false>(t, kh, e, active, nullptr, NoEmit());
-    int claimed = 0;
-    if (active && loc.found < 0) {
-      const ll_t uuid = kh.uuid;
-      ll_t slot = (ll_t)__umul64hi(dok_mix64((ull_t)uuid ^ 0x5851f42d4c957f2dULL), (ull_t)scratch_slots);
-      for (ll_t i = 0; i < scratch_slots; i++) {
-        ll_t tag = __ldcg(&scratch[slot]);
-        if (tag == DOK_EMPTY) {
-          tag = (ll_t)atomicCAS((ull_t *)&scratch[slot], (ull_t)DOK_EMPTY, (ull_t)uuid);
-          if (tag == DOK_EMPTY) { claimed = 1; break; }
-        }
-        if (tag == uuid) break;
-        if (++slot == scratch_slots) slot = 0;
+  ll_t e;
+  bool active = keys.row(e);
+  KeyHash kh{0, 0};
+  if (active) kh = keys.hash(hp, e);
+  active = dok_in_window(t, kh, active);
+  const Located loc = dok_locate<SB, 1, false>(t, kh, e, active, nullptr, NoEmit());
+  int claimed = 0;
+  if (active && loc.found < 0) {
+    const ll_t uuid = kh.uuid;
+    ll_t slot = (ll_t)__umul64hi(dok_mix64((ull_t)uuid ^ 0x5851f42d4c957f2dULL), (ull_t)scratch_slots);
+    for (ll_t i = 0; i < scratch_slots; i++) {
+      ll_t tag = __ldcg(&scratch[slot]);
+      if (tag == DOK_EMPTY) {
+        tag = (ll_t)atomicCAS((ull_t *)&scratch[slot], (ull_t)DOK_EMPTY, (ull_t)uuid);
+        if (tag == DOK_EMPTY) { claimed = 1; break; }
       }
+      if (tag == uuid) break;
+      if (++slot == scratch_slots) slot = 0;
     }
-    dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, claimed);
-  });
+  }
+  dok_tally_add(tally, DOK_CNT_CLAIMED_EMPTY, claimed);
   dok_tally_flush(tally, counters, nullptr);
 }
 

@@ -6,6 +6,8 @@ static bool prepare(const dok_table *t, const dok_hash_params *hp, DevTable *dt,
   return dt->kb == dh->ks * dh->elem_bytes;
 }
 
+static unsigned grid_for(ll_t n) { return (unsigned)((n + DOK_TPB - 1) / DOK_TPB); }
+
 extern "C" {
 
 int dok_version(void) { return 2; }
@@ -126,8 +128,8 @@ int dok_map_count_new(const dok_table *t, const dok_hash_params *hp, const void 
   if (rc != DOK_OK) return rc;
   RowKeys rk{keys, n};
   rc = DOK_OK;
-  DOK_DISPATCH_SB(dt, DOK_DISPATCH_PICK(dt, DOK_FOR_WINDOWS(dt, rc, (k_count_new<SB, PICK><<<dok_grid(rk, wt), DOK_TPB, 0, (cudaStream_t)stream>>>(
-                                                  wt, dh, rk, (ll_t *)scratch_tags, scratch_slots, (ll_t *)counters)))));
+  DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_count_new<SB><<<grid_for(n), DOK_TPB, 0, (cudaStream_t)stream>>>(
+                                                  wt, dh, rk, (ll_t *)scratch_tags, scratch_slots, (ll_t *)counters))));
   return rc;
 }
 

@@ -75,8 +75,9 @@ int dok_map_count_new_static(const dok_table *t, const dok_hash_params *hp, cons
   rc = dok_check_launch();
   if (rc != DOK_OK) return rc;
   RowKeys rk{keys, n};
+  const unsigned grid = (unsigned)((n + DOK_TPB - 1) / DOK_TPB);
   rc = DOK_OK;
-  DOK_DISPATCH_SB(dt, DOK_DISPATCH_PICK(dt, DOK_FOR_WINDOWS(dt, rc, (k_count_new<SB, PICK><<<dok_grid(rk, wt), DOK_TPB, 0, st>>>(wt, dh, rk, scratch, slots, (ll_t *)counters)))));
+  DOK_DISPATCH_SB(dt, DOK_FOR_WINDOWS(dt, rc, (k_count_new<SB><<<grid, DOK_TPB, 0, st>>>(wt, dh, rk, scratch, slots, (ll_t *)counters))));
   return rc;
 }
 

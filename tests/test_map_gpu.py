@@ -196,6 +196,7 @@ def test_tiny_tables_wraparound_and_full():
     for nb in (8, 13, 64):
         rng = np.random.default_rng(nb)
         p = Pair(seed=nb, n_buckets=nb, rehash_threshold=100.0, **good_parameters(nb, 1, seed=nb))
+        p.c._tombstone_threshold = None              # the reference's behaviour: tombstones stay (the default cleans up)
         keys = rng.permutation(10 * nb)[: 2 * nb].astype(np.int64)[:, None]
         vals = rng.standard_normal((2 * nb, 2)).astype(np.float32)
         first, second = keys[:nb], keys[nb:]
@@ -448,17 +449,17 @@ def test_default_maintenance_keeps_a_churned_table_from_running_out_of_empty_slo
     params = good_parameters(nb, 1, seed=9)
     plain = CudaClosedHashmap(n_buckets=nb, device="cuda:0", rehash_threshold=2.0, tombstone_threshold=None, **params)
     kept = CudaClosedHashmap(n_buckets=nb, device="cuda:0", rehash_threshold=2.0, **params)
-    base = rng.permutation(1 << 30)[:3000].astype(np.int64)[:, None]
+    base = np.unique(rng.integers(0, 1 << 30, size=4000))[:3000].astype(np.int64)[:, None]
     for t in (plain, kept):
         t.set(dev(base), dev(np.ones((3000, 1), np.float32)))
     for step in range(40):                                  # 500 fresh keys in, the same 500 out again
-        fresh = rng.permutation(1 << 30)[:500].astype(np.int64)[:, None] + (1 << 31)
+        fresh = np.unique(rng.integers(0, 1 << 30, size=700))[:500].astype(np.int64)[:, None] + (1 << 31) + (step << 32)
         for t in (plain, kept):
             t.set(dev(fresh), dev(np.full((500, 1), step, np.float32)))
             assert bool(t.remove_rows(dev(fresh)).all())
     assert plain.n_tombstones + plain.n_elements >= 0.99 * nb          # no empty slot left to stop a miss
     assert kept.n_tombstones + kept.n_elements <= 0.95 * nb + 500
-    probe = dev(rng.permutation(1 << 30)[:2000].astype(np.int64)[:, None] + (1 << 32))
+    probe = dev(rng.integers(0, 1 << 30, size=(2000, 1)).astype(np.int64) + (1 << 50))
     (pv, pf), (kv, kf) = plain.get(probe), kept.get(probe)
     assert not pf.any() and not kf.any()
     assert plain.probe_stats(probe)[0] > 20 * kept.probe_stats(probe)[0]
