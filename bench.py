@@ -619,6 +619,7 @@ def run_candidate(args):
         time.sleep(0.5)
         sampler.rows.clear()
 
+    exchange_phases = None
     # ---- timed region: exactly K steps, device-resident inputs
     launches0 = L.lib().dok_launch_count()
     events = []
@@ -643,9 +644,12 @@ def run_candidate(args):
         phase_steps = 3
         step(0, [])                                   # warm the sequential path (allocator pools of the main stream)
         barrier()
+        table.profile = []                            # stage boundaries of every operation, as CUDA events
         for s in range(phase_steps):
             step(s + 1, events)
         barrier()
+        exchange_phases = table.phase_times()
+        table.profile = None
     phase = torch.zeros(3, device=device)
     for s in range(phase_steps):
         e = events[4 * s: 4 * s + 4]
@@ -797,7 +801,8 @@ def run_candidate(args):
             "vs_baseline": None, "dtype": "int64", "data": "synthetic", "config": workload_config(args, world),
             "roofline": roofline, "kernels": per_kernel, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks, "checks": checks,
-            "mean_probe_groups": probe_len, "host_enqueue_ms_per_step": host_enqueue_ms, **extra,
+            "mean_probe_groups": probe_len, "host_enqueue_ms_per_step": host_enqueue_ms,
+            "exchange_phases_ms": exchange_phases, **extra,
         }
         print(json.dumps(line))
     if world > 1:

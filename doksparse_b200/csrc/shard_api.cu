@@ -120,12 +120,20 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (dst.status != nullptr && *dst.status != 0) return;       // uniform over the grid
   for (int i = threadIdx.x; i < n_shards * CELLS; i += DOK_TPB) (&before[0][0])[i] = 0;
+  // one thread per owner fetches its words (a single thread walking the owners would wait for 2 * n_shards dependent
+  // loads at the head of every block)
+  if ((int)threadIdx.x < n_shards) {
+    const int o = threadIdx.x;
+    tile_first[o] = tile_offsets[(ll_t)o * tiles + blockIdx.x] - tile_offsets[(ll_t)o * tiles];
+    local_start[o] = shard_counts[n_shards + o];
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
     ll_t padded = 0;                              // owner o's segment starts at the sum of the padded counts before it
     for (int o = 0; o < n_shards; o++) {
-      tile_first[o] = tile_offsets[(ll_t)o * tiles + blockIdx.x] - tile_offsets[(ll_t)o * tiles];
+      const ll_t c = local_start[o];
       local_start[o] = padded;
-      padded += shard_counts[n_shards + o];
+      padded += c;
     }
   }
   __syncthreads();

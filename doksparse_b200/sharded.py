@@ -478,6 +478,23 @@ class ShardedClosedHashmap:
         self._value_dtype = None
         self._key_shape = None
         self._key_dtype = None
+        self.profile = None           # a list: run() appends (kind, [CUDA events at the stage boundaries]) per operation
+
+    def phase_times(self):
+        """Mean milliseconds per stage and operation kind of the operations recorded while `profile` was a list:
+        partition+scatter and fence of the SEND stage; table work with answer delivery, fence and inverse permutation
+        of the APPLY stage.  Synchronises."""
+        torch.cuda.synchronize(self.ops.device)
+        names = ("send_partition_scatter", "send_fence", "apply_table_and_answers", "apply_fence", "apply_unpermute")
+        acc = {}
+        for kind, ev in self.profile or []:
+            row = acc.setdefault(kind, [0.0] * len(names) + [0])
+            spans = [ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2]), ev[3].elapsed_time(ev[4]), ev[4].elapsed_time(ev[5]),
+                     ev[5].elapsed_time(ev[6])]
+            for i, ms in enumerate(spans):
+                row[i] += ms
+            row[-1] += 1
+        return {kind: {name: row[i] / row[-1] for i, name in enumerate(names)} for kind, row in acc.items()}
 
     # ------------------------------------------------------------------ argument checks (before anything is launched)
     def _check_keys(self, keys):
@@ -606,45 +623,61 @@ class ShardedClosedHashmap:
         with torch.cuda.stream(s_send):
             tokens = torch.zeros((len(operations), 3), device=device, dtype=torch.long)
         applied = self._last_applied          # table work of an earlier submission that was not waited for
-        keep = []
         for i, op in enumerate(operations):
             kind, keys, values = prepared[i]
             generation = self._seq & 1
             self._seq += 1
             token = tokens[i]
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(7)] if self.profile is not None else None
+            mark = (lambda k, stream: marks[k].record(stream)) if marks else (lambda k, stream: None)
             nvtx.range_push(f"dok.sharded.{kind}.send")
             with torch.cuda.stream(s_send):
+                mark(0, s_send)
                 dest = ops.sliced_send(keys, values, generation, want_dest=(kind != "set"), force_overflow=_force_overflow)
                 if applied is not None:
                     # the inbox generation that the NEXT operation's send overwrites is the one the previous
                     # operation's apply reads: the fence below (all ranks) must come after that apply
                     s_send.wait_event(applied)
+                mark(1, s_send)
                 ops.sliced_fence(token, self._signature(kind))
+                mark(2, s_send)
                 sent = torch.cuda.Event()
                 sent.record(s_send)
-            keep.append((keys, values, dest))
+                if dest is not None:
+                    # allocated on the send stream, read on the apply stream: the allocator may hand the block out again
+                    # only after that read.  Nothing of an operation is held until wait() -- holding it would make every
+                    # step of a long submission allocate fresh device memory (a device-wide synchronisation each time).
+                    dest.record_stream(s_apply)
             nvtx.range_pop()
             nvtx.range_push(f"dok.sharded.{kind}.apply")
             with torch.cuda.stream(s_apply):
                 s_apply.wait_event(sent)
+                mark(3, s_apply)
                 abort = token[0:1]
                 if kind == "set":
                     ops.sliced_apply_set(generation, abort, op[3] if len(op) > 3 else False)
+                    mark(4, s_apply)
                     ops.sliced_apply_fence()      # nothing to deliver, but every kind issues the same collectives
+                    mark(5, s_apply)
                 else:
                     with_values = kind == "get"
                     ops.sliced_apply_lookup(generation, abort, with_values, (op[2] if len(op) > 2 else None) if with_values else None)
+                    mark(4, s_apply)
                     ops.sliced_apply_fence()
+                    mark(5, s_apply)
                     out_values, out_flags = ops.sliced_results(generation, dest, with_values, abort)
                     results[i] = (out_values, out_flags) if with_values else out_flags
                     for t in (out_values, out_flags):
                         if t is not None:
                             t.record_stream(main)
+                mark(6, s_apply)
                 applied = torch.cuda.Event()
                 applied.record(s_apply)
+            if marks:
+                self.profile.append((kind, marks))
             nvtx.range_pop()
         self._last_applied = applied
-        self._pending.append((list(operations), results, tokens, keep))
+        self._pending.append((list(operations), results, tokens))
         if wait:
             self.wait()
         return results
@@ -664,9 +697,9 @@ class ShardedClosedHashmap:
         pending, self._pending = self._pending, []
         if not pending:
             return
-        flat = torch.cat([t for _, _, t, _ in pending]).cpu().tolist()         # waits for the device
+        flat = torch.cat([t for _, _, t in pending]).cpu().tolist()         # waits for the device
         redo, i = False, 0
-        for operations, results, _, _ in pending:
+        for operations, results, _ in pending:
             for k, op in enumerate(operations):
                 flag, sig_max, neg_sig_min = flat[i]
                 i += 1

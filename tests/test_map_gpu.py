@@ -452,7 +452,7 @@ def test_default_maintenance_keeps_a_churned_table_from_running_out_of_empty_slo
     base = np.unique(rng.integers(0, 1 << 30, size=4000))[:3000].astype(np.int64)[:, None]
     for t in (plain, kept):
         t.set(dev(base), dev(np.ones((3000, 1), np.float32)))
-    for step in range(40):                                  # 500 fresh keys in, the same 500 out again
+    for step in range(100):                                 # 500 fresh keys in, the same 500 out again
         fresh = np.unique(rng.integers(0, 1 << 30, size=700))[:500].astype(np.int64)[:, None] + (1 << 31) + (step << 32)
         for t in (plain, kept):
             t.set(dev(fresh), dev(np.full((500, 1), step, np.float32)))
@@ -462,7 +462,7 @@ def test_default_maintenance_keeps_a_churned_table_from_running_out_of_empty_slo
     probe = dev(rng.integers(0, 1 << 30, size=(2000, 1)).astype(np.int64) + (1 << 50))
     (pv, pf), (kv, kf) = plain.get(probe), kept.get(probe)
     assert not pf.any() and not kf.any()
-    assert plain.probe_stats(probe)[0] > 20 * kept.probe_stats(probe)[0]
+    assert plain.probe_stats(probe)[0] > 4 * kept.probe_stats(probe)[0]           # groups walked per miss
     (pv, pf), (kv, kf) = plain.get(dev(base)), kept.get(dev(base))
     assert pf.all() and kf.all() and torch.equal(pv, kv)
 
