@@ -103,6 +103,7 @@ def _declare(lib):
         "dok_dense_count_nonzero": ([P, I64, I, I, P, P], I),
         "dok_dense_insert_nonzero": ([TP, HP, P, P, I64, I, P, P], I),
         "dok_partition_tiles": ([I64], I64),
+        "dok_partition_offset_words": ([I64, I], I64),
         "dok_shard_partition_count": ([HP, P, I64, I, P, P, P, P], I),
         "dok_partition_capacity": ([I64, I], I64),
         "dok_shard_partition_scatter": ([P, I, P, I, I64, I, P, P, P, P, P, P, P], I),

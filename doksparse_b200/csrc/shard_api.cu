@@ -47,23 +47,98 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_count(DevHash hp, RowKe
   if (threadIdx.x < n_shards) tile_counts[(ll_t)threadIdx.x * tiles + blockIdx.x] = hist[threadIdx.x];
 }
 
-// In-place exclusive scan by one block; a[n] receives the total.
-static __global__ void __launch_bounds__(1024) k_part_scan(ll_t *a, ll_t n) {
+// In-place exclusive scan of a[0 .. n); a[n] receives the total.  Three small launches: sums of chunks of
+// DOK_SCAN_CHUNK elements (coalesced), a scan of those sums by one block, and the scan of every chunk on top of its
+// offset.  (One block walking the whole array -- 131 K tile counts for 32 Mi rows and 8 owners -- took longer than the
+// partition pass it follows.)
+#define DOK_SCAN_CHUNK 2048
+__device__ __forceinline__ ll_t dok_block_sum(ll_t v, ll_t *warp_sums) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = v;
+  __syncthreads();
+  ll_t total = 0;
+  for (int w = 0; w < (int)(blockDim.x >> 5); w++) total += warp_sums[w];
+  __syncthreads();
+  return total;
+}
+static __global__ void __launch_bounds__(256) k_scan_chunk_sums(const ll_t *__restrict__ a, ll_t n, ll_t *__restrict__ sums) {
+  __shared__ ll_t warp_sums[8];
+  const ll_t base = (ll_t)blockIdx.x * DOK_SCAN_CHUNK;
+  ll_t v = 0;
+#pragma unroll
+  for (int r = 0; r < DOK_SCAN_CHUNK / 256; r++) {
+    const ll_t i = base + r * 256 + threadIdx.x;
+    if (i < n) v += a[i];
+  }
+  const ll_t total = dok_block_sum(v, warp_sums);
+  if (threadIdx.x == 0) sums[blockIdx.x] = total;
+}
+// exclusive scan of sums[0 .. m) by one block, sums[m] = total (m = chunks: 64 for the case above)
+static __global__ void __launch_bounds__(1024) k_scan_sums(ll_t *sums, ll_t m) {
   __shared__ ll_t partial[1024];
-  const ll_t per = (n + 1023) / 1024;
-  const ll_t lo = threadIdx.x * per, hi = lo + per < n ? lo + per : n;
+  const ll_t per = (m + 1023) / 1024;
+  const ll_t lo = threadIdx.x * per, hi = lo + per < m ? lo + per : m;
   ll_t s = 0;
-  for (ll_t i = lo; i < hi; i++) s += a[i];
+  for (ll_t i = lo; i < hi; i++) s += sums[i];
   partial[threadIdx.x] = s;
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {                       // one warp scans the 1024 partial sums, 32 per lane
     ll_t run = 0;
-    for (int i = 0; i < 1024; i++) { const ll_t v = partial[i]; partial[i] = run; run += v; }
-    a[n] = run;
+    for (int i = 0; i < 32; i++) run += partial[threadIdx.x * 32 + i];
+    ll_t inc = run;
+    for (int d = 1; d < 32; d <<= 1) {
+      const ll_t up = __shfl_up_sync(0xffffffffu, inc, d);
+      if ((int)threadIdx.x >= d) inc += up;
+    }
+    ll_t start = inc - run;
+    for (int i = 0; i < 32; i++) { const ll_t v = partial[threadIdx.x * 32 + i]; partial[threadIdx.x * 32 + i] = start; start += v; }
+    if (threadIdx.x == 31) sums[m] = inc;
   }
   __syncthreads();
   ll_t run = partial[threadIdx.x];
-  for (ll_t i = lo; i < hi; i++) { const ll_t v = a[i]; a[i] = run; run += v; }
+  for (ll_t i = lo; i < hi; i++) { const ll_t v = sums[i]; sums[i] = run; run += v; }
+}
+static __global__ void __launch_bounds__(256) k_scan_chunks(ll_t *__restrict__ a, ll_t n, const ll_t *__restrict__ sums, ll_t m) {
+  __shared__ ll_t warp_sums[8];
+  __shared__ ll_t carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const ll_t base = (ll_t)blockIdx.x * DOK_SCAN_CHUNK;
+  if (threadIdx.x == 0) carry = sums[blockIdx.x];
+  __syncthreads();
+  for (int r = 0; r < DOK_SCAN_CHUNK / 256; r++) {
+    const ll_t i = base + r * 256 + threadIdx.x;
+    const ll_t v = i < n ? a[i] : 0;
+    ll_t inc = v;
+    for (int d = 1; d < 32; d <<= 1) {
+      const ll_t up = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += up;
+    }
+    if (lane == 31) warp_sums[warp] = inc;
+    __syncthreads();
+    ll_t before = carry;
+    for (int w = 0; w < warp; w++) before += warp_sums[w];
+    if (i < n) a[i] = before + inc - v;
+    __syncthreads();
+    if (threadIdx.x == 255) carry = before + inc;
+    __syncthreads();
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) a[n] = sums[m];
+}
+// scratch: int64[n / DOK_SCAN_CHUNK + 2]
+static int dok_exclusive_scan(ll_t *a, ll_t n, ll_t *scratch, cudaStream_t st) {
+  const ll_t chunks = (n + DOK_SCAN_CHUNK - 1) / DOK_SCAN_CHUNK;
+  if (chunks == 0) {                             // nothing to scan: the total is zero
+    if (cudaMemsetAsync(a, 0, sizeof(ll_t), st) != cudaSuccess) return dok_check_launch();
+    return DOK_OK;
+  }
+  k_scan_chunk_sums<<<(unsigned)chunks, 256, 0, st>>>(a, n, scratch);
+  int rc = dok_check_launch();
+  if (rc != DOK_OK) return rc;
+  k_scan_sums<<<1, 1024, 0, st>>>(scratch, chunks);
+  rc = dok_check_launch();
+  if (rc != DOK_OK) return rc;
+  k_scan_chunks<<<(unsigned)chunks, 256, 0, st>>>(a, n, scratch, chunks);
+  return dok_check_launch();
 }
 
 // shard_counts[0 .. P) = rows per owner, shard_counts[P .. 2P) = the same rounded up to whole alignment units
@@ -111,15 +186,18 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
                                                                  const __grid_constant__ PartDest dst,
                                                                  ll_t *__restrict__ dest_index) {
   constexpr int WARPS = DOK_TPB / 32, CELLS = DOK_PART_ROUNDS * WARPS;        // cells of one owner, in row order
-  extern __shared__ __align__(16) char stage[];   // STAGED: key rows of the tile sorted by owner, then value rows
-  __shared__ int before[DOK_MAX_SHARDS][CELLS];   // same-owner rows of the tile before cell (round, warp)
+  // dynamic shared memory: before[n_shards][CELLS] (same-owner rows of the tile before cell (round, warp)), then,
+  // STAGED, the key rows of the tile sorted by owner and the value rows
+  extern __shared__ __align__(16) char dyn_smem[];
+  int (*before)[CELLS] = (int (*)[CELLS])dyn_smem;
+  char *stage = dyn_smem + (size_t)n_shards * CELLS * sizeof(int);
   __shared__ int tile_total[DOK_MAX_SHARDS];      // rows of the owner in this tile
   __shared__ int sorted_start[DOK_MAX_SHARDS + 1];// STAGED: first sorted position of the owner's run in the tile
   __shared__ ll_t tile_first[DOK_MAX_SHARDS];     // rows of this owner in earlier tiles
   __shared__ ll_t local_start[DOK_MAX_SHARDS];    // start of the owner's segment in this rank's grouped order
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (dst.status != nullptr && *dst.status != 0) return;       // uniform over the grid
-  for (int i = threadIdx.x; i < n_shards * CELLS; i += DOK_TPB) (&before[0][0])[i] = 0;
+  for (int i = threadIdx.x; i < n_shards * CELLS; i += DOK_TPB) ((int *)dyn_smem)[i] = 0;
   // one thread per owner fetches its words (a single thread walking the owners would wait for 2 * n_shards dependent
   // loads at the head of every block)
   if ((int)threadIdx.x < n_shards) {
@@ -186,7 +264,7 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, i
     sorted_start[n_shards] = run;
   }
   __syncthreads();
-  char *stage_values = stage + (size_t)DOK_PART_TILE * kb;
+  char *stage_values = stage + (size_t)DOK_PART_TILE * kb;      // cell counts are a multiple of 16 bytes: still aligned
 #pragma unroll
   for (int r = 0; r < DOK_PART_ROUNDS; r++) {
     if (owner[r] < 0) continue;
@@ -216,14 +294,15 @@ static int dok_launch_scatter(const RowKeys &rk, int kb, const char *values, int
                               cudaStream_t st) {
   const ll_t tiles = dok_partition_tiles(rk.n);
   const size_t stage_bytes = (size_t)DOK_PART_TILE * (size_t)(kb + (values ? vb : 0));
+  const size_t cell_bytes = (size_t)n_shards * DOK_PART_ROUNDS * (DOK_TPB / 32) * sizeof(int);
   if (n_shards > 2 && stage_bytes <= DOK_PART_STAGE_LIMIT) {
     // more than the 48 KiB a kernel gets by default: the attribute is per device, and setting it again is cheap
-    cudaFuncSetAttribute(k_part_scatter<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DOK_PART_STAGE_LIMIT);
-    k_part_scatter<true><<<(unsigned)tiles, DOK_TPB, stage_bytes, st>>>(rk, kb, values, vb, owners, n_shards, tiles,
-                                                                        tile_offsets, shard_counts, dst, dest_index);
+    cudaFuncSetAttribute(k_part_scatter<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DOK_PART_STAGE_LIMIT + 16 * 1024);
+    k_part_scatter<true><<<(unsigned)tiles, DOK_TPB, cell_bytes + stage_bytes, st>>>(rk, kb, values, vb, owners, n_shards, tiles,
+                                                                                     tile_offsets, shard_counts, dst, dest_index);
   } else {
-    k_part_scatter<false><<<(unsigned)tiles, DOK_TPB, 0, st>>>(rk, kb, values, vb, owners, n_shards, tiles, tile_offsets,
-                                                               shard_counts, dst, dest_index);
+    k_part_scatter<false><<<(unsigned)tiles, DOK_TPB, cell_bytes, st>>>(rk, kb, values, vb, owners, n_shards, tiles, tile_offsets,
+                                                                        shard_counts, dst, dest_index);
   }
   return dok_check_launch();
 }
@@ -299,6 +378,10 @@ static __global__ void __launch_bounds__(DOK_TPB) k_unpermute(const char *__rest
 extern "C" {
 
 int64_t dok_partition_tiles(int64_t n) { return (n + DOK_PART_TILE - 1) / DOK_PART_TILE; }
+int64_t dok_partition_offset_words(int64_t n, int n_shards) {
+  const int64_t cells = (int64_t)n_shards * dok_partition_tiles(n);
+  return cells + 1 + (cells + DOK_SCAN_CHUNK - 1) / DOK_SCAN_CHUNK + 2;      // offsets, total, scan scratch
+}
 int64_t dok_partition_capacity(int64_t n, int n_shards) { return n + (int64_t)n_shards * (DOK_SEGMENT_ALIGN_ROWS - 1); }
 
 int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, uint8_t *owners,
@@ -314,8 +397,8 @@ int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64
     int rc = dok_check_launch();
     if (rc != DOK_OK) return rc;
   }
-  k_part_scan<<<1, 1024, 0, st>>>((ll_t *)tile_offsets, (ll_t)n_shards * tiles);
-  int rc = dok_check_launch();
+  const ll_t cells = (ll_t)n_shards * tiles;
+  int rc = dok_exclusive_scan((ll_t *)tile_offsets, cells, (ll_t *)tile_offsets + cells + 1, st);
   if (rc != DOK_OK) return rc;
   k_part_shard_counts<<<1, DOK_MAX_SHARDS, 0, st>>>((const ll_t *)tile_offsets, n_shards, tiles, (ll_t *)shard_counts);
   return dok_check_launch();

@@ -322,8 +322,7 @@ class CudaShardOps:
         lib = L.lib()
         n = keys.shape[0]
         with torch.cuda.device(self.device):
-            tiles = lib.dok_partition_tiles(n)
-            offsets = torch.empty(world * tiles + 1, device=self.device, dtype=torch.long)
+            offsets = torch.empty(lib.dok_partition_offset_words(n, world), device=self.device, dtype=torch.long)
             counts = torch.empty(2 * world, device=self.device, dtype=torch.long)
             owners = torch.empty(max(n, 1), device=self.device, dtype=torch.uint8)
             L.check(lib.dok_shard_partition_count(self._routing_hash(keys), L.ptr(keys), n, world, L.ptr(owners),
@@ -341,9 +340,8 @@ class CudaShardOps:
         keys = keys.contiguous()
         with torch.cuda.device(self.device):
             st = L.stream_ptr(self.device)
-            tiles = lib.dok_partition_tiles(n)
             cap = lib.dok_partition_capacity(n, world)
-            offsets = torch.empty(world * tiles + 1, device=self.device, dtype=torch.long)
+            offsets = torch.empty(lib.dok_partition_offset_words(n, world), device=self.device, dtype=torch.long)
             counts = torch.empty(2 * world, device=self.device, dtype=torch.long)
             owners = torch.empty(n, device=self.device, dtype=torch.uint8)
             L.check(lib.dok_shard_partition_count(self._routing_hash(keys), L.ptr(keys), n, world, L.ptr(owners),

@@ -294,7 +294,8 @@ int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, cons
 
 /* Owner shard of each row: mulhi64(mix(uuid ^ salt), n_shards).  Stable partition of a batch by owner:
  * step 1 computes every row's owner (owners[n], one byte per row), a per-tile histogram and its scan ->
- * tile_offsets int64[n_shards * dok_partition_tiles(n) + 1] and shard_counts int64[2 * n_shards]: rows per
+ * tile_offsets int64[dok_partition_offset_words(n, n_shards)] (the offsets, their total, and the scan's scratch behind
+ * them) and shard_counts int64[2 * n_shards]: rows per
  * owner, then the same rounded up to multiples of 16 rows;
  * step 2 scatters key rows of key_bytes (and value rows, if values != NULL) into keys_out/values_out grouped by
  * owner, order within an owner preserved.  Each owner's segment starts at the sum of the ROUNDED counts before it
@@ -302,6 +303,7 @@ int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, cons
  * and must be ignored by the receiver.  keys_out/values_out need dok_partition_capacity(n, n_shards) rows.
  * dest_index[n] (may be NULL) receives each row's position in that grouped order (for dok_shard_unpermute). */
 int64_t dok_partition_tiles(int64_t n);
+int64_t dok_partition_offset_words(int64_t n, int n_shards);
 int64_t dok_partition_capacity(int64_t n, int n_shards);
 int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64_t n, int n_shards, uint8_t *owners,
                               int64_t *tile_offsets, int64_t *shard_counts, void *stream);
