@@ -38,7 +38,7 @@ N_BATCHES = 4          # distinct query/update batches rotated over the steps (e
 # DRAM bytes per operation of the kernels, dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture divided by
 # the rows of the launch (profiles/k_*_c5_shard_2e26keys.md; the capture ran at 2^26 keys and 2^24 rows, traffic per row
 # does not depend on the size once the table is much larger than L2)
-TRAFFIC_BYTES_PER_OP = {"get": 171.5, "set": 210.4, "remove": 230.3}
+TRAFFIC_BYTES_PER_OP = {"get": 169.6, "set": 206.9, "remove": 237.4}
 
 
 def parse_args():
@@ -62,6 +62,10 @@ def parse_args():
     ap.add_argument("--no-shard-point", action="store_true",
                     help="1 GPU, strong scaling: skip the extra leg on a 2^28-key table (the size the reference's kernels can hold)")
     ap.add_argument("--no-extras", action="store_true", help="1 GPU: skip the legs on BASELINE configs 1', 2, 3 and 4")
+    ap.add_argument("--small-dok", action="store_true",
+                    help="instead of the benchmark: one small pass over the DOK tensor and partition kernels (fused "
+                         "get over selectors, to_sparse_coo, from_dense, partition scatter) on tables a few times L2; "
+                         "the case to capture them under a profiler")
     ap.add_argument("--hw-probe", action="store_true",
                     help="instead of the benchmark: rate of random requests of 8..128 bytes over buffers of --probe-mib "
                          "MiB (what bounds every probing kernel); one JSON line")
@@ -857,9 +861,42 @@ def hw_probe(args):
                       "l2_fetch_granularity_limit": limit, "rows": rows}))
 
 
+def small_dok(args):
+    """One launch each of the DOK-side and routing kernels on small inputs (tables of 0.27-0.54 GB: a few times L2)."""
+    import torch
+    from doksparse_b200 import SparseDOKTensor
+    from doksparse_b200.sharded import CudaShardOps
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    g = torch.Generator(device=device).manual_seed(0)
+    n_rows = n_cols = 1 << 15
+    lin = torch.unique(torch.randint(0, n_rows * n_cols, (5 << 20,), generator=g, device=device))[: 1 << 22]
+    np.random.seed(0)
+    t = SparseDOKTensor((n_rows, n_cols), torch.stack([lin // n_cols, lin % n_cols]), torch.randn(lin.numel(), generator=g, device=device))
+    i = torch.randint(0, n_rows, (1 << 22,), generator=g, device=device)
+    j = torch.randint(0, n_cols, (1 << 22,), generator=g, device=device)
+    out = {"nnz": int(lin.numel()), "n_buckets": t.storage().n_buckets}
+    got = t[i, j]                                                    # k_get over SelKeys
+    t[i, j] = 1.0                                                    # k_set_claim over SelKeys (with its rehash)
+    coo = t.to_sparse_coo()                                          # k_compact_count / k_compact_scatter
+    block = torch.randn(4096, 4096, generator=g, device=device) * (torch.rand(4096, 4096, generator=g, device=device) < 0.01)
+    d = SparseDOKTensor.from_dense(block)                            # k_dense_count / k_dense_insert
+    ops = CudaShardOps(device, 1024, fixed_parameters(), 2.0, 0.75)
+    idx = torch.arange(1 << 24, device=device)
+    keys, values = mix62_torch(idx)[:, None].contiguous(), value_of_index(idx, torch).contiguous()
+    gk, gv, dest, counts = ops.partition(keys, values, 8)           # k_part_count / scan / k_part_scatter<staged>
+    ops.unpermute(gv, None, dest)                                    # k_unpermute
+    torch.cuda.synchronize()
+    out.update({"getitem_sum": float(got.sum()), "coo_nnz": int(coo._nnz()), "from_dense_nnz": d._nnz(),
+                "partition_counts": counts[0].tolist()})
+    print(json.dumps({"small_dok": out}))
+
+
 def main():
     args = parse_args()
-    if args.hw_probe:
+    if args.small_dok:
+        small_dok(args)
+    elif args.hw_probe:
         hw_probe(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -61,58 +61,96 @@ __global__ void __launch_bounds__(DOK_TPB) k_dense_count(const T *__restrict__ d
 
 struct DenseShape { int ndim; ll_t sizes[DOK_MAX_KEY_SIZE]; };
 
+// A block takes DOK_DENSE_SPAN consecutive elements at a time: every thread looks at DOK_DENSE_ROUNDS of them
+// (coalesced), the non-zero ones are collected in shared memory (position inside the span and value), and the block
+// then inserts the collected elements 256 at a time with every lane busy.  At the 1 % density of BASELINE config 3 a
+// warp of the one-element-per-thread form ran the whole cooperative insert for a single active lane.
+#define DOK_DENSE_ROUNDS 8
+#define DOK_DENSE_SPAN (DOK_TPB * DOK_DENSE_ROUNDS)
+
 template <int SB, typename T>
 __global__ void __launch_bounds__(DOK_TPB) k_dense_insert(DevTable t, DevHash hp, const T *__restrict__ dense, ll_t numel,
                                                           int is_float, DenseShape shape, ll_t *counters) {
-  const ll_t stride = (ll_t)gridDim.x * DOK_TPB;
-  for (ll_t base = (ll_t)blockIdx.x * DOK_TPB; base < numel; base += stride) {     // uniform over the block
-    const ll_t i = base + threadIdx.x;
-    int outcome = -1;
-    T v = 0;
-    bool active = false;
-    if (i < numel) {
-      v = __ldcs(dense + i);
-      active = dok_nonzero<T>(v, is_float);
-    }
-    ll_t idx[DOK_MAX_KEY_SIZE];
-    KeyHash kh{0, 0};
-    if (active) {
-      // unravel the row-major position into the index tuple; each index is one factor of the hash products
-      ull_t rem = (ull_t)i;
+  __shared__ T found_value[DOK_DENSE_SPAN];
+  __shared__ unsigned short found_at[DOK_DENSE_SPAN];
+  __shared__ int n_found;
+  const ll_t stride = (ll_t)gridDim.x * DOK_DENSE_SPAN;
+  int claimed = 0, reused = 0, failed = 0, hits = 0;
+  for (ll_t base = (ll_t)blockIdx.x * DOK_DENSE_SPAN; base < numel; base += stride) {     // uniform over the block
+    if (threadIdx.x == 0) n_found = 0;
+    __syncthreads();
 #pragma unroll
-      for (int d = DOK_MAX_KEY_SIZE - 1; d >= 0; d--) {
-        idx[d] = 0;
-        if (d < shape.ndim) {
-          const ull_t size = (ull_t)shape.sizes[d];
-          const ull_t q = rem / size;
-          idx[d] = (ll_t)(rem - q * size);
-          rem = q;
-        }
+    for (int r = 0; r < DOK_DENSE_ROUNDS; r++) {
+      const int j = r * DOK_TPB + (int)threadIdx.x;
+      const ll_t i = base + j;
+      T v = 0;
+      bool nz = false;
+      if (i < numel) {
+        v = __ldcs(dense + i);
+        nz = dok_nonzero<T>(v, is_float);
       }
-      ll_t u = dok_uuid_term(idx[0], hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
-      ull_t h = (ull_t)idx[0] * (ull_t)hp.a1[0] + (ull_t)hp.b1[0];
+      const unsigned votes = __ballot_sync(0xffffffffu, nz);
+      int at = 0;
+      if ((threadIdx.x & 31) == 0 && votes) at = atomicAdd(&n_found, __popc(votes));
+      at = __shfl_sync(0xffffffffu, at, 0) + __popc(votes & ((1u << (threadIdx.x & 31)) - 1u));
+      if (nz) {
+        found_value[at] = v;
+        found_at[at] = (unsigned short)j;
+      }
+    }
+    __syncthreads();
+    const int total = n_found;
+    for (int first = 0; first < total; first += DOK_TPB) {                                // uniform over the block
+      const int k = first + (int)threadIdx.x;
+      bool active = k < total;
+      int outcome = -1;
+      T v = 0;
+      ll_t idx[DOK_MAX_KEY_SIZE];
+      KeyHash kh{0, 0};
+      if (active) {
+        v = found_value[k];
+        // unravel the row-major position into the index tuple; each index is one factor of the hash products
+        ull_t rem = (ull_t)(base + found_at[k]);
 #pragma unroll
-      for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
-        if (d < shape.ndim) {
-          u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
-          h *= (ull_t)idx[d] * (ull_t)hp.a1[d] + (ull_t)hp.b1[d];
+        for (int d = DOK_MAX_KEY_SIZE - 1; d >= 0; d--) {
+          idx[d] = 0;
+          if (d < shape.ndim) {
+            const ull_t size = (ull_t)shape.sizes[d];
+            const ull_t q = rem / size;
+            idx[d] = (ll_t)(rem - q * size);
+            rem = q;
+          }
         }
-      kh = KeyHash{dok_llabs(u), (ll_t)h};
-    }
-    active = dok_in_window(t, kh, active);
-    const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
-    if (active && slot >= 0) {
-      ll_t *krow = (ll_t *)dok_key_row(t, slot);
+        ll_t u = dok_uuid_term(idx[0], hp.a[0], hp.b[0], hp.p[0], hp.m[0]);
+        ull_t h = (ull_t)idx[0] * (ull_t)hp.a1[0] + (ull_t)hp.b1[0];
 #pragma unroll
-      for (int d = 0; d < DOK_MAX_KEY_SIZE; d++) if (d < shape.ndim) krow[hp.perm[d]] = idx[d];
-      *(T *)dok_value_ptr(t, slot) = v;
+        for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
+          if (d < shape.ndim) {
+            u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], hp.a[d], hp.b[d], hp.p[d], hp.m[d]));
+            h *= (ull_t)idx[d] * (ull_t)hp.a1[d] + (ull_t)hp.b1[d];
+          }
+        kh = KeyHash{dok_llabs(u), (ll_t)h};
+      }
+      active = dok_in_window(t, kh, active);
+      const ll_t slot = dok_find_or_claim<SB>(t, kh, active, &outcome);
+      if (active && slot >= 0) {
+        ll_t *krow = (ll_t *)dok_key_row(t, slot);
+#pragma unroll
+        for (int d = 0; d < DOK_MAX_KEY_SIZE; d++) if (d < shape.ndim) krow[hp.perm[d]] = idx[d];
+        *(T *)dok_value_ptr(t, slot) = v;
+      }
+      claimed += outcome == DOK_OUT_CLAIMED_EMPTY;
+      reused += outcome == DOK_OUT_REUSED;
+      failed += outcome == DOK_OUT_FAILED;
+      hits += outcome == DOK_OUT_FOUND;
     }
-    if (counters) {
-      dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY);
-      dok_warp_add(counters + DOK_CNT_REUSED_REMOVED, outcome == DOK_OUT_REUSED);
-      dok_warp_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
-      dok_warp_add(counters + DOK_CNT_HITS, outcome == DOK_OUT_FOUND);
-    }
+    __syncthreads();                                     // the lists are rewritten by the next span
+  }
+  if (counters) {
+    dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, claimed);
+    dok_warp_add(counters + DOK_CNT_REUSED_REMOVED, reused);
+    dok_warp_add(counters + DOK_CNT_FAILED, failed);
+    dok_warp_add(counters + DOK_CNT_HITS, hits);
   }
 }
 
@@ -305,7 +343,7 @@ int dok_dense_insert_nonzero(const dok_table *t, const dok_hash_params *hp, cons
     prod *= shape.sizes[d];
   }
   if (prod != numel) return DOK_BAD_ARG;
-  const unsigned grid = streaming_grid(numel);
+  const unsigned grid = streaming_grid((numel + DOK_DENSE_ROUNDS - 1) / DOK_DENSE_ROUNDS);
   cudaStream_t st = (cudaStream_t)stream;
   int rc = DOK_OK;
   switch (dt.vb) {

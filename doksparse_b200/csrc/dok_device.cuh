@@ -156,6 +156,13 @@ struct RowKeys {          // contiguous [n, ks] rows of the key dtype (closed_ha
     e = (ll_t)blockIdx.y * slice_rows + j;
     return j < slice_rows && j < slice_counts[blockIdx.y];
   }
+  // the same for position j of the batch (of slice blockIdx.y), for kernels that stride over the rows
+  __device__ __forceinline__ bool at(ll_t j, ll_t &e) const {
+    if (slice_rows == 0) { e = j; return j < n; }
+    e = (ll_t)blockIdx.y * slice_rows + j;
+    return j < slice_rows && j < slice_counts[blockIdx.y];
+  }
+  __device__ __forceinline__ ll_t span() const { return slice_rows == 0 ? n : slice_rows; }
   // block-uniform: nothing for this block to do
   __device__ __forceinline__ bool idle() const {
     if (slice_rows == 0) return false;
@@ -200,6 +207,8 @@ struct SelKeys {
   ll_t n;
   __device__ __forceinline__ ll_t count() const { return n; }
   __device__ __forceinline__ bool row(ll_t &e) const { e = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x; return e < n; }
+  __device__ __forceinline__ bool at(ll_t j, ll_t &e) const { e = j; return j < n; }
+  __device__ __forceinline__ ll_t span() const { return n; }
   __device__ __forceinline__ bool idle() const { return false; }
   // element offsets of batch element e into each of the ndim index tensors (fully unrolled over the
   // maximum ndim with predication, so `off` stays in registers)

@@ -176,16 +176,21 @@ __global__ void __launch_bounds__(DOK_TPB) k_set_resolve(DevTable t, DevHash hp,
                                                          const ll_t *__restrict__ slot_in, ll_t epoch) {
   if (slot_in[keys.count()] == 0) return;        // the first kernel met no duplicate: every row is already in place
   if (keys.idle()) return;
-  ll_t e;
-  if (!keys.row(e)) return;
-  const ll_t slot = slot_in[e];
-  if (slot < 0) return;
-  if (t.win_hi != 0) {                           // windowed passes: by the slot's own group (each slot has one pass)
-    const ll_t g = slot / t.spg;
-    if (g < t.win_lo || g >= t.win_hi) return;
+  // a few blocks per SM stride over the rows: the usual launch has nothing to do, and a grid of one block per 256
+  // rows would cost a millisecond at 2^28 rows just to find that out
+  const ll_t span = keys.span(), stride = (ll_t)gridDim.x * DOK_TPB;
+  for (ll_t j = (ll_t)blockIdx.x * DOK_TPB + threadIdx.x; j < span; j += stride) {
+    ll_t e;
+    if (!keys.at(j, e)) continue;
+    const ll_t slot = slot_in[e];
+    if (slot < 0) continue;
+    if (t.win_hi != 0) {                         // windowed passes: by the slot's own group (each slot has one pass)
+      const ll_t g = slot / t.spg;
+      if (g < t.win_lo || g >= t.win_hi) continue;
+    }
+    if (__ldcg(dok_stamp_ptr(t, slot)) != (dok_stamp(epoch, e) | 1)) continue;
+    dok_write_row(t, hp, keys, values, e, slot, true);
   }
-  if (__ldcg(dok_stamp_ptr(t, slot)) != (dok_stamp(epoch, e) | 1)) return;
-  dok_write_row(t, hp, keys, values, e, slot, true);
 }
 
 // contiguous value rows [n, value_bytes]
@@ -198,7 +203,9 @@ inline int launch_set_general(const DevTable &t, const DevHash &hp, const Keys &
   DOK_DISPATCH_SB(t, DOK_FOR_WINDOWS(t, rc, (k_set_claim<SB><<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, values, (ll_t *)slot_scratch,
                                                                                        (ll_t)epoch, out_stored, (ll_t *)counters))));
   if (rc != DOK_OK) return rc;
-  DOK_FOR_WINDOWS(t, rc, (k_set_resolve<<<grid, DOK_TPB, 0, st>>>(wt, hp, keys, values, (const ll_t *)slot_scratch, (ll_t)epoch)));
+  dim3 few = grid;
+  if (few.x > 148 * 8) few.x = 148 * 8;
+  DOK_FOR_WINDOWS(t, rc, (k_set_resolve<<<few, DOK_TPB, 0, st>>>(wt, hp, keys, values, (const ll_t *)slot_scratch, (ll_t)epoch)));
   return rc;
 }
 

@@ -178,7 +178,7 @@ struct PartDest {
 // dest_index[e] is always the row's position in THIS rank's grouped order (segments at the padded local offsets),
 // which is where the owner's answer for the row will be found.
 template <bool STAGED>
-static __global__ void __launch_bounds__(DOK_TPB) k_part_scatter(RowKeys keys, int kb, const char *__restrict__ values,
+static __global__ void __launch_bounds__(DOK_TPB, 6) k_part_scatter(RowKeys keys, int kb, const char *__restrict__ values,
                                                                  int vb, const uint8_t *__restrict__ owners,
                                                                  int n_shards, ll_t tiles,
                                                                  const ll_t *__restrict__ tile_offsets,
