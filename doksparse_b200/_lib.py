@@ -99,6 +99,7 @@ def _declare(lib):
         "dok_dok_get": ([TP, HP, SP, P, P, P, P, P], I),
         "dok_dok_count_exists": ([TP, HP, SP, P, P], I),
         "dok_dok_zero_items": ([TP, HP, SP, P, P], I),
+        "dok_dok_gather_insert": ([TP, HP, SP, TP, HP, P, P], I),
         "dok_dok_set_dense": ([TP, HP, SP, P, P, P, I64, P, P], I),
         "dok_dense_count_nonzero": ([P, I64, I, I, P, P], I),
         "dok_dense_insert_nonzero": ([TP, HP, P, P, I64, I, P, P], I),

@@ -224,6 +224,61 @@ __global__ void __launch_bounds__(DOK_TPB) k_rekey_insert(DevTable src, DevTable
   }
 }
 
+// ---- sparse gather: lookup over the selectors and insert of the hits into a second table, one kernel -----
+
+// One thread per selector element: the key formed from the selectors is looked up in `src`; a hit is inserted into
+// `dst` under the element's POSITION in the selection (its index tuple in the selection's shape, int64), with the
+// stored value.  Positions are pairwise different, so every insert claims a fresh slot.  Replaces
+// sparse_dok_get_items (sparse_dok_tensor_impl.cu:110-160), which does the same per thread.
+template <int SBS, int SBD>
+__global__ void __launch_bounds__(DOK_TPB) k_gather_insert(DevTable src, DevHash shp, SelKeys sel, DevTable dst, DevHash dhp,
+                                                           ll_t *counters) {
+  ll_t e;
+  const bool active = sel.row(e);
+  KeyHash kh{0, 0};
+  if (active) kh = sel.hash(shp, e);
+  const Located loc = dok_locate<SBS, 1, false>(src, kh, e, active, nullptr, NoEmit());
+  const bool hit = active && loc.found >= 0;
+  ll_t idx[DOK_MAX_KEY_SIZE];
+  KeyHash kd{0, 0};
+  if (hit) {
+    // the element's index tuple in the selection's shape (row-major); a 0-dim selection is position (0,)
+    ull_t rem = (ull_t)e;
+#pragma unroll
+    for (int d = DOK_MAX_KEY_SIZE - 1; d >= 0; d--) {
+      idx[d] = 0;
+      if (d < sel.s.selector_ndim) {
+        const ull_t size = (ull_t)sel.s.sizes[d];
+        const ull_t q = rem / size;
+        idx[d] = (ll_t)(rem - q * size);
+        rem = q;
+      }
+    }
+    ll_t u = dok_uuid_term(idx[0], dhp.a[0], dhp.b[0], dhp.p[0], dhp.m[0]);
+    ull_t h = (ull_t)idx[0] * (ull_t)dhp.a1[0] + (ull_t)dhp.b1[0];
+#pragma unroll
+    for (int d = 1; d < DOK_MAX_KEY_SIZE; d++)
+      if (d < dhp.ks) {
+        u = (ll_t)((ull_t)u * (ull_t)dok_uuid_term(idx[d], dhp.a[d], dhp.b[d], dhp.p[d], dhp.m[d]));
+        h *= (ull_t)idx[d] * (ull_t)dhp.a1[d] + (ull_t)dhp.b1[d];
+      }
+    kd = KeyHash{dok_llabs(u), (ll_t)h};
+  }
+  int outcome = -1;
+  const ll_t slot = dok_find_or_claim<SBD>(dst, kd, hit, &outcome);
+  if (hit && slot >= 0) {
+    ll_t *krow = (ll_t *)dok_key_row(dst, slot);
+#pragma unroll
+    for (int d = 0; d < DOK_MAX_KEY_SIZE; d++) if (d < dhp.ks) krow[dhp.perm[d]] = idx[d];
+    dok_store_value(dst, slot, dok_value_ptr(src, loc.found));
+  }
+  if (counters) {
+    dok_warp_add(counters + DOK_CNT_HITS, hit);
+    dok_warp_add(counters + DOK_CNT_CLAIMED_EMPTY, outcome == DOK_OUT_CLAIMED_EMPTY || outcome == DOK_OUT_REUSED);
+    dok_warp_add(counters + DOK_CNT_FAILED, outcome == DOK_OUT_FAILED);
+  }
+}
+
 static unsigned streaming_grid(ll_t numel) {
   const ll_t blocks = (numel + DOK_TPB - 1) / DOK_TPB;
   const ll_t cap = 148 * 8;   // 8 resident blocks of 256 threads per SM
@@ -279,6 +334,33 @@ int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_s
     sv.strides[j] = j < sel->selector_ndim ? src_strides[j] : 0;
   }
   return launch_set_general(dt, dh, sk, sv, slot_scratch, epoch, nullptr, counters, (cudaStream_t)stream);
+}
+
+int dok_dok_gather_insert(const dok_table *src, const dok_hash_params *src_hp, const dok_selectors *sel,
+                          const dok_table *dst, const dok_hash_params *dst_hp, int64_t *counters, void *stream) {
+  DevHash sh, dh;
+  DevTable st_, dt;
+  SelKeys sk;
+  if (!prepare(src, src_hp, &st_, &sh) || !prepare(dst, dst_hp, &dt, &dh) || !make_sel(sel, sh, &sk)) return DOK_BAD_ARG;
+  if (dh.dtype != DOK_I64 || st_.vb != dt.vb || dh.ks != (sel->selector_ndim > 0 ? sel->selector_ndim : 1)) return DOK_BAD_ARG;
+  if (st_.sb > 128 || dt.sb > 128) return DOK_BAD_ARG;                 // DOK tables: int64 index keys, one value element
+  if (dok_window_passes(st_) > 1 || dok_window_passes(dt) > 1) return DOK_TOO_LARGE;   // callers take the two-step route
+  if (sk.n == 0) return DOK_OK;
+  const unsigned grid = (unsigned)((sk.n + DOK_TPB - 1) / DOK_TPB);
+  cudaStream_t st = (cudaStream_t)stream;
+#define DOK_GATHER(SBS) \
+  switch (dt.sb) { \
+    case 32: k_gather_insert<SBS, 32><<<grid, DOK_TPB, 0, st>>>(st_, sh, sk, dt, dh, (ll_t *)counters); break; \
+    case 64: k_gather_insert<SBS, 64><<<grid, DOK_TPB, 0, st>>>(st_, sh, sk, dt, dh, (ll_t *)counters); break; \
+    default: k_gather_insert<SBS, 128><<<grid, DOK_TPB, 0, st>>>(st_, sh, sk, dt, dh, (ll_t *)counters); break; \
+  }
+  switch (st_.sb) {
+    case 32: DOK_GATHER(32); break;
+    case 64: DOK_GATHER(64); break;
+    default: DOK_GATHER(128); break;
+  }
+#undef DOK_GATHER
+  return dok_check_launch();
 }
 
 int dok_dok_rekey_insert(const dok_table *src, const dok_hash_params *src_hp, const int64_t *src_sizes,

@@ -248,30 +248,47 @@ class SparseDOKTensor(object):
     def __spgetitem__(self, selectors):
         """Sparse gather (sparse_dok_tensor.py:342-350 -> get_items, sparse_dok_tensor_impl.py:148-232; kernels
         sparse_dok_tensor_impl.cu:110-268): a SparseDOKTensor of the selection's broadcast shape that holds the selected
-        positions which are stored, keyed by their position in the selection.  One fused lookup over the selectors,
-        a compaction of the hits, and one insert of pairwise different keys into a map of int(2 * hits) buckets (the
-        reference's size).  A selection without a hit gives an empty tensor (the reference builds a 0-bucket map)."""
+        positions which are stored, keyed by their position in the selection.  Two fused kernels over the selectors,
+        like the reference: a count of the hits (it sizes the new map: int(2 * hits) buckets), then lookup and insert
+        into the new map in one kernel.  A selection without a hit gives an empty tensor (the reference builds a
+        0-bucket map)."""
         selectors, _ = self._handle_selectors(selectors)
         shape = tuple(selectors[0].shape)
         hashmap = self._hashmap
         n_sel = int(selectors[0].numel())
         if hashmap._values is None or n_sel == 0:
             return SparseDOKTensor(size=shape, device=self.device, dtype=self.dtype)
-        values = torch.empty(n_sel, device=self.device, dtype=self.dtype)
-        found = torch.empty(n_sel, device=self.device, dtype=torch.bool)
         sel = _selectors_struct(selectors)
+        lib = L.lib()
+        # pass 1: how many selected positions are stored (sizes the new map like the reference: int(2 * hits) buckets)
+        cnt = hashmap._counters()
         with torch.cuda.device(self.device):
-            L.check(L.lib().dok_dok_get(hashmap._c_table(), hashmap._c_hash(), ctypes.byref(sel), L.ptr(values),
-                                        L.ptr(found), None, None, L.stream_ptr(self.device)), "dok_dok_get")
-        hits = found.nonzero().flatten()                       # row-major positions in the selection
-        n = int(hits.numel())
+            L.check(lib.dok_dok_count_exists(hashmap._c_table(), hashmap._c_hash(), ctypes.byref(sel), L.ptr(cnt),
+                                             L.stream_ptr(self.device)), "dok_dok_count_exists")
+        n = int(cnt[L.CNT_HITS].item())
         if not shape:
             shape = (1,)                                       # all selectors scalar: a one-element selection
         if n == 0:
             return SparseDOKTensor(size=shape, device=self.device, dtype=self.dtype)
-        keys = torch.stack(torch.unravel_index(hits, shape), dim=1)
         out = CudaClosedHashmap(n_buckets=int(n * 2.0), device=self.device)
-        out.set(keys.contiguous(), values[hits][:, None].contiguous(), assume_unique=True)
+        out._begin_bulk_insert((len(shape),), torch.long, (1,), self.dtype, n)
+        # pass 2: lookup and insert in ONE kernel (positions in the selection are the new keys)
+        cnt = hashmap._counters()
+        with torch.cuda.device(self.device):
+            rc = lib.dok_dok_gather_insert(hashmap._c_table(), hashmap._c_hash(), ctypes.byref(sel), out._c_table(),
+                                           out._c_hash(), L.ptr(cnt), L.stream_ptr(self.device))
+        if rc == 3:                                            # a table served in passes: lookup, then insert
+            values = torch.empty(n_sel, device=self.device, dtype=self.dtype)
+            found = torch.empty(n_sel, device=self.device, dtype=torch.bool)
+            with torch.cuda.device(self.device):
+                L.check(lib.dok_dok_get(hashmap._c_table(), hashmap._c_hash(), ctypes.byref(sel), L.ptr(values),
+                                        L.ptr(found), None, None, L.stream_ptr(self.device)), "dok_dok_get")
+            hits = found.nonzero().flatten()
+            keys = torch.stack(torch.unravel_index(hits, shape), dim=1)
+            out.set_rows(keys.contiguous(), values[hits][:, None].contiguous(), assume_unique=True)
+            out._n_elements.fill_(n)
+        else:
+            L.check(rc, "dok_dok_gather_insert")
         return SparseDOKTensor.from_storage(out, size=shape)
 
     def _set_items_sparse(self, src, selectors):

@@ -263,6 +263,14 @@ int dok_dok_set_dense(const dok_table *t, const dok_hash_params *hp, const dok_s
 int dok_dok_zero_items(const dok_table *t, const dok_hash_params *hp, const dok_selectors *sel,
                        int64_t *counters, void *stream);
 
+/* Sparse gather in one kernel (replaces sparse_dok_get_items, sparse_dok_tensor_impl.cu:110-160, launcher
+ * sparse_dok_tensor_impl.py:148-232): every selected element that is stored in src is inserted into dst -- an
+ * initialised table with int64 keys of max(selector_ndim, 1) elements, the same value_bytes and room for the hits --
+ * under its index tuple in the selection's shape.  counters[DOK_CNT_HITS] += hits, [DOK_CNT_CLAIMED_EMPTY] += rows
+ * inserted, [DOK_CNT_FAILED] += rows that found dst full.  DOK_TOO_LARGE for tables served in several passes. */
+int dok_dok_gather_insert(const dok_table *src, const dok_hash_params *src_hp, const dok_selectors *sel,
+                          const dok_table *dst, const dok_hash_params *dst_hp, int64_t *counters, void *stream);
+
 /* from_dense: counts the non-zero elements of a contiguous dense tensor (step 1), then inserts
  * (unravelled index -> value) for each of them (step 2) without materialising COO indices.
  * Replaces tensor.to_sparse() + coalesce + set of SparseDOKTensor.from_dense (sparse_dok_tensor.py:71-90).
