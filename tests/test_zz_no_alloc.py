@@ -59,3 +59,32 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
     assert rc == 3      # DOK_TOO_LARGE
     rc, full = count_new(m, torch.arange(max_rows, device="cuda:0")[:, None] + (1 << 50), static=True)
     assert rc == 0 and full == max_rows
+
+
+def test_static_calls_take_no_device_memory_and_run_on_any_stream():
+    """What the entry point is for: after the first call on a device (which looks up the scratch array's address)
+    further calls leave the device's free memory untouched, on the default stream and on another one."""
+    from doksparse_b200 import CudaClosedHashmap, _lib as L
+    lib = L.lib()
+    np.random.seed(4)
+    m = CudaClosedHashmap(n_buckets=1 << 16)
+    g = torch.Generator(device="cuda:0").manual_seed(1)
+    stored = torch.randint(0, 1 << 40, (20_000, 1), device="cuda:0", generator=g)
+    m.set(stored, torch.zeros(20_000, 2, device="cuda:0"))
+    batch = torch.cat([stored[:5000], torch.arange(9000, device="cuda:0")[:, None] + (1 << 45)]).contiguous()
+    cnt = torch.zeros(L.N_COUNTERS, device="cuda:0", dtype=torch.long)          # everything is allocated up front
+    side = torch.cuda.Stream(device="cuda:0")
+    table, params = m._c_table(), m._c_hash()
+    assert lib.dok_map_count_new_static(table, params, L.ptr(batch), batch.shape[0], L.ptr(cnt), L.stream_ptr(torch.device("cuda:0"))) == 0
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(0)
+    reserved_before = torch.cuda.memory_reserved(0)
+    for rep in range(4):
+        stream = side if rep % 2 else torch.cuda.current_stream()
+        with torch.cuda.stream(stream):
+            assert lib.dok_map_count_new_static(table, params, L.ptr(batch), batch.shape[0], L.ptr(cnt),
+                                                ctypes.c_void_p(stream.cuda_stream)) == 0
+        stream.synchronize()              # calls share the scratch array: one at a time
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_after >= free_before and torch.cuda.memory_reserved(0) == reserved_before
+    assert int(cnt[L.CNT_CLAIMED_EMPTY].item()) == 5 * 9000
