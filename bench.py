@@ -62,6 +62,8 @@ def parse_args():
     ap.add_argument("--no-shard-point", action="store_true",
                     help="1 GPU, strong scaling: skip the extra leg on a 2^28-key table (the size the reference's kernels can hold)")
     ap.add_argument("--no-extras", action="store_true", help="1 GPU: skip the legs on BASELINE configs 1', 2, 3 and 4")
+    ap.add_argument("--window-gib", type=float, default=0.0,
+                    help="serve tables beyond the TLB's reach in windows of at most this many GiB (default: the library's 58)")
     ap.add_argument("--small-dok", action="store_true",
                     help="instead of the benchmark: one small pass over the DOK tensor and partition kernels (fused "
                          "get over selectors, to_sparse_coo, from_dense, partition scatter) on tables a few times L2; "
@@ -548,6 +550,8 @@ def run_candidate(args):
     total_keys = n_keys * world
     nb = int(n_keys / LOAD_FACTOR)
     n_batches = N_BATCHES if q < (1 << 27) else 2
+    if args.window_gib > 0:
+        L.check(L.lib().dok_set_window_bytes(72 << 30, int(args.window_gib * (1 << 30))), "dok_set_window_bytes")
     # rows of a batch go straight into fixed slices of the owners' memory over NVLink; --no-peer keeps the NCCL
     # all-to-all exchange
     peer_rows = 0 if (world == 1 or args.no_peer) else q

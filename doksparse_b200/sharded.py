@@ -257,48 +257,68 @@ class CudaShardOps:
 
     def sliced_apply_lookup(self, generation, abort, with_values, fallback_value):
         """get (with_values) or remove of what this rank received, source by source, answers into the askers' result
-        regions: this rank's own rows directly, another rank's rows into a local buffer that a copy kernel on a side
-        stream carries over NVLink while the next source's rows are probed (row-sized stores from the probing kernel
-        itself use the link far worse).  Lookups commute, so the other ranks' rows go first; removals go in rank order,
-        because among equal keys of different ranks the earlier rank reports the removal."""
+        regions: this rank's own rows directly, another rank's rows into a local buffer that copy kernels on a side
+        stream carry over NVLink while the next launch probes (row-sized stores from the probing kernel itself use
+        the link far worse).  Lookups commute, so the other ranks' rows go first, in at most two launches over several
+        slices each; removals go source by source in rank order, because among equal keys of different ranks the
+        earlier rank reports the removal."""
         lib = L.lib()
         p = self._sx
         w, rows, r = p["world"], p["slice_rows"], p["rank"]
         plan = p.setdefault("lookup_plans", {}).get((generation, with_values))
         if plan is None:                                  # views and addresses of a generation never change: build once
             counts = self._region(r, generation, 2)
-            plan = []
-            for s in (([s for s in range(w) if s != r] + [r]) if with_values else list(range(w))):
-                keys = self._region(r, generation, 0, rows=rows, row0=s * rows)
-                if s == r:
+
+            def piece(first, n_slices):
+                """slices [first, first + n_slices) of the inbox as one launch; answers go to the local buffer, or --
+                for this rank's own slice -- straight into its result region"""
+                keys = self._region(r, generation, 0, rows=n_slices * rows, row0=first * rows)
+                if first == r and n_slices == 1:
                     out_values = self._region(r, generation, 3, rows=rows, row0=r * rows) if with_values else None
                     out_flags = self._region(r, generation, 4, rows=rows, row0=r * rows)
-                    remote = None
                 else:
-                    out_values = p["answer_values"][s * rows:(s + 1) * rows] if with_values else None
-                    out_flags = p["answer_flags"][s * rows:(s + 1) * rows]
-                    remote = (ctypes.c_void_p(self._region_ptr(s, generation, 3, r * rows)) if with_values else None,
-                              ctypes.c_void_p(self._region_ptr(s, generation, 4, r * rows)))
-                plan.append((keys, counts[s:s + 1], out_values, out_flags, remote))
-            p["lookup_plans"][(generation, with_values)] = plan
-        for keys, count, out_values, out_flags, remote in plan:
+                    out_values = p["answer_values"][first * rows:(first + n_slices) * rows] if with_values else None
+                    out_flags = p["answer_flags"][first * rows:(first + n_slices) * rows]
+                copies = []
+                for s in range(first, first + n_slices):
+                    if s != r:
+                        lo = (s - first) * rows
+                        copies.append((ctypes.c_void_p(self._region_ptr(s, generation, 3, r * rows)) if with_values else None,
+                                       out_values[lo:lo + rows] if with_values else None,
+                                       ctypes.c_void_p(self._region_ptr(s, generation, 4, r * rows)), out_flags[lo:lo + rows],
+                                       counts[s:s + 1]))
+                return (keys, n_slices, counts[first:first + n_slices], out_values, out_flags, copies)
+
             if with_values:
-                self.local.get_sliced(keys, 1, rows, count, abort, fallback_value, out_values, out_flags)
+                # lookups commute: everything the other ranks sent in (at most) two launches -- the slices below and
+                # above this rank's own -- then this rank's own rows, which are probed while the answers travel
+                plan = [piece(0, r)] if r > 0 else []
+                if r + 1 < w:
+                    plan.append(piece(r + 1, w - r - 1))
+                plan.append(piece(r, 1))
             else:
-                self.local.remove_sliced(keys, 1, rows, count, abort, out_flags)
-            if remote is None:
+                # removals source by source in rank order: among equal keys of different ranks the earlier rank reports
+                plan = [piece(s, 1) for s in range(w)]
+            p["lookup_plans"][(generation, with_values)] = plan
+        for keys, n_slices, count, out_values, out_flags, copies in plan:
+            if with_values:
+                self.local.get_sliced(keys, n_slices, rows, count, abort, fallback_value, out_values, out_flags)
+            else:
+                self.local.remove_sliced(keys, n_slices, rows, count, abort, out_flags)
+            if not copies:
                 continue
             if self._copy_stream is None:
-                # high priority: the copy kernel's few blocks must not queue behind the big grid of the next source's
-                # probing, which they are meant to overlap
+                # high priority: the copy kernels' few blocks must not queue behind the big grid of the next launch,
+                # which they are meant to overlap
                 self._copy_stream = torch.cuda.Stream(device=self.device, priority=-1)
             answered = torch.cuda.Event()
             answered.record()
             with torch.cuda.stream(self._copy_stream):
                 self._copy_stream.wait_event(answered)
                 with torch.cuda.device(self.device):
-                    L.check(lib.dok_copy_counted(remote[0], L.ptr(out_values), p["vb"], remote[1], L.ptr(out_flags), 1, rows,
-                                                 L.ptr(count), L.ptr(abort), L.stream_ptr(self.device)), "dok_copy_counted")
+                    for dst_values, src_values, dst_flags, src_flags, one_count in copies:
+                        L.check(lib.dok_copy_counted(dst_values, L.ptr(src_values), p["vb"], dst_flags, L.ptr(src_flags), 1, rows,
+                                                     L.ptr(one_count), L.ptr(abort), L.stream_ptr(self.device)), "dok_copy_counted")
             self._in_flight.append(True)
         self.answers_delivered()
 
