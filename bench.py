@@ -793,7 +793,7 @@ def run_candidate(args):
     extra = {}
     if rank == 0 and world == 1:
         table.close()
-        del table, local, slots, batches
+        del table, local, slots, batches, d0
         torch.cuda.empty_cache()
         if args.scaling == "strong" and not args.no_shard_point:
             extra["shard_point"] = shard_point(torch, device)

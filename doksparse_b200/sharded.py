@@ -633,6 +633,10 @@ class ShardedClosedHashmap:
         main = torch.cuda.current_stream(device)
         # copies that make the inputs contiguous run on the caller's stream, before the side streams branch off
         prepared = [(op[0], op[1].contiguous(), op[2].contiguous() if op[0] == "set" else None) for op in operations]
+        for op, (_, keys, values) in zip(operations, prepared):
+            for made, given in ((keys, op[1]), (values, op[2] if op[0] == "set" else None)):
+                if made is not None and made is not given:
+                    made.record_stream(s_send)            # a copy made here is read on the send stream after we return
         start = torch.cuda.Event()
         start.record(main)
         s_send.wait_event(start)
