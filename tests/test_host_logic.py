@@ -45,3 +45,26 @@ def test_shape_helpers():
     assert util.next_power_of_2(1) == 1 and util.next_power_of_2(10_000_000) == 1 << 24 and util.next_power_of_2(1 << 20) == 1 << 20
     assert list(util.shape_to_stride((4, 3, 2))) == [6, 2, 1]
     assert util.next_prime(14) == 17 and util.next_prime(17) in (17, 19)
+
+
+def test_sliced_exchange_geometry():
+    """Arena layout of the sliced exchange: slices hold the mean plus eight standard deviations of the binomial row
+    count plus a constant, never more than the capacity, start on 256-row boundaries, and the regions of a generation
+    do not overlap."""
+    import math
+    import torch
+    from doksparse_b200.sharded import CudaShardOps
+    key_row, value_row = ((1,), torch.int64), ((2,), torch.float32)
+    for world, cap in ((2, 30000), (8, 1 << 25), (4, 100), (16, 1 << 20), (8, 1)):
+        g = CudaShardOps.sliced_geometry(world, cap, key_row, value_row)
+        rows = g["slice_rows"]
+        mean = cap / world
+        assert rows % 256 == 0 and rows >= min(cap, math.ceil(mean + 8 * math.sqrt(mean))) and rows <= (cap + 255) // 256 * 256
+        assert rows <= max(256, mean + 8 * math.sqrt(mean) + 64 + 256)
+        if cap >= 1 << 25:
+            assert rows <= 1.005 * mean                         # the slack is a fraction of a percent for large batches
+        sizes, offs = g["sizes"], g["offs"]
+        assert sizes[0] >= world * rows * 8 and sizes[1] >= world * rows * 8 and sizes[2] >= world * 8
+        assert sizes[3] >= world * rows * 8 and sizes[4] >= world * rows
+        assert all(o % 256 == 0 for o in offs) and all(offs[i] + sizes[i] == offs[i + 1] for i in range(4))
+        assert g["gen_bytes"] == offs[4] + sizes[4]
