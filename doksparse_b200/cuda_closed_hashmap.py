@@ -322,6 +322,17 @@ class CudaClosedHashmap:
             sh["bound"] = min(sh["bound"], int(sh["ring"][newest[1]]) + newest[2])
         return sh["bound"]
 
+    def _room_for(self, rows, limit):
+        """bound + rows <= limit?  When the bound is too high only because the host runs ahead of the device, wait
+        for the count copies still in flight to land -- oldest first, each an event on the stream -- instead of for the
+        whole stream: the device keeps the work that is queued behind them."""
+        bound = self._element_bound()
+        snaps = self._shared["snapshots"]
+        while bound + rows > limit and snaps:
+            snaps[0][0].synchronize()
+            bound = self._element_bound()
+        return bound + rows <= limit
+
     # ------------------------------------------------------------------ compaction
     def items(self, keys=True, values=True, uuid=True, transposed_keys=False):
         """(keys, values, uuid) of the live slots in slot order, from one pass over the tags."""
@@ -583,7 +594,7 @@ class CudaClosedHashmap:
         self._materialise_parameters()
         limit = int(self._rehash_threshold * self.n_buckets)
         row_counted = new_keys.dtype in L.FLOAT_DTYPES
-        fast = not row_counted and self._element_bound() + n <= limit
+        fast = not row_counted and self._room_for(n, limit)
         if not fast and not row_counted:
             # the bound may only be stale (the host runs ahead of the device): fetch the exact count before paying
             # for a pass that counts the distinct new keys
@@ -666,7 +677,7 @@ class CudaClosedHashmap:
         self._materialise_parameters()
         rows = n_slices * slice_rows
         limit = int(self._rehash_threshold * self.n_buckets)
-        fast = self._element_bound() + rows <= limit
+        fast = self._room_for(rows, limit)
         if not fast:
             torch.cuda.current_stream(self.device).synchronize()
             fast = self.n_elements + rows <= limit
