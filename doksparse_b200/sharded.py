@@ -260,8 +260,8 @@ class CudaShardOps:
         regions: this rank's own rows directly, another rank's rows into a local buffer that copy kernels on a side
         stream carry over NVLink while the next launch probes (row-sized stores from the probing kernel itself use
         the link far worse).  Lookups commute, so the other ranks' rows go first, in at most two launches over several
-        slices each; removals go source by source in rank order, because among equal keys of different ranks the
-        earlier rank reports the removal."""
+        slices each; removals are one launch over all slices (equal keys report once; which of them is unspecified,
+        across ranks as within a batch)."""
         lib = L.lib()
         p = self._sx
         w, rows, r = p["world"], p["slice_rows"], p["rank"]
@@ -290,15 +290,25 @@ class CudaShardOps:
                 return (keys, n_slices, counts[first:first + n_slices], out_values, out_flags, copies)
 
             if with_values:
-                # lookups commute: everything the other ranks sent in (at most) two launches -- the slices below and
-                # above this rank's own -- then this rank's own rows, which are probed while the answers travel
-                plan = [piece(0, r)] if r > 0 else []
-                if r + 1 < w:
-                    plan.append(piece(r + 1, w - r - 1))
+                # lookups commute: everything the other ranks sent in two or three launches over several slices each
+                # (runs of slices below and above this rank's own), then this rank's own rows: the answers of one
+                # launch travel while the next one probes
+                plan, most = [], max(1, (w - 1 + 1) // 2)
+                for first, n_slices in ((0, r), (r + 1, w - r - 1)):
+                    while n_slices > 0:                       # no launch over more than half of the other ranks' slices:
+                        take = min(n_slices, most)            # its answers travel while the next launch probes
+                        plan.append(piece(first, take))
+                        first, n_slices = first + take, n_slices - take
                 plan.append(piece(r, 1))
             else:
-                # removals source by source in rank order: among equal keys of different ranks the earlier rank reports
-                plan = [piece(s, 1) for s in range(w)]
+                # removals: ONE launch over everything received.  Equal keys report once, wherever they came from;
+                # which of them reports is left to the race, as it is among the rows of one batch on one GPU.  The
+                # flags of this rank's own rows take the same way back as the others' (a copy into its result region).
+                keys = self._region(r, generation, 0)
+                flags = p["answer_flags"]
+                copies = [(None, None, ctypes.c_void_p(self._region_ptr(s, generation, 4, r * rows)),
+                           flags[s * rows:(s + 1) * rows], counts[s:s + 1]) for s in range(w)]
+                plan = [(keys, w, counts, None, flags, copies)]
             p["lookup_plans"][(generation, with_values)] = plan
         for keys, n_slices, count, out_values, out_flags, copies in plan:
             if with_values:
@@ -895,7 +905,9 @@ class ShardedClosedHashmap:
         return self._lookup(keys, lambda k, seg: self.ops.local_get(k, seg, fallback_value), True, fallback_value)
 
     def remove(self, keys):
-        """Collective removal -> is_removed[n] aligned to the caller's rows (equal keys report once)."""
+        """Collective removal -> is_removed[n] aligned to the caller's rows.  Equal keys -- in one rank's batch or in
+        several ranks' batches -- report once; which of them reports is unspecified (over the all-to-all exchange it is
+        the first in rank order)."""
         if self._value_shape is None:
             raise RuntimeError("store something first")
         self._check_keys(keys)

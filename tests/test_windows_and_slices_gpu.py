@@ -190,8 +190,14 @@ def test_emulated_ranks_equal_one_serial_table(world, value_columns):
                 np.testing.assert_array_equal(host(gf), wf)
                 assert_same_bytes(host(gv), wv)
             removed = ranks.step("remove", [(dev(d),) for d in doomed])
-            for (_, rf), d in zip(removed, doomed):
-                np.testing.assert_array_equal(host(rf), single.remove_rows(d))
+            # a stored key is reported by exactly one of the rows asking for it, in whichever rank's batch
+            every = np.concatenate(doomed)[:, 0]
+            distinct, inverse = np.unique(every, return_inverse=True)
+            was_stored = single.get(distinct[:, None], fallback_value=0.0)[1].astype(np.int64)
+            reports = np.bincount(inverse, weights=np.concatenate([host(rf) for _, rf in removed]).astype(np.float64),
+                                  minlength=len(distinct)).astype(np.int64)
+            np.testing.assert_array_equal(reports, was_stored)
+            single.remove_rows(distinct[:, None])
             assert sum(o.local.n_elements for o in ranks.ops) == single.n_elements
         # an overflow anywhere makes every rank skip the operation: nothing changes
         before = [o.local.n_elements for o in ranks.ops]
