@@ -73,6 +73,12 @@ class CudaShardOps:
         def __init__(self, ptr, nbytes):
             self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
 
+    # Generations of the arena, used in turn by consecutive operations.  Two would do for correctness (the send of
+    # operation k + 1 overlaps the apply of operation k), but then the fence of operation k must wait for every rank's
+    # apply of k - 1, which turns every apply into a barrier across the ranks; with four, a fence waits for the apply of
+    # three operations back, and the ranks drift freely within a step.
+    GENERATIONS = 4
+
     @staticmethod
     def sliced_geometry(world, capacity_rows, key_row, value_row, slack_sigmas=8.0):
         """Arena layout for batches of up to `capacity_rows` rows per rank.  A slice holds the rows one source sends
@@ -93,13 +99,13 @@ class CudaShardOps:
         sizes = [up(world * rows * kb), up(world * rows * vb), up(world * 8), up(world * rows * vb), up(world * rows)]
         return dict(world=world, cap=cap, slice_rows=rows, kb=kb, vb=vb, kshape=tuple(kshape), kdtype=kdtype,
                     vshape=tuple(vshape), vdtype=vdtype, sizes=sizes, offs=[sum(sizes[:i]) for i in range(5)],
-                    gen_bytes=sum(sizes))
+                    gen_bytes=sum(sizes), generations=CudaShardOps.GENERATIONS)
 
     def sliced_alloc(self, geometry):
-        """This rank's arena (two generations); returns its base address or None."""
+        """This rank's arena (all generations); returns its base address or None."""
         base = ctypes.c_void_p()
         with torch.cuda.device(self.device):
-            if L.lib().dok_peer_alloc(2 * geometry["gen_bytes"], ctypes.byref(base)) != 0:
+            if L.lib().dok_peer_alloc(geometry["generations"] * geometry["gen_bytes"], ctypes.byref(base)) != 0:
                 return None
         return base.value
 
@@ -108,13 +114,13 @@ class CudaShardOps:
         peer's, or -- when several ranks are emulated in one process -- another local allocation)."""
         g = dict(geometry)
         w, rows = g["world"], g["slice_rows"]
-        views = [torch.as_tensor(self._RawDeviceBytes(b, 2 * g["gen_bytes"]), device=self.device) for b in bases]
+        views = [torch.as_tensor(self._RawDeviceBytes(b, g["generations"] * g["gen_bytes"]), device=self.device) for b in bases]
         g.update(bases=list(bases), views=views, rank=rank, group=group, group_apply=group_apply, own_base=own_base, ipc=ipc,
                  status=torch.zeros(1, device=self.device, dtype=torch.long),
                  token_apply=torch.zeros(1, device=self.device),
                  answer_values=torch.empty((w * rows,) + g["vshape"], device=self.device, dtype=g["vdtype"]),
                  answer_flags=torch.empty(w * rows, device=self.device, dtype=torch.bool))
-        for gen in range(2):                                   # counts start at zero
+        for gen in range(g["generations"]):                    # counts start at zero
             self._sx = g
             self._region(rank, gen, 2).zero_()
         self._sx = g
@@ -249,6 +255,9 @@ class CudaShardOps:
 
     def can_pipeline(self):
         return getattr(self, "_sx", None) is not None
+
+    def generations(self):
+        return self._sx["generations"]
 
     def sliced_apply_set(self, generation, abort, assume_unique):
         p = self._sx
@@ -501,6 +510,7 @@ class ShardedClosedHashmap:
         self._seq = 0
         self._streams = None
         self._last_applied = None
+        self._recent_applied = []     # apply-done events of the last GENERATIONS - 1 operations submitted
         self._pending = []            # submissions whose tokens have not been read yet: (operations, results, tokens)
         self._value_shape = None
         self._value_dtype = None
@@ -654,10 +664,11 @@ class ShardedClosedHashmap:
         results = [None] * len(operations)
         with torch.cuda.stream(s_send):
             tokens = torch.zeros((len(operations), 3), device=device, dtype=torch.long)
-        applied = self._last_applied          # table work of an earlier submission that was not waited for
+        n_gen = ops.generations()
+        recent = self._recent_applied         # apply-done events of the last operations (also of earlier submissions)
         for i, op in enumerate(operations):
             kind, keys, values = prepared[i]
-            generation = self._seq & 1
+            generation = self._seq % n_gen
             self._seq += 1
             token = tokens[i]
             marks = [torch.cuda.Event(enable_timing=True) for _ in range(7)] if self.profile is not None else None
@@ -666,10 +677,10 @@ class ShardedClosedHashmap:
             with torch.cuda.stream(s_send):
                 mark(0, s_send)
                 dest = ops.sliced_send(keys, values, generation, want_dest=(kind != "set"), force_overflow=_force_overflow)
-                if applied is not None:
-                    # the inbox generation that the NEXT operation's send overwrites is the one the previous
-                    # operation's apply reads: the fence below (all ranks) must come after that apply
-                    s_send.wait_event(applied)
+                if len(recent) >= n_gen - 1:
+                    # the NEXT operation's send overwrites the generation that the apply of n_gen - 1 operations back
+                    # reads: the fence below (all ranks) must come after that apply, on every rank
+                    s_send.wait_event(recent[-(n_gen - 1)])
                 mark(1, s_send)
                 ops.sliced_fence(token, self._signature(kind))
                 mark(2, s_send)
@@ -705,6 +716,8 @@ class ShardedClosedHashmap:
                 mark(6, s_apply)
                 applied = torch.cuda.Event()
                 applied.record(s_apply)
+            recent.append(applied)
+            del recent[:-(n_gen - 1)]
             if marks:
                 self.profile.append((kind, marks))
             nvtx.range_pop()
@@ -726,6 +739,7 @@ class ShardedClosedHashmap:
                 ev.record(s)
                 main.wait_event(ev)
         self._last_applied = None
+        self._recent_applied = []
         pending, self._pending = self._pending, []
         if not pending:
             return

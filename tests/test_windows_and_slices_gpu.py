@@ -140,7 +140,7 @@ class EmulatedRanks:
 
     def step(self, kind, batches, fallback=None, force=False):
         """batches[r] = (keys,) or (keys, values) of rank r -> per-rank results, or None when the step overflowed"""
-        gen = self.seq & 1
+        gen = self.seq % self.geometry["generations"]
         self.seq += 1
         tokens = [torch.zeros(3, device="cuda", dtype=torch.long) for _ in self.ops]
         dests = []
