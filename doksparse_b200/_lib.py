@@ -117,6 +117,7 @@ def _declare(lib):
         "dok_shard_partition_scatter_sliced": ([P, I, P, I, I64, I, P, P, P, P, P, P, I64, P, P, P], I),
         "dok_copy_counted": ([P, P, I, P, P, I, I64, P, P, P], I),
         "dok_shard_token_prepare": ([P, I64, P, P], I),
+        "dok_set_routing_blocks": ([I], I),
         "dok_shard_token_finish": ([P, P, P], I),
         "dok_peer_alloc": ([I64, P], I),
         "dok_peer_free": ([P], I),

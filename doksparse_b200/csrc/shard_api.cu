@@ -28,23 +28,26 @@ static __global__ void __launch_bounds__(DOK_TPB) k_part_count(DevHash hp, RowKe
                                                                uint8_t *__restrict__ owners,
                                                                ll_t *__restrict__ tile_counts) {
   __shared__ int hist[DOK_MAX_SHARDS];
-  if (threadIdx.x < DOK_MAX_SHARDS) hist[threadIdx.x] = 0;
-  __syncthreads();
   const int lane = threadIdx.x & 31;
-  const ll_t base = (ll_t)blockIdx.x * DOK_PART_TILE;
+  for (ll_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    if (threadIdx.x < DOK_MAX_SHARDS) hist[threadIdx.x] = 0;
+    __syncthreads();
+    const ll_t base = tile * DOK_PART_TILE;
 #pragma unroll
-  for (int r = 0; r < DOK_PART_ROUNDS; r++) {
-    const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    int owner = -1;
-    if (e < keys.n) {
-      owner = dok_owner_shard(keys.hash(hp, e).uuid, n_shards);
-      owners[e] = (uint8_t)owner;
+    for (int r = 0; r < DOK_PART_ROUNDS; r++) {
+      const ll_t e = base + r * DOK_TPB + threadIdx.x;
+      int owner = -1;
+      if (e < keys.n) {
+        owner = dok_owner_shard(keys.hash(hp, e).uuid, n_shards);
+        owners[e] = (uint8_t)owner;
+      }
+      const unsigned peers = __match_any_sync(0xffffffffu, owner);
+      if (owner >= 0 && (peers & ((1u << lane) - 1u)) == 0) atomicAdd(&hist[owner], __popc(peers));
     }
-    const unsigned peers = __match_any_sync(0xffffffffu, owner);
-    if (owner >= 0 && (peers & ((1u << lane) - 1u)) == 0) atomicAdd(&hist[owner], __popc(peers));
+    __syncthreads();
+    // the thread that reads a counter is the one that clears it for the next tile
+    if (threadIdx.x < n_shards) tile_counts[(ll_t)threadIdx.x * tiles + tile] = hist[threadIdx.x];
   }
-  __syncthreads();
-  if (threadIdx.x < n_shards) tile_counts[(ll_t)threadIdx.x * tiles + blockIdx.x] = hist[threadIdx.x];
 }
 
 // In-place exclusive scan of a[0 .. n); a[n] receives the total.  Three small launches: sums of chunks of
@@ -197,14 +200,9 @@ static __global__ void __launch_bounds__(DOK_TPB, 6) k_part_scatter(RowKeys keys
   __shared__ ll_t local_start[DOK_MAX_SHARDS];    // start of the owner's segment in this rank's grouped order
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (dst.status != nullptr && *dst.status != 0) return;       // uniform over the grid
-  for (int i = threadIdx.x; i < n_shards * CELLS; i += DOK_TPB) ((int *)dyn_smem)[i] = 0;
   // one thread per owner fetches its words (a single thread walking the owners would wait for 2 * n_shards dependent
   // loads at the head of every block)
-  if ((int)threadIdx.x < n_shards) {
-    const int o = threadIdx.x;
-    tile_first[o] = tile_offsets[(ll_t)o * tiles + blockIdx.x] - tile_offsets[(ll_t)o * tiles];
-    local_start[o] = shard_counts[n_shards + o];
-  }
+  if ((int)threadIdx.x < n_shards) local_start[threadIdx.x] = shard_counts[n_shards + threadIdx.x];
   __syncthreads();
   if (threadIdx.x == 0) {
     ll_t padded = 0;                              // owner o's segment starts at the sum of the padded counts before it
@@ -214,77 +212,92 @@ static __global__ void __launch_bounds__(DOK_TPB, 6) k_part_scatter(RowKeys keys
       padded += c;
     }
   }
-  __syncthreads();
-  const ll_t base = (ll_t)blockIdx.x * DOK_PART_TILE;
-  int owner[DOK_PART_ROUNDS];
-  int rank[DOK_PART_ROUNDS];                      // same-owner lanes of the warp below this one
+  char *stage_values = stage + (size_t)DOK_PART_TILE * kb;      // cell counts are a multiple of 16 bytes: still aligned
+  for (ll_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    for (int i = threadIdx.x; i < n_shards * CELLS; i += DOK_TPB) ((int *)dyn_smem)[i] = 0;
+    if ((int)threadIdx.x < n_shards)
+      tile_first[threadIdx.x] = tile_offsets[(ll_t)threadIdx.x * tiles + tile] - tile_offsets[(ll_t)threadIdx.x * tiles];
+    __syncthreads();
+    const ll_t base = tile * DOK_PART_TILE;
+    int owner[DOK_PART_ROUNDS];
+    int rank[DOK_PART_ROUNDS];                    // same-owner lanes of the warp below this one
 #pragma unroll
-  for (int r = 0; r < DOK_PART_ROUNDS; r++) {
-    const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    owner[r] = e < keys.n ? (int)owners[e] : -1;
-    const unsigned peers = __match_any_sync(0xffffffffu, owner[r]);
-    rank[r] = __popc(peers & ((1u << lane) - 1u));
-    if (owner[r] >= 0 && rank[r] == 0) before[owner[r]][r * WARPS + warp] = __popc(peers);
-  }
-  __syncthreads();
-  for (int o = warp; o < n_shards; o += WARPS) {  // exclusive scan of the owner's CELLS counts by one warp
-    int run = 0;
-#pragma unroll
-    for (int c0 = 0; c0 < CELLS; c0 += 32) {
-      const int v = before[o][c0 + lane];
-      int inc = v;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, inc, d);
-        if (lane >= d) inc += up;
-      }
-      before[o][c0 + lane] = run + inc - v;
-      run += __shfl_sync(0xffffffffu, inc, 31);
+    for (int r = 0; r < DOK_PART_ROUNDS; r++) {
+      const ll_t e = base + r * DOK_TPB + threadIdx.x;
+      owner[r] = e < keys.n ? (int)owners[e] : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, owner[r]);
+      rank[r] = __popc(peers & ((1u << lane) - 1u));
+      if (owner[r] >= 0 && rank[r] == 0) before[owner[r]][r * WARPS + warp] = __popc(peers);
     }
-    if (lane == 0) tile_total[o] = run;
-  }
-  __syncthreads();
-  if (!STAGED) {
+    __syncthreads();
+    for (int o = warp; o < n_shards; o += WARPS) {  // exclusive scan of the owner's CELLS counts by one warp
+      int run = 0;
+#pragma unroll
+      for (int c0 = 0; c0 < CELLS; c0 += 32) {
+        const int v = before[o][c0 + lane];
+        int inc = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += up;
+        }
+        before[o][c0 + lane] = run + inc - v;
+        run += __shfl_sync(0xffffffffu, inc, 31);
+      }
+      if (lane == 0) tile_total[o] = run;
+    }
+    __syncthreads();
+    if (!STAGED) {
+#pragma unroll
+      for (int r = 0; r < DOK_PART_ROUNDS; r++) {
+        if (owner[r] < 0) continue;
+        const int o = owner[r];
+        const ll_t e = base + r * DOK_TPB + threadIdx.x;
+        const ll_t in_segment = tile_first[o] + before[o][r * WARPS + warp] + rank[r];
+        if (dest_index) dest_index[e] = (dst.slice_rows > 0 ? (ll_t)o * dst.slice_rows : local_start[o]) + in_segment;
+        const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + in_segment;
+        dok_copy_row(dst.keys[o] + row * kb, (const char *)keys.keys + e * kb, kb);
+        if (values) dok_copy_row(dst.values[o] + row * vb, values + e * vb, vb);
+      }
+      __syncthreads();                            // the cells are cleared for the next tile
+      continue;
+    }
+    if (threadIdx.x == 0) {
+      int run = 0;
+      for (int o = 0; o < n_shards; o++) { sorted_start[o] = run; run += tile_total[o]; }
+      sorted_start[n_shards] = run;
+    }
+    __syncthreads();
 #pragma unroll
     for (int r = 0; r < DOK_PART_ROUNDS; r++) {
       if (owner[r] < 0) continue;
       const int o = owner[r];
       const ll_t e = base + r * DOK_TPB + threadIdx.x;
-      const ll_t in_segment = tile_first[o] + before[o][r * WARPS + warp] + rank[r];
-      if (dest_index) dest_index[e] = (dst.slice_rows > 0 ? (ll_t)o * dst.slice_rows : local_start[o]) + in_segment;
-      const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + in_segment;
-      dok_copy_row(dst.keys[o] + row * kb, (const char *)keys.keys + e * kb, kb);
-      if (values) dok_copy_row(dst.values[o] + row * vb, values + e * vb, vb);
+      const int in_tile = before[o][r * WARPS + warp] + rank[r];
+      if (dest_index) dest_index[e] = (dst.slice_rows > 0 ? (ll_t)o * dst.slice_rows : local_start[o]) + tile_first[o] + in_tile;
+      const int pos = sorted_start[o] + in_tile;
+      dok_copy_row(stage + (size_t)pos * kb, (const char *)keys.keys + e * kb, kb);
+      if (values) dok_copy_row(stage_values + (size_t)pos * vb, values + e * vb, vb);
     }
-    return;
+    __syncthreads();
+    const int tile_rows = sorted_start[n_shards];
+    for (int i = threadIdx.x; i < tile_rows; i += DOK_TPB) {
+      int o = 0;                                  // the run that sorted position i belongs to
+      while (sorted_start[o + 1] <= i) o++;
+      const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + tile_first[o] + (i - sorted_start[o]);
+      dok_copy_row(dst.keys[o] + row * kb, stage + (size_t)i * kb, kb);
+      if (values) dok_copy_row(dst.values[o] + row * vb, stage_values + (size_t)i * vb, vb);
+    }
+    __syncthreads();                              // the staging area and the cells are reused by the next tile
   }
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int o = 0; o < n_shards; o++) { sorted_start[o] = run; run += tile_total[o]; }
-    sorted_start[n_shards] = run;
-  }
-  __syncthreads();
-  char *stage_values = stage + (size_t)DOK_PART_TILE * kb;      // cell counts are a multiple of 16 bytes: still aligned
-#pragma unroll
-  for (int r = 0; r < DOK_PART_ROUNDS; r++) {
-    if (owner[r] < 0) continue;
-    const int o = owner[r];
-    const ll_t e = base + r * DOK_TPB + threadIdx.x;
-    const int in_tile = before[o][r * WARPS + warp] + rank[r];
-    if (dest_index) dest_index[e] = (dst.slice_rows > 0 ? (ll_t)o * dst.slice_rows : local_start[o]) + tile_first[o] + in_tile;
-    const int pos = sorted_start[o] + in_tile;
-    dok_copy_row(stage + (size_t)pos * kb, (const char *)keys.keys + e * kb, kb);
-    if (values) dok_copy_row(stage_values + (size_t)pos * vb, values + e * vb, vb);
-  }
-  __syncthreads();
-  const int tile_rows = sorted_start[n_shards];
-  for (int i = threadIdx.x; i < tile_rows; i += DOK_TPB) {
-    int o = 0;                                    // the run that sorted position i belongs to
-    while (sorted_start[o + 1] <= i) o++;
-    const ll_t row = (dst.row0[o] >= 0 ? dst.row0[o] : local_start[o]) + tile_first[o] + (i - sorted_start[o]);
-    dok_copy_row(dst.keys[o] + row * kb, stage + (size_t)i * kb, kb);
-    if (values) dok_copy_row(dst.values[o] + row * vb, stage_values + (size_t)i * vb, vb);
-  }
+}
+
+// Blocks of the two partition passes: one per tile by default; a smaller number makes every block walk several tiles,
+// which leaves room on the SMs for the table kernels of another operation running at the same time.
+static std::atomic<int> g_routing_blocks{0};
+static unsigned dok_routing_grid(ll_t tiles) {
+  const int cap = g_routing_blocks.load(std::memory_order_relaxed);
+  return (unsigned)(cap > 0 && tiles > cap ? cap : tiles);
 }
 
 // staged when the tile's rows fit the shared memory a block may ask for without crowding out its neighbours
@@ -298,10 +311,10 @@ static int dok_launch_scatter(const RowKeys &rk, int kb, const char *values, int
   if (n_shards > 2 && stage_bytes <= DOK_PART_STAGE_LIMIT) {
     // more than the 48 KiB a kernel gets by default: the attribute is per device, and setting it again is cheap
     cudaFuncSetAttribute(k_part_scatter<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DOK_PART_STAGE_LIMIT + 16 * 1024);
-    k_part_scatter<true><<<(unsigned)tiles, DOK_TPB, cell_bytes + stage_bytes, st>>>(rk, kb, values, vb, owners, n_shards, tiles,
+    k_part_scatter<true><<<dok_routing_grid(tiles), DOK_TPB, cell_bytes + stage_bytes, st>>>(rk, kb, values, vb, owners, n_shards, tiles,
                                                                                      tile_offsets, shard_counts, dst, dest_index);
   } else {
-    k_part_scatter<false><<<(unsigned)tiles, DOK_TPB, cell_bytes, st>>>(rk, kb, values, vb, owners, n_shards, tiles, tile_offsets,
+    k_part_scatter<false><<<dok_routing_grid(tiles), DOK_TPB, cell_bytes, st>>>(rk, kb, values, vb, owners, n_shards, tiles, tile_offsets,
                                                                         shard_counts, dst, dest_index);
   }
   return dok_check_launch();
@@ -393,7 +406,7 @@ int dok_shard_partition_count(const dok_hash_params *hp, const void *keys, int64
   const ll_t tiles = dok_partition_tiles(n);
   if (tiles > 0) {
     RowKeys rk{keys, n};
-    k_part_count<<<(unsigned)tiles, DOK_TPB, 0, st>>>(dh, rk, n_shards, tiles, owners, (ll_t *)tile_offsets);
+    k_part_count<<<dok_routing_grid(tiles), DOK_TPB, 0, st>>>(dh, rk, n_shards, tiles, owners, (ll_t *)tile_offsets);
     int rc = dok_check_launch();
     if (rc != DOK_OK) return rc;
   }
@@ -480,6 +493,12 @@ int dok_shard_partition_scatter_sliced(const void *keys, int key_bytes, const vo
   RowKeys rk{keys, n};
   return dok_launch_scatter(rk, key_bytes, (const char *)values, value_bytes, owners, n_shards, (const ll_t *)tile_offsets,
                             (const ll_t *)shard_counts, dst, (ll_t *)dest_index, st);
+}
+
+int dok_set_routing_blocks(int blocks) {
+  if (blocks < 0) return DOK_BAD_ARG;
+  g_routing_blocks.store(blocks, std::memory_order_relaxed);
+  return DOK_OK;
 }
 
 int dok_shard_token_prepare(const int64_t *status, int64_t signature, int64_t *token, void *stream) {

@@ -204,10 +204,30 @@ class CudaShardOps:
         cache[asked] = view = flat.view(dtype).view((rows,) + tuple(shape))
         return view
 
-    def sliced_send(self, keys, values, generation, want_dest, force_overflow=False):
+    # Blocks per SM of the partition passes while the table kernels of another operation are running: with one block
+    # per tile the (high-priority) send stage takes three quarters of every SM's threads for as long as it runs and
+    # the table work stands still, so nothing overlaps; a few blocks per SM walking the tiles keep NVLink busy and
+    # leave the rest of the SM to the probing (2 ranks, 2^25 rows each: 6.6 ms per step uncapped, 5.3 with 2 to 4
+    # blocks per SM, 8.0 with 1.5 -- a grid that is not a whole number of waves is worse than none).
+    OVERLAPPED_ROUTING_BLOCKS_PER_SM = 3
+
+    def sliced_send(self, keys, values, generation, want_dest, force_overflow=False, overlapped=False):
         """SEND stage: owner of every row, then every row into its owner's inbox slice for this rank and this rank's
         row counts into the owners' count words -- plain stores, over NVLink for other ranks' memory.  A slice that
-        would overflow raises the sticky status word instead, and nothing is stored.  -> dest_index (or None)."""
+        would overflow raises the sticky status word instead, and nothing is stored.  -> dest_index (or None).
+        overlapped: table kernels of an earlier operation are in flight; the partition passes then run on a small
+        grid (see OVERLAPPED_ROUTING_BLOCKS_PER_SM)."""
+        lib = L.lib()
+        if overlapped:
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            L.check(lib.dok_set_routing_blocks(self.OVERLAPPED_ROUTING_BLOCKS_PER_SM * sms), "dok_set_routing_blocks")
+        try:
+            return self._sliced_send(keys, values, generation, want_dest, force_overflow)
+        finally:
+            if overlapped:
+                L.check(lib.dok_set_routing_blocks(0), "dok_set_routing_blocks")
+
+    def _sliced_send(self, keys, values, generation, want_dest, force_overflow):
         lib = L.lib()
         p = self._sx
         w, rows, r = p["world"], p["slice_rows"], p["rank"]
@@ -483,6 +503,7 @@ class ShardedClosedHashmap:
     the caller's row order.  `prime1..beta2` must be given explicitly (lists or tensors of key_size entries) and be
     identical on all ranks: they define the uuid, which decides the owner shard.
     """
+    SEND_STREAM_PRIORITY = -1       # the send stage's stream: high priority (see run())
 
     KINDS = {"get": 1, "set": 2, "remove": 3}
 
@@ -648,7 +669,7 @@ class ShardedClosedHashmap:
         if self._streams is None:
             # the send stage runs at high priority: its kernels are short, and behind the big grids of the table work
             # they would otherwise only start when those have handed out all their blocks
-            self._streams = (torch.cuda.Stream(device=device, priority=-1), torch.cuda.Stream(device=device))
+            self._streams = (torch.cuda.Stream(device=device, priority=self.SEND_STREAM_PRIORITY), torch.cuda.Stream(device=device))
         s_send, s_apply = self._streams
         main = torch.cuda.current_stream(device)
         # copies that make the inputs contiguous run on the caller's stream, before the side streams branch off
@@ -676,7 +697,8 @@ class ShardedClosedHashmap:
             nvtx.range_push(f"dok.sharded.{kind}.send")
             with torch.cuda.stream(s_send):
                 mark(0, s_send)
-                dest = ops.sliced_send(keys, values, generation, want_dest=(kind != "set"), force_overflow=_force_overflow)
+                dest = ops.sliced_send(keys, values, generation, want_dest=(kind != "set"), force_overflow=_force_overflow,
+                                       overlapped=(i > 0 or bool(self._pending)))
                 if len(recent) >= n_gen - 1:
                     # the NEXT operation's send overwrites the generation that the apply of n_gen - 1 operations back
                     # reads: the fence below (all ranks) must come after that apply, on every rank

@@ -357,6 +357,10 @@ int dok_shard_partition_scatter_sliced(const void *keys, int key_bytes, const vo
                                        int64_t *const *count_dst, int64_t slice_rows, const int64_t *status,
                                        int64_t *dest_index, void *stream);
 int dok_shard_token_prepare(const int64_t *status, int64_t signature, int64_t *token, void *stream);
+/* Blocks of the two partition passes (dok_shard_partition_count and the scatter calls): 0 = one block per tile of
+ * 2048 rows (the default); a positive number caps the grid and every block walks several tiles, which leaves room
+ * on the SMs for the table kernels of another operation in flight.  Process-wide.  No counterpart in the reference. */
+int dok_set_routing_blocks(int blocks);
 int dok_shard_token_finish(int64_t *token, int64_t *status, void *stream);
 int dok_copy_counted(void *dst_a, const void *src_a, int row_bytes_a, void *dst_b, const void *src_b, int row_bytes_b,
                      int64_t max_rows, const int64_t *count, const int64_t *abort_flag, void *stream);

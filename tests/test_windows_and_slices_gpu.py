@@ -166,10 +166,13 @@ class EmulatedRanks:
         return out
 
 
-@pytest.mark.parametrize("world,value_columns", [(2, 2), (4, 1), (8, 3)])
-def test_emulated_ranks_equal_one_serial_table(world, value_columns):
+@pytest.mark.parametrize("world,value_columns,routing_blocks", [(2, 2, 0), (4, 1, 0), (8, 3, 0), (4, 2, 1), (8, 1, 2)])
+def test_emulated_ranks_equal_one_serial_table(world, value_columns, routing_blocks):
+    """routing_blocks > 0: the partition passes run with that many blocks, each walking several tiles"""
+    from doksparse_b200 import _lib as L
     params = good_parameters(1 << 15, 1, seed=world)
     cap = 6000
+    L.check(L.lib().dok_set_routing_blocks(routing_blocks), "dok_set_routing_blocks")
     ranks = EmulatedRanks(world, 1 << 15, cap, params, value_columns)
     single = port.OracleHashmap(n_buckets=(1 << 15) * world, **params)
     rng = np.random.default_rng(world)
@@ -209,3 +212,4 @@ def test_emulated_ranks_equal_one_serial_table(world, value_columns):
         assert ranks.step("get", [(dev(q),) for q in qs]) is not None              # the status word was reset
     finally:
         ranks.close()
+        L.check(L.lib().dok_set_routing_blocks(0), "dok_set_routing_blocks")
