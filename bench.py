@@ -500,6 +500,25 @@ def shard_point(torch, device):
         step(s)
     torch.cuda.synchronize()
     ms, phase = time_steps(torch, step, 10, 4)
+
+    # the same step as the drop-in API is called: remove() makes the keys unique first, as the reference's does
+    # (cuda_closed_hashmap.py:423-454 of the reference); compare with reference_kernels_gpu.api_path
+    def api_step(b):
+        d = batches[b % N_BATCHES]
+        table.get(d["get_keys"])
+        table.set(d["set_keys"], d["set_values"])
+        table.remove(d["fresh_keys"])
+
+    for s in range(3):
+        api_step(s)
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a0.record()
+    for s in range(5):
+        api_step(3 + s)
+    a1.record()
+    torch.cuda.synchronize()
+    api_ms = a0.elapsed_time(a1) / 5
     # load 0.5, the point the north-star is worded on: the same keys in a table of 2 * n_keys buckets
     half = CudaClosedHashmap(n_buckets=2 * n_keys, device=device, rehash_threshold=0.95, **fixed_parameters())
     build_table(torch, half, n_keys, 0, device)
@@ -517,6 +536,8 @@ def shard_point(torch, device):
     peak, _ = measured_peak_gbs()
     return {"keys": n_keys, "batch": q, "value": 2 * q / (ms * 1e-3) / 1e6, "unit": "Mops/s", "ms_per_step": ms,
             "get_ms": phase[0], "set_ms": phase[1], "remove_ms": phase[2], "results_ok": ok,
+            "api_path": {"value": 2 * q / (api_ms * 1e-3) / 1e6, "unit": "Mops/s", "ms_per_step": api_ms, "steps": 5,
+                         "what": "get, set, remove() with its unique-keys pass, as the drop-in API is called"},
             "get_frac": algorithmic_bytes("get") * q / (phase[0] * 1e-3) / 1e9 / peak,
             "set_frac": algorithmic_bytes("set") * q / (phase[1] * 1e-3) / 1e9 / peak,
             "remove_frac": algorithmic_bytes("remove") * (q - int(q * HIT_FRACTION)) / (phase[2] * 1e-3) / 1e9 / peak,
