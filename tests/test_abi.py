@@ -34,6 +34,29 @@ def test_library_exports_every_declared_symbol():
     assert set(_lib.EXPORTED) == set(declared_functions())
 
 
+def declared_parameter_counts():
+    """function name -> number of parameters of its prototype in include/doksparse.h"""
+    text = open(os.path.join(ROOT, "include", "doksparse.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    counts = {}
+    for name, params in re.findall(r"\b(dok_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text):
+        params = params.strip()
+        counts[name] = 0 if params in ("", "void") else params.count(",") + 1
+    return counts
+
+
+def test_python_bindings_match_the_header_arity():
+    """A prototype that gains or loses a parameter in the header must change in the ctypes table too: with a stale
+    argtypes list ctypes would pass garbage for the missing argument without any complaint."""
+    from doksparse_b200 import _lib
+    lib = _lib.lib()
+    counts = declared_parameter_counts()
+    assert set(counts) == set(declared_functions())
+    for name, n in counts.items():
+        argtypes = getattr(lib, name).argtypes
+        assert argtypes is not None and len(argtypes) == n, f"{name}: header has {n} parameters, _lib.py declares {argtypes}"
+
+
 def test_slot_geometry():
     from doksparse_b200 import _lib
     lib = _lib.lib()
