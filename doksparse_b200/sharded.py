@@ -188,7 +188,7 @@ class CudaShardOps:
 
     def _region(self, rank, generation, which, rows=None, row0=0):
         """Typed view of region `which` (0 inbox keys, 1 inbox values, 2 inbox counts, 3 result values, 4 result
-        flags) of `rank`'s arena, generation 0 / 1, rows [row0, row0 + rows)."""
+        flags) of `rank`'s arena, generation 0 .. GENERATIONS - 1, rows [row0, row0 + rows)."""
         p = self._sx
         cache = p.setdefault("region_cache", {})
         hit = cache.get((rank, generation, which, rows, row0))
