@@ -57,6 +57,11 @@ def parse_args():
                     help="multi-GPU: exchange rows with NCCL all-to-all instead of stores into the peers' memory")
     ap.add_argument("--no-pipeline", action="store_true",
                     help="multi-GPU: call get / set / remove one after the other instead of one pipelined submission")
+    ap.add_argument("--send-blocks-per-sm", type=float, default=None,
+                    help="multi-GPU: blocks per SM of the partition kernels while table kernels of another operation are "
+                         "in flight (library default 3; 0 = one block per tile of 2048 rows, the whole grid at once)")
+    ap.add_argument("--send-priority", type=int, default=None, choices=[-1, 0],
+                    help="multi-GPU: priority of the stream the send stages run on (library default -1, high)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-shard-point", action="store_true",
@@ -411,7 +416,13 @@ def run_reference(args):
 def workload_config(args, world):
     n_keys, q = sizes_per_gpu(args, world)
     n_batches = N_BATCHES if q < (1 << 27) else 2
+    tuning = {}
+    if getattr(args, "send_blocks_per_sm", None) is not None:
+        tuning["send_blocks_per_sm"] = args.send_blocks_per_sm
+    if getattr(args, "send_priority", None) is not None:
+        tuning["send_priority"] = args.send_priority
     return {
+        **tuning,
         "workload": "BASELINE configs[4]: hash-sharded CudaClosedHashmap, int64 keys uniform in [0,2^62) -> float32[2], "
                     f"{n_keys * world} keys in total ({n_keys} per GPU) at load {LOAD_FACTOR}; a step = get of {q * world} rows "
                     f"(80% hits) + set of {q * world} rows (80% overwrite, 20% insert) + remove of the inserted rows, "
@@ -566,6 +577,11 @@ def run_candidate(args):
         os.environ.setdefault("TORCH_NCCL_HIGH_PRIORITY", "1")
         dist.init_process_group("nccl", device_id=device)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    if args.send_blocks_per_sm is not None:
+        from doksparse_b200.sharded import CudaShardOps
+        CudaShardOps.OVERLAPPED_ROUTING_BLOCKS_PER_SM = args.send_blocks_per_sm
+    if args.send_priority is not None:
+        ShardedClosedHashmap.SEND_STREAM_PRIORITY = args.send_priority
 
     n_keys, q = sizes_per_gpu(args, world)
     total_keys = n_keys * world

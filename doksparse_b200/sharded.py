@@ -220,7 +220,7 @@ class CudaShardOps:
         lib = L.lib()
         if overlapped:
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            L.check(lib.dok_set_routing_blocks(self.OVERLAPPED_ROUTING_BLOCKS_PER_SM * sms), "dok_set_routing_blocks")
+            L.check(lib.dok_set_routing_blocks(int(self.OVERLAPPED_ROUTING_BLOCKS_PER_SM * sms)), "dok_set_routing_blocks")
         try:
             return self._sliced_send(keys, values, generation, want_dest, force_overflow)
         finally:
